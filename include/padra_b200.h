@@ -1,0 +1,160 @@
+/*
+ * padra_b200 -- C ABI of the B200 (sm_100a) EXL3 mixture-of-experts expert kernels.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues work on the given CUDA stream and
+ * returns at once; none of them allocates, frees, synchronises or reads device memory on the host, so all
+ * of them may be recorded into CUDA graphs.  Activations follow the reference's conventions: decode-side
+ * buffers are `float` arrays holding BF16-representable values, prefill-side buffers are BF16 bit patterns
+ * in `unsigned short`.  Errors discovered on the device (a descriptor that does not fit the call, an expert
+ * id outside 0..63, a non-finite or FP16-overflowing value) set the caller's sticky `*bad` flag with an
+ * atomic exchange and skip the affected work; nothing traps.  Host-side argument errors are returned as a
+ * status code whose values equal mellum16::StatusCode (include/mellum16/status.h:11-21).
+ *
+ * The reference has no FFI for this path: its launchers are inline host functions in headers of one
+ * translation unit.  Each function below names the reference launcher (file:line) whose argument list it
+ * keeps; the trailing `hidden` / `inter` arguments replace the Mellum dimensions (2304 / 896) the reference
+ * hard-codes, and `stream` is a cudaStream_t.
+ */
+#ifndef PADRA_B200_H
+#define PADRA_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define PADRA_API
+#else
+#define PADRA_API __attribute__((visibility("default")))
+#endif
+
+/* Status codes: numerically mellum16::StatusCode (include/mellum16/status.h:11-21). */
+enum {
+  PADRA_OK = 0,
+  PADRA_INVALID_ARGUMENT = 1,
+  PADRA_UNSUPPORTED = 5,
+  PADRA_RESOURCE_EXHAUSTED = 6,
+  PADRA_INTERNAL = 8
+};
+
+/* Weight descriptor: field for field the reference's DeviceMatrix (src/cuda/device_matrix.cuh:6-13),
+ * 56 bytes.  rows = outputs, cols = inputs; format 3 = K4, 5 = K6, 6 = K3 (:30-44).  data holds
+ * (cols/16)*(rows/16) tiles of 32*rate bytes, input-block-major; suh/svh are FP16 bit patterns. */
+typedef struct padra_matrix {
+  const unsigned char *data;
+  const unsigned char *scales;
+  const float *divisor;
+  int rows, cols, format;
+  const uint16_t *suh;
+  const uint16_t *svh;
+} padra_matrix;
+
+/* Prefill tile descriptor: src/runtime/exl3_masked_schedule.h:6-8. */
+typedef struct padra_tile {
+  int expert, begin, valid_rows;
+} padra_tile;
+
+typedef void *padra_stream; /* cudaStream_t */
+
+PADRA_API int padra_version(void);
+PADRA_API const char *padra_status_string(int status);
+/* Returns PADRA_OK when the current device is an sm_100 part this library's kernels were built for. */
+PADRA_API int padra_device_supported(void);
+
+/* ---- decode, M = 1 --------------------------------------------------------------------------------
+ * exl3_mma_dual::Launch (src/cuda/expert_exl3_decode_dual.cuh:132-146).  matrices is the table indexed
+ * (layer*64+expert)*3+part, part 0 = gate, 1 = up, 2 = down.  ids[pairs] are expert ids.  part == 0 computes
+ * gate into output and up into other_output in one launch.  Input row is pair/8 for gate/up and pair for
+ * down; output row is pair.  scratch and ranges are accepted for signature compatibility and unused. */
+PADRA_API int padra_exl3_decode_launch(const padra_matrix *matrices, int layer, int part, const int *ids,
+                                       const float *input, float *output, float *scratch, int pairs, int *bad,
+                                       padra_stream stream, unsigned *ranges, float *other_output, int rate,
+                                       int hidden, int inter);
+
+/* ---- decode, M = 2..16 rows sharing decoded tiles ---------------------------------------------------
+ * mtp_experts::BuildUnion<true> (src/cuda/mtp_experts.cuh:7-40): per expert a row mask, the slot each row
+ * used, and the ascending list of active experts.  slots is [64][slot_stride]; the reference fixes the
+ * stride at 5 (its kRows) and rows at 2..5, this library accepts rows 1..16 with slot_stride >= rows. */
+PADRA_API int padra_mtp_build_union(const int *ids, unsigned *masks, int *slots, int rows, int *bad,
+                                    int *active_experts, int *active_count, padra_stream stream, int slot_stride);
+/* mtp_experts::Launch (src/cuda/mtp_experts.cuh:225-245).  Gate/up read input row r, down reads row
+ * r*8+slot; every part writes output row r*8+slot.  part == 0 writes gate to output and up to `up`. */
+PADRA_API int padra_mtp_experts_launch(const padra_matrix *matrices, int layer, int part, const unsigned *masks,
+                                       const int *slots, int rows, const float *input, float *output, float *up,
+                                       int *bad, padra_stream stream, const int *active_experts,
+                                       const int *active_count, int rate, int hidden, int inter, int slot_stride);
+
+/* ---- SwiGLU -------------------------------------------------------------------------------------------
+ * exl3_silu_lut::Build / Activate (src/cuda/exl3_silu_lut.cuh:9-31): table[65536] maps the BF16 bits of g
+ * to the BF16 bits of silu(g); gate[i] = B(table[gate[i]] * up[i]). */
+PADRA_API int padra_exl3_silu_build(unsigned short *table, padra_stream stream);
+PADRA_API int padra_exl3_silu_activate(float *gate, const float *up, const unsigned short *table, int count,
+                                       int *bad, padra_stream stream);
+
+/* ---- combine ------------------------------------------------------------------------------------------
+ * Combine (src/cuda/inference.cu:580-594): x[r] = B(x[r] + sum), sum = B(sum + B(down[r][s] * weights[r][s]))
+ * over the eight slots in order.  rows tokens, x [rows][hidden], down [rows][8][hidden]. */
+PADRA_API int padra_combine(float *x, const float *down, const float *weights, int *bad, int rows, int hidden,
+                            padra_stream stream);
+/* exl3_packed_activations::Combine (src/cuda/expert_exl3_prefill_packed_activations.cuh:86-103): the same
+ * with BF16-bit down rows; residual == 0 stores the sum alone. */
+PADRA_API int padra_combine_packed(float *x, const unsigned short *down, const float *weights, int tokens,
+                                   int *bad, int residual, int hidden, padra_stream stream);
+
+/* ---- prefill scheduling -------------------------------------------------------------------------------
+ * fast_expert::Group (src/cuda/expert_schedule.cuh:11-69): groups[e*tokens + n] = n-th pair (token*8+slot)
+ * routed to expert e in ascending pair order, counts[e] their number; validates ids and per-token uniqueness.
+ * exl3_masked::Schedule (src/cuda/expert_exl3_prefill_masked.cuh:12-45): tiles of at most 32 pairs,
+ * experts ascending; capacity (tokens*8+31)/32+64 (src/runtime/exl3_masked_schedule.h:15-17). */
+PADRA_API int padra_expert_group(const int *ids, int *groups, int *counts, int tokens, int *bad,
+                                 padra_stream stream);
+PADRA_API int padra_exl3_schedule(const int *counts, padra_tile *tiles, int *tile_count, int tokens, int *bad,
+                                  padra_stream stream);
+
+/* ---- prefill projection, T >= 4 -----------------------------------------------------------------------
+ * exl3_transport_async64::Launch (src/cuda/expert_exl3_prefill_transport_async64.cuh:136-157) for K4 and
+ * exl3_packed_activations::Launch (src/cuda/expert_exl3_prefill_packed_activations.cuh:250-277) for K3/K6:
+ * one argument list for all three rates.  input is FP32-held BF16 [tokens][hidden] (parts 0, 1); gate/up are
+ * BF16-bit [pairs][inter] (part 2, SwiGLU applied while building the down input); output is BF16-bit
+ * [pairs][rows]; transformed is workspace of pairs*cols halves.  tiles/tile_count/counts/ids are read only
+ * through `groups` and `counts` here; stats and wide_input are accepted and unused.
+ * Returns PADRA_INVALID_ARGUMENT for tokens < 4, where the reference throws. */
+PADRA_API int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer, int part, const int *ids,
+                                        const int *groups, const int *counts, const padra_tile *tiles,
+                                        const int *tile_count, const float *input, unsigned short *output,
+                                        const unsigned short *gate, const unsigned short *up,
+                                        const unsigned short *table, void *transformed, int tokens, int *bad,
+                                        padra_stream stream, unsigned *stats, int wide_input, int rate,
+                                        int hidden, int inter);
+
+/* ---- small-batch projection (T < 4) -------------------------------------------------------------------
+ * exl3_expert::Launch (src/cuda/expert_exl3.cuh:137-151): pairs = tokens*8, input row pair/8 (gate/up) or
+ * pair (down), FP32-held BF16 in and out.  in_scratch / out_scratch are accepted and unused. */
+PADRA_API int padra_exl3_expert_launch(const padra_matrix *matrices, int layer, int part, const int *ids,
+                                       const float *input, float *output, float *in_scratch, float *out_scratch,
+                                       int tokens, int *bad, padra_stream stream, int rate, int hidden, int inter);
+
+/* ---- whole expert layer at decode (M = 1..16), one call ------------------------------------------------
+ * The call order of the reference's decode layer (src/cuda/inference.cu:2963-2975: gate/up projection,
+ * SwiGLU, down projection, combine with residual) behind one entry point.  ids/routing are [tokens][8]
+ * (ascending expert id per token, BF16-valued weights), normalized [tokens][hidden] is the post-norm input,
+ * x [tokens][hidden] the residual stream updated in place.  workspace must hold
+ * padra_exl3_moe_decode_workspace_bytes() bytes and need not be initialised. */
+PADRA_API size_t padra_exl3_moe_decode_workspace_bytes(int tokens, int hidden, int inter);
+PADRA_API int padra_exl3_moe_decode_layer(const padra_matrix *matrices, int layer, const int *ids,
+                                          const float *routing, const float *normalized, float *x, int tokens,
+                                          int rate, int hidden, int inter, const unsigned short *table,
+                                          void *workspace, size_t workspace_bytes, int *bad, padra_stream stream);
+
+/* ---- utilities ------------------------------------------------------------------------------------------
+ * Full FP16 decode of one matrix through the same codec the kernels use: out[input*rows + output].
+ * `matrix` is a device pointer to one descriptor.  For verification; not on the timed path. */
+PADRA_API int padra_exl3_decode_weights(const padra_matrix *matrix, unsigned short *out, int rows, int cols,
+                                        int rate, int *bad, padra_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -223,12 +223,15 @@ class COracle:
 
     @staticmethod
     def matrix(data, suh, svh, rows, cols, rate) -> Matrix:
+        data, suh, svh = (np.ascontiguousarray(a) for a in (data, suh, svh))
         m = Matrix()
         m.data, m.suh, m.svh = data.ctypes.data, suh.ctypes.data, svh.ctypes.data
         m.rows, m.cols, m.format = rows, cols, FORMAT_OF_RATE[rate]
+        m._keep = (data, suh, svh)  # the descriptor only holds addresses
         return m
 
     def decode_matrix(self, data, rows, cols, rate) -> np.ndarray:
+        data = np.ascontiguousarray(data)
         m = Matrix()
         m.data, m.rows, m.cols, m.format = data.ctypes.data, rows, cols, FORMAT_OF_RATE[rate]
         out = np.empty((cols, rows), dtype=np.uint16)
@@ -309,6 +312,7 @@ class RefWeight:
         return (HERE / "_ref" / "libref_weight.so").exists()
 
     def decode_matrix(self, data, rows, cols, rate) -> np.ndarray:
+        data = np.ascontiguousarray(data)
         out = np.empty((cols, rows), dtype=np.float32)
         self.lib.ref_decode_matrix(data.ctypes.data, rows, cols, FORMAT_OF_RATE[rate], out.ctypes.data)
         return out
@@ -316,3 +320,47 @@ class RefWeight:
 
 def ref_kernels_path() -> Path:
     return HERE / "_ref" / "libref_kernels.so"
+
+
+class RefKernels:
+    """_ref/libref_kernels.so: the reference's own CUDA kernels (sm_100a build).  Arguments are raw device
+    addresses (ints); see oracle/ref_kernels_post.h for what each entry launches."""
+
+    def __init__(self, path: os.PathLike | None = None):
+        self.lib = C.CDLL(str(path or ref_kernels_path()))
+        p, i = C.c_void_p, C.c_int
+        sig = {
+            "ref_decode_dual": [p, i, i, p, p, p, p, i, p, p, i, i],
+            "ref_decode_dual_launch": [p, i, i, p, p, p, p, i, p, p, i],
+            "ref_simt_linear": [p, i, i, p, p, p, p, p, i, p, p, i, i],
+            "ref_mtp_build_union": [p, p, p, i, p, p, p, p],
+            "ref_mtp_projection": [p, i, i, p, p, i, p, p, p, p, p, p, p, i, i],
+            "ref_group": [p, p, p, i, p, p],
+            "ref_schedule": [p, p, p, i, p, p],
+            "ref_prefill_launch": [p, i, i, p, p, p, p, p, p, p, p, p, p, p, i, p, p, i],
+            "ref_prefill_generic": [p, i, i, p, p, p, p, p, p, p, p, p, p, p, i, p, p, i, i, i],
+            "ref_silu_build": [p, p],
+            "ref_silu_activate": [p, p, p, i, p, p],
+            "ref_combine": [p, p, p, i, p, p],
+            "ref_combine_packed": [p, p, p, i, p, i, p],
+            "ref_route": [p, p, p, i, p, p],
+            "ref_route_rank_exact": [p, p, p, i, p, p],
+        }
+        for name, args in sig.items():
+            f = getattr(self.lib, name)
+            f.argtypes = args
+            f.restype = i
+
+    @staticmethod
+    def available() -> bool:
+        return ref_kernels_path().exists()
+
+    def __getattr__(self, name):
+        fn = getattr(self.lib, name)
+
+        def call(*args):
+            status = fn(*args)
+            if status != 0:
+                raise RuntimeError(f"{name}: CUDA error {status}")
+
+        return call

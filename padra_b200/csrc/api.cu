@@ -1,0 +1,209 @@
+// The C ABI of the library: argument checks, then the launchers.  No allocation, no synchronisation.
+#include "kernels.cuh"
+
+using namespace padra;
+
+namespace {
+cudaStream_t S(padra_stream s) {
+  return static_cast<cudaStream_t>(s);
+}
+bool RateOk(int rate) {
+  return rate == 3 || rate == 4 || rate == 6;
+}
+size_t Align256(size_t n) {
+  return (n + 255) & ~static_cast<size_t>(255);
+}
+// Layout of the decode-layer workspace: three activation planes, then the row-union tables.
+struct DecodeWorkspace {
+  size_t gate, up, down, masks, slots, active, count, total;
+  DecodeWorkspace(int tokens, int hidden, int inter) {
+    const size_t pairs = static_cast<size_t>(tokens) * kTopK;
+    size_t at = 0;
+    gate = at, at += Align256(pairs * inter * sizeof(float));
+    up = at, at += Align256(pairs * inter * sizeof(float));
+    down = at, at += Align256(pairs * hidden * sizeof(float));
+    masks = at, at += Align256(kExperts * sizeof(unsigned));
+    slots = at, at += Align256(static_cast<size_t>(kExperts) * kMaxDecodeRows * sizeof(int));
+    active = at, at += Align256(kExperts * sizeof(int));
+    count = at, at += Align256(sizeof(int));
+    total = at;
+  }
+};
+} // namespace
+
+extern "C" {
+
+int padra_version(void) {
+  return 100; // 0.1.0
+}
+
+const char *padra_status_string(int status) {
+  switch (status) {
+  case PADRA_OK:
+    return "ok";
+  case PADRA_INVALID_ARGUMENT:
+    return "invalid argument";
+  case PADRA_UNSUPPORTED:
+    return "unsupported";
+  case PADRA_RESOURCE_EXHAUSTED:
+    return "resource exhausted";
+  case PADRA_INTERNAL:
+    return "internal (CUDA error)";
+  default:
+    return "unknown status";
+  }
+}
+
+int padra_device_supported(void) {
+  int device = 0, major = 0;
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess)
+    return PADRA_INTERNAL;
+  return major == 10 ? PADRA_OK : PADRA_UNSUPPORTED;
+}
+
+int padra_exl3_decode_launch(const padra_matrix *matrices, int layer, int part, const int *ids, const float *input,
+                             float *output, float *scratch, int pairs, int *bad, padra_stream stream, unsigned *ranges,
+                             float *other_output, int rate, int hidden, int inter) {
+  (void)scratch;
+  (void)ranges;
+  if (!RateOk(rate))
+    return PADRA_UNSUPPORTED;
+  return LaunchPairProjection(matrices, layer, part, ids, input, output, other_output, pairs, bad, S(stream), rate,
+                              hidden, inter);
+}
+
+int padra_mtp_build_union(const int *ids, unsigned *masks, int *slots, int rows, int *bad, int *active_experts,
+                          int *active_count, padra_stream stream, int slot_stride) {
+  return LaunchBuildUnion(ids, masks, slots, rows, slot_stride, bad, active_experts, active_count, S(stream));
+}
+
+int padra_mtp_experts_launch(const padra_matrix *matrices, int layer, int part, const unsigned *masks, const int *slots,
+                             int rows, const float *input, float *output, float *up, int *bad, padra_stream stream,
+                             const int *active_experts, const int *active_count, int rate, int hidden, int inter,
+                             int slot_stride) {
+  if (!RateOk(rate))
+    return PADRA_UNSUPPORTED;
+  return LaunchUnionProjection(matrices, layer, part, masks, slots, slot_stride, rows, input, output, up, bad, S(stream),
+                               active_experts, active_count, rate, hidden, inter);
+}
+
+int padra_exl3_silu_build(unsigned short *table, padra_stream stream) {
+  return LaunchSiluBuild(table, S(stream));
+}
+
+int padra_exl3_silu_activate(float *gate, const float *up, const unsigned short *table, int count, int *bad,
+                             padra_stream stream) {
+  return LaunchSiluActivate(gate, up, table, count, bad, S(stream));
+}
+
+int padra_combine(float *x, const float *down, const float *weights, int *bad, int rows, int hidden,
+                  padra_stream stream) {
+  return LaunchCombine(x, down, weights, bad, rows, hidden, S(stream));
+}
+
+int padra_combine_packed(float *x, const unsigned short *down, const float *weights, int tokens, int *bad, int residual,
+                         int hidden, padra_stream stream) {
+  return LaunchCombinePacked(x, down, weights, tokens, bad, residual, hidden, S(stream));
+}
+
+int padra_expert_group(const int *ids, int *groups, int *counts, int tokens, int *bad, padra_stream stream) {
+  return LaunchGroup(ids, groups, counts, tokens, bad, S(stream));
+}
+
+int padra_exl3_schedule(const int *counts, padra_tile *tiles, int *tile_count, int tokens, int *bad,
+                        padra_stream stream) {
+  return LaunchSchedule(counts, tiles, tile_count, tokens, bad, S(stream));
+}
+
+int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer, int part, const int *ids, const int *groups,
+                              const int *counts, const padra_tile *tiles, const int *tile_count, const float *input,
+                              unsigned short *output, const unsigned short *gate, const unsigned short *up,
+                              const unsigned short *table, void *transformed, int tokens, int *bad, padra_stream stream,
+                              unsigned *stats, int wide_input, int rate, int hidden, int inter) {
+  (void)stats;
+  (void)wide_input;
+  (void)ids;
+  (void)counts;
+  (void)transformed;
+  if (!RateOk(rate))
+    return PADRA_UNSUPPORTED;
+  if (tokens < 4 || tokens > 2048 || part < 0 || part > 2) // the reference throws below four tokens
+    return PADRA_INVALID_ARGUMENT;
+  if (!matrices || !groups || !tiles || !tile_count || !output || !bad || hidden < 128 || inter < 128 ||
+      (hidden % 128) || (inter % 128) || (part == 2 ? (!gate || !up || !table) : !input))
+    return PADRA_INVALID_ARGUMENT;
+  return LaunchTileProjection(matrices, layer, part, groups, tiles, tile_count, input, output, gate, up, table, tokens,
+                              bad, S(stream), rate, hidden, inter);
+}
+
+int padra_exl3_expert_launch(const padra_matrix *matrices, int layer, int part, const int *ids, const float *input,
+                             float *output, float *in_scratch, float *out_scratch, int tokens, int *bad,
+                             padra_stream stream, int rate, int hidden, int inter) {
+  (void)in_scratch;
+  (void)out_scratch;
+  if (!RateOk(rate))
+    return PADRA_UNSUPPORTED;
+  if (tokens < 1 || part < 0 || part > 2)
+    return PADRA_INVALID_ARGUMENT;
+  // one part per call, FP32-held BF16 out, exactly like the reference's small-batch launcher
+  return LaunchPairProjection(matrices, layer, part, ids, input, output, nullptr, tokens * kTopK, bad, S(stream), rate,
+                              hidden, inter, /*gate_and_up=*/false);
+}
+
+size_t padra_exl3_moe_decode_workspace_bytes(int tokens, int hidden, int inter) {
+  if (tokens < 1 || tokens > kMaxDecodeRows || hidden < 128 || inter < 128)
+    return 0;
+  return DecodeWorkspace(tokens, hidden, inter).total;
+}
+
+int padra_exl3_moe_decode_layer(const padra_matrix *matrices, int layer, const int *ids, const float *routing,
+                                const float *normalized, float *x, int tokens, int rate, int hidden, int inter,
+                                const unsigned short *table, void *workspace, size_t workspace_bytes, int *bad,
+                                padra_stream stream) {
+  if (!RateOk(rate))
+    return PADRA_UNSUPPORTED;
+  if (!matrices || !ids || !routing || !normalized || !x || !table || !workspace || !bad || tokens < 1 ||
+      tokens > kMaxDecodeRows || hidden < 128 || inter < 128 || (hidden % 128) || (inter % 128))
+    return PADRA_INVALID_ARGUMENT;
+  const DecodeWorkspace w(tokens, hidden, inter);
+  if (workspace_bytes < w.total)
+    return PADRA_RESOURCE_EXHAUSTED;
+  auto *base = static_cast<unsigned char *>(workspace);
+  auto *gate = reinterpret_cast<float *>(base + w.gate), *up = reinterpret_cast<float *>(base + w.up),
+       *down = reinterpret_cast<float *>(base + w.down);
+  const int pairs = tokens * kTopK;
+  int status;
+  if (tokens == 1) {
+    status = LaunchPairProjection(matrices, layer, 0, ids, normalized, gate, up, pairs, bad, S(stream), rate, hidden, inter);
+    if (status == PADRA_OK)
+      status = LaunchSiluActivate(gate, up, table, pairs * inter, bad, S(stream));
+    if (status == PADRA_OK)
+      status = LaunchPairProjection(matrices, layer, 2, ids, gate, down, nullptr, pairs, bad, S(stream), rate, hidden, inter);
+  } else {
+    auto *masks = reinterpret_cast<unsigned *>(base + w.masks);
+    auto *slots = reinterpret_cast<int *>(base + w.slots), *active = reinterpret_cast<int *>(base + w.active),
+         *count = reinterpret_cast<int *>(base + w.count);
+    status = LaunchBuildUnion(ids, masks, slots, tokens, kMaxDecodeRows, bad, active, count, S(stream));
+    if (status == PADRA_OK)
+      status = LaunchUnionProjection(matrices, layer, 0, masks, slots, kMaxDecodeRows, tokens, normalized, gate, up, bad,
+                                     S(stream), active, count, rate, hidden, inter);
+    if (status == PADRA_OK)
+      status = LaunchSiluActivate(gate, up, table, pairs * inter, bad, S(stream));
+    if (status == PADRA_OK)
+      status = LaunchUnionProjection(matrices, layer, 2, masks, slots, kMaxDecodeRows, tokens, gate, down, nullptr, bad,
+                                     S(stream), active, count, rate, hidden, inter);
+  }
+  if (status == PADRA_OK)
+    status = LaunchCombine(x, down, routing, bad, tokens, hidden, S(stream));
+  return status;
+}
+
+int padra_exl3_decode_weights(const padra_matrix *matrix, unsigned short *out, int rows, int cols, int rate, int *bad,
+                              padra_stream stream) {
+  if (!RateOk(rate))
+    return PADRA_UNSUPPORTED;
+  return LaunchDecodeWeights(matrix, out, rows, cols, rate, bad, S(stream));
+}
+
+} // extern "C"

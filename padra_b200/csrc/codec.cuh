@@ -1,0 +1,153 @@
+// EXL3 trellis codec for a "row-pair" lane ownership.
+//
+// A 16x16 weight tile is a cyclic MSB-first bit stream of 256*Rate bits held in 8*Rate little-endian u32
+// words.  The weight for (input i, output o) sits at stream position
+//     p = ((o&7)*4 + ((i&7)>>1))*8 + [o>=8]*4 + [i>=8]*2 + (i&1)
+// and its 16-bit state is the window that ends at bit Rate*(p+1) (reference: src/cuda/expert_exl3.cuh:4-22).
+// So the 32 positions with (o&7) == g are the contiguous bits [32*Rate*g, 32*Rate*(g+1)): exactly Rate
+// words at word offset Rate*g.  A lane that loads those Rate words (16 bytes at K4) owns the two output
+// rows g and g+8 for all sixteen inputs of the tile, and needs only the word just before them (the last
+// word of row-pair g-1, cyclically) to complete its first windows.
+//
+// Position inside the lane's 32: q = 8*c + j with c = (i&7)>>1 and j = [o>=8]*4 + [i>=8]*2 + (i&1).
+// Decoded values come out as four groups c = 0..3 of four FP16 pairs in mma.m16n8k16 A-fragment order:
+//     a[c][0] = (row g  ; inputs 2c, 2c+1)     a[c][1] = (row g+8; inputs 2c, 2c+1)
+//     a[c][2] = (row g  ; inputs 2c+8, 2c+9)   a[c][3] = (row g+8; inputs 2c+8, 2c+9)
+// with the even input in the low half.  The same a[c][r] viewed per r over c = 0..3 is one full 16-byte row
+// of an 8x8 FP16 core matrix, which is what the tensor-memory (tcgen05) path stores.
+#pragma once
+#include <cuda_fp16.h>
+#include <cstdint>
+
+#if defined(__CUDACC__)
+#define PADRA_HD __host__ __device__ __forceinline__
+#else
+#define PADRA_HD inline
+#endif
+
+namespace padra {
+namespace codec {
+
+// Bytes one lane owns per tile (32 positions * Rate bits).
+template <int Rate> struct Lane {
+  static_assert(Rate == 3 || Rate == 4 || Rate == 6, "EXL3 rates on this path are K3, K4 and K6");
+  static constexpr int kWords = Rate;
+  static constexpr int kBytes = 4 * Rate;
+  static constexpr int kTileBytes = 32 * Rate;
+};
+
+PADRA_HD uint32_t FunnelRight(uint32_t lo, uint32_t hi, int shift) {
+#if defined(__CUDA_ARCH__)
+  return __funnelshift_r(lo, hi, shift);
+#else
+  return static_cast<uint32_t>(((static_cast<uint64_t>(hi) << 32) | lo) >> (shift & 31));
+#endif
+}
+
+// 0x6400 + (sum of the four bytes of state*0x83DCD12D): the FP16 bit pattern of 1024 + s.  The byte sum is at
+// most 1020, so it never carries into the exponent.
+PADRA_HD uint32_t HashedHalfBits(uint32_t state) {
+  const uint32_t h = state * 0x83DCD12Du;
+#if defined(__CUDA_ARCH__)
+  return __dp4a(h, 0x01010101u, 0x6400u);
+#else
+  return 0x6400u + (h & 255u) + ((h >> 8) & 255u) + ((h >> 16) & 255u) + (h >> 24);
+#endif
+}
+
+#if defined(__CUDACC__)
+// Two states -> two FP16 weights: one packed fused multiply-add (1024+s)*0x1eee + 0xc931, rounded once.
+__device__ __forceinline__ uint32_t PairToHalf2(uint32_t even_state, uint32_t odd_state) {
+  const uint32_t packed = __byte_perm(HashedHalfBits(even_state), HashedHalfBits(odd_state), 0x5410);
+  const __half2 scale = __halves2half2(__ushort_as_half(0x1eee), __ushort_as_half(0x1eee));
+  const __half2 shift = __halves2half2(__ushort_as_half(0xc931), __ushort_as_half(0xc931));
+  const __half2 w = __hfma2(*reinterpret_cast<const __half2 *>(&packed), scale, shift);
+  return *reinterpret_cast<const uint32_t *>(&w);
+}
+#endif
+
+// The 32-bit window ending at the end bit of local position q (odd q): low 16 bits are the state of q, bits
+// [Rate, Rate+16) the state of q-1.  `words` are the lane's own words, `previous` the word before them.
+template <int Rate, int Q>
+PADRA_HD uint32_t PairWindow(const uint32_t (&words)[Rate], uint32_t previous) {
+  constexpr int end = Rate * (Q + 1);
+  constexpr int last = (end - 1) / 32;
+  constexpr int shift = (last + 1) * 32 - end;
+  const uint32_t lo = words[last];
+  const uint32_t hi = last > 0 ? words[last > 0 ? last - 1 : 0] : previous;
+  return shift == 0 ? lo : FunnelRight(lo, hi, shift);
+}
+
+// State (16 bits) of local position q, for host-side checks and the scalar paths.
+template <int Rate> PADRA_HD uint32_t StateAt(const uint32_t (&words)[Rate], uint32_t previous, int q) {
+  const int end = Rate * (q + 1);
+  const int last = (end - 1) / 32;
+  const int shift = (last + 1) * 32 - end;
+  const uint32_t lo = words[last];
+  const uint32_t hi = last > 0 ? words[last - 1] : previous;
+  const uint64_t both = (static_cast<uint64_t>(hi) << 32) | lo;
+  return static_cast<uint32_t>(both >> shift) & 0xffffu;
+}
+
+// Fragment register index for pair m (positions 8c+2m, 8c+2m+1): m bit0 = [i>=8], bit1 = [o>=8].
+PADRA_HD constexpr int FragmentOfPair(int m) {
+  return (m >> 1) + 2 * (m & 1);
+}
+
+#if defined(__CUDACC__)
+template <int Rate, int C, int M>
+__device__ __forceinline__ uint32_t DecodePair(const uint32_t (&words)[Rate], uint32_t previous) {
+  const uint32_t window = PairWindow<Rate, 8 * C + 2 * M + 1>(words, previous);
+  return PairToHalf2((window >> Rate) & 0xffffu, window & 0xffffu);
+}
+// All 32 weights of the lane.
+template <int Rate>
+__device__ __forceinline__ void Decode32(const uint32_t (&words)[Rate], uint32_t previous, uint32_t (&a)[4][4]) {
+#define PADRA_DECODE_GROUP(C)                                            \
+  a[C][FragmentOfPair(0)] = DecodePair<Rate, C, 0>(words, previous);     \
+  a[C][FragmentOfPair(1)] = DecodePair<Rate, C, 1>(words, previous);     \
+  a[C][FragmentOfPair(2)] = DecodePair<Rate, C, 2>(words, previous);     \
+  a[C][FragmentOfPair(3)] = DecodePair<Rate, C, 3>(words, previous);
+  PADRA_DECODE_GROUP(0)
+  PADRA_DECODE_GROUP(1)
+  PADRA_DECODE_GROUP(2)
+  PADRA_DECODE_GROUP(3)
+#undef PADRA_DECODE_GROUP
+}
+
+// The lane's Rate words of one tile.  `lane_bytes` points at tile + g*4*Rate.  Weights are read exactly once
+// per pass, so the loads go through the read-only path without claiming L1 lines.
+template <int Rate> __device__ __forceinline__ void LoadWords(const unsigned char *lane_bytes, uint32_t (&w)[Rate]) {
+  if constexpr (Rate == 4) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(lane_bytes));
+    w[0] = v.x;
+    w[1] = v.y;
+    w[2] = v.z;
+    w[3] = v.w;
+  } else if constexpr (Rate == 6) {
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      uint2 v;
+      asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(lane_bytes + 8 * i));
+      w[2 * i] = v.x;
+      w[2 * i + 1] = v.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 3; ++i)
+      asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(w[i]) : "l"(lane_bytes + 4 * i));
+  }
+}
+#endif
+
+// Place of input i (0..15) of a K16 step inside the permuted activation row the tensor-core B fragments are
+// read from: group c = (i&7)>>1 occupies four consecutive halves {2c, 2c+1, 2c+8, 2c+9}.
+PADRA_HD constexpr int PermutedInput(int i) {
+  return 4 * ((i & 7) >> 1) + 2 * (i >> 3) + (i & 1);
+}
+
+} // namespace codec
+} // namespace padra

@@ -1,0 +1,37 @@
+// Host-side launchers shared between translation units; the C ABI (api.cu) is a thin layer over these.
+#pragma once
+#include "common.cuh"
+
+namespace padra {
+
+int LaunchPairProjection(const Matrix *matrices, int layer, int part, const int *ids, const float *input, float *output,
+                         float *other, int pairs, int *bad, cudaStream_t stream, int rate, int hidden, int inter,
+                         bool gate_and_up = true);
+int LaunchUnionProjection(const Matrix *matrices, int layer, int part, const unsigned *masks, const int *slots,
+                          int slot_stride, int rows, const float *input, float *output, float *up, int *bad,
+                          cudaStream_t stream, const int *active, const int *active_count, int rate, int hidden,
+                          int inter);
+int LaunchBuildUnion(const int *ids, unsigned *masks, int *slots, int rows, int slot_stride, int *bad, int *active,
+                     int *active_count, cudaStream_t stream);
+int LaunchSiluBuild(unsigned short *table, cudaStream_t stream);
+int LaunchSiluActivate(float *gate, const float *up, const unsigned short *table, int count, int *bad,
+                       cudaStream_t stream);
+int LaunchCombine(float *x, const float *down, const float *weights, int *bad, int rows, int hidden,
+                  cudaStream_t stream);
+int LaunchCombinePacked(float *x, const unsigned short *down, const float *weights, int tokens, int *bad, int residual,
+                        int hidden, cudaStream_t stream);
+int LaunchDecodeWeights(const Matrix *matrix, unsigned short *out, int rows, int cols, int rate, int *bad,
+                        cudaStream_t stream);
+
+int LaunchTileProjection(const Matrix *matrices, int layer, int part, const int *groups, const padra_tile *tiles,
+                         const int *tile_count, const float *input, unsigned short *output,
+                         const unsigned short *gate, const unsigned short *up, const unsigned short *table, int tokens,
+                         int *bad, cudaStream_t stream, int rate, int hidden, int inter);
+int LaunchGroup(const int *ids, int *groups, int *counts, int tokens, int *bad, cudaStream_t stream);
+int LaunchSchedule(const int *counts, padra_tile *tiles, int *tile_count, int tokens, int *bad, cudaStream_t stream);
+int LaunchPrefill(const Matrix *matrices, int layer, int part, const int *ids, const int *groups, const int *counts,
+                  const float *input, unsigned short *output, const unsigned short *gate, const unsigned short *up,
+                  const unsigned short *table, void *transformed, int tokens, int *bad, cudaStream_t stream, int rate,
+                  int hidden, int inter);
+
+} // namespace padra

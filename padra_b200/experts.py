@@ -1,0 +1,305 @@
+"""Expert weight tables in device memory and Python-side wrappers of the library's entry points.
+
+`ExpertTable` lays the packed EXL3 tensors of `layers x 64 experts x {gate, up, down}` out in one device arena
+(each region 256-byte aligned, like the reference artifact: src/model/compiled.cpp:187-216) and builds the
+descriptor table the kernels index as (layer*64+expert)*3+part (reference: src/cuda/inference.cu:1599-1602).
+`Workspace` owns the caller-side buffers the entry points expect; the wrappers only pass pointers through.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import binding as B
+
+DESCRIPTOR = np.dtype(
+    {
+        "names": ["data", "scales", "divisor", "rows", "cols", "format", "suh", "svh"],
+        "formats": ["<u8", "<u8", "<u8", "<i4", "<i4", "<i4", "<u8", "<u8"],
+        "offsets": [0, 8, 16, 24, 28, 32, 40, 48],
+        "itemsize": 56,
+    }
+)
+EXPERTS, TOPK = 64, 8
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class ExpertTable:
+    """Packed expert weights of `layers` MoE layers in one device arena plus the descriptor table."""
+
+    def __init__(self, layers: int, hidden: int, inter: int, rate: int, device="cuda"):
+        assert rate in B.FORMAT_OF_RATE and hidden % 128 == 0 and inter % 128 == 0
+        self.layers, self.hidden, self.inter, self.rate = layers, hidden, inter, rate
+        self.device = torch.device(device)
+        self.packed_bytes = hidden * inter * rate // 8
+        # per matrix: packed | suh (2*cols) | svh (2*rows)
+        self.region = {}
+        at = 0
+        for part in range(3):
+            rows, cols = self.shape(part)
+            p = at
+            at += _align(self.packed_bytes)
+            s = at
+            at += _align(2 * cols)
+            v = at
+            at += _align(2 * rows)
+            self.region[part] = (p, s, v)
+        self.expert_bytes = at
+        self.total_bytes = layers * EXPERTS * self.expert_bytes
+        self.arena = torch.empty(self.total_bytes, dtype=torch.uint8, device=self.device)
+        self.descriptors = None  # device uint8 [layers*64*3*56]
+
+    def shape(self, part: int) -> tuple[int, int]:
+        """(rows = outputs, cols = inputs) of part 0 gate, 1 up, 2 down."""
+        return (self.hidden, self.inter) if part == 2 else (self.inter, self.hidden)
+
+    def offsets(self, layer: int, expert: int, part: int) -> tuple[int, int, int]:
+        base = (layer * EXPERTS + expert) * self.expert_bytes
+        p, s, v = self.region[part]
+        return base + p, base + s, base + v
+
+    def algorithmic_bytes_per_expert(self) -> int:
+        """Packed words of the three matrices plus their FP16 sidecars."""
+        return 3 * self.packed_bytes + 2 * 2 * (self.hidden + self.inter) + 2 * (self.inter + self.hidden)
+
+    def finalize(self) -> "ExpertTable":
+        """(Re)builds the device descriptor table from the arena address."""
+        n = self.layers * EXPERTS * 3
+        d = np.zeros(n, dtype=DESCRIPTOR)
+        base = self.arena.data_ptr()
+        idx = np.arange(n)
+        part = idx % 3
+        matrix_base = base + (idx // 3).astype(np.uint64) * np.uint64(self.expert_bytes)
+        for q in range(3):
+            sel = part == q
+            p, s, v = self.region[q]
+            rows, cols = self.shape(q)
+            d["data"][sel] = matrix_base[sel] + np.uint64(p)
+            d["suh"][sel] = matrix_base[sel] + np.uint64(s)
+            d["svh"][sel] = matrix_base[sel] + np.uint64(v)
+            d["rows"][sel], d["cols"][sel] = rows, cols
+        d["format"] = B.FORMAT_OF_RATE[self.rate]
+        self.host_descriptors = d
+        self.descriptors = torch.from_numpy(d.view(np.uint8).copy()).to(self.device)
+        return self
+
+    def descriptor_ptr(self, layer: int = 0, expert: int = 0, part: int = 0) -> int:
+        return self.descriptors.data_ptr() + ((layer * EXPERTS + expert) * 3 + part) * 56
+
+    # ---- filling -------------------------------------------------------------------------------------
+    def fill_random(self, seed: int = 0) -> "ExpertTable":
+        """Seeded synthetic weights generated on the device: uniformly random trellis words (every bit pattern is
+        a valid tail-biting stream) and FP16 sidecars (+-1) * U(0.5, 1.5)."""
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed)
+        words = self.arena.view(torch.int32)
+        chunk = 1 << 26
+        for at in range(0, words.numel(), chunk):
+            n = min(chunk, words.numel() - at)
+            words[at:at + n] = torch.randint(-(2**31), 2**31 - 1, (n,), dtype=torch.int32, device=self.device, generator=g)
+        per = self.arena.view(self.layers * EXPERTS, self.expert_bytes)
+        for part in range(3):
+            rows, cols = self.shape(part)
+            p, s, v = self.region[part]
+            for off, n in ((s, cols), (v, rows)):
+                mag = torch.rand((per.shape[0], n), device=self.device, generator=g) + 0.5
+                sign = torch.randint(0, 2, (per.shape[0], n), device=self.device, generator=g) * 2 - 1
+                side = (mag * sign).to(torch.float16)
+                per[:, off:off + 2 * n] = side.view(torch.uint8)
+        return self.finalize()
+
+    def fill_from_host(self, host) -> "ExpertTable":
+        """Uploads the arrays of an oracle-side host table (same shapes), so CPU and GPU see identical bytes."""
+        staging = np.zeros(self.total_bytes, dtype=np.uint8)
+        for layer in range(self.layers):
+            for e in range(EXPERTS):
+                for part in range(3):
+                    data, suh, svh = host.get(layer, e, part)
+                    p, s, v = self.offsets(layer, e, part)
+                    staging[p:p + data.size] = data
+                    staging[s:s + 2 * suh.size] = suh.view(np.uint8)
+                    staging[v:v + 2 * svh.size] = svh.view(np.uint8)
+        self.arena.copy_(torch.from_numpy(staging))
+        return self.finalize()
+
+    def host_matrix(self, layer: int, expert: int, part: int):
+        """(data u8, suh u16, svh u16) copied back to the host, for checks against the CPU oracle."""
+        rows, cols = self.shape(part)
+        p, s, v = self.offsets(layer, expert, part)
+        a = self.arena
+        return (a[p:p + self.packed_bytes].cpu().numpy().copy(),
+                a[s:s + 2 * cols].cpu().numpy().view(np.uint16).copy(),
+                a[v:v + 2 * rows].cpu().numpy().view(np.uint16).copy())
+
+
+class ExpertKernels:
+    """Thin callers of the C ABI for one table.  Names follow the reference launchers they stand in for."""
+
+    def __init__(self, table: ExpertTable):
+        self.lib = B.load()
+        self.t = table
+        dev = table.device
+        self.bad = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.table = torch.empty(65536, dtype=torch.uint16, device=dev)
+        B.check(self.lib.padra_exl3_silu_build(B.ptr(self.table), B.stream_handle()), "padra_exl3_silu_build")
+        self._workspace = {}
+
+    @property
+    def dims(self):
+        return self.t.hidden, self.t.inter
+
+    def reset_bad(self):
+        self.bad.zero_()
+
+    def bad_flag(self) -> int:
+        return int(self.bad.item())
+
+    # exl3_mma_dual::Launch
+    def decode_launch(self, layer, part, ids, x, output, other=None, stream=None):
+        pairs = ids.numel()
+        st = self.lib.padra_exl3_decode_launch(self.t.descriptors.data_ptr(), layer, part, B.ptr(ids), B.ptr(x), B.ptr(output),
+                                               None, pairs, B.ptr(self.bad), B.stream_handle(stream), None, B.ptr(other),
+                                               self.t.rate, *self.dims)
+        B.check(st, "padra_exl3_decode_launch")
+
+    # exl3_expert::Launch
+    def expert_launch(self, layer, part, ids, x, output, tokens, stream=None):
+        st = self.lib.padra_exl3_expert_launch(self.t.descriptors.data_ptr(), layer, part, B.ptr(ids), B.ptr(x), B.ptr(output),
+                                               None, None, tokens, B.ptr(self.bad), B.stream_handle(stream), self.t.rate,
+                                               *self.dims)
+        B.check(st, "padra_exl3_expert_launch")
+
+    # mtp_experts::BuildUnion + Launch
+    def build_union(self, ids, rows, slot_stride=B.MAX_DECODE_ROWS, stream=None):
+        dev = self.t.device
+        masks = torch.zeros(EXPERTS, dtype=torch.int32, device=dev)
+        slots = torch.full((EXPERTS, slot_stride), -1, dtype=torch.int32, device=dev)
+        active = torch.zeros(EXPERTS, dtype=torch.int32, device=dev)
+        count = torch.zeros(1, dtype=torch.int32, device=dev)
+        st = self.lib.padra_mtp_build_union(B.ptr(ids), B.ptr(masks), B.ptr(slots), rows, B.ptr(self.bad), B.ptr(active),
+                                            B.ptr(count), B.stream_handle(stream), slot_stride)
+        B.check(st, "padra_mtp_build_union")
+        return masks, slots, active, count
+
+    def mtp_launch(self, layer, part, union, rows, x, output, up=None, slot_stride=B.MAX_DECODE_ROWS, stream=None):
+        masks, slots, active, count = union
+        st = self.lib.padra_mtp_experts_launch(self.t.descriptors.data_ptr(), layer, part, B.ptr(masks), B.ptr(slots), rows,
+                                               B.ptr(x), B.ptr(output), B.ptr(up), B.ptr(self.bad), B.stream_handle(stream),
+                                               B.ptr(active), B.ptr(count), self.t.rate, *self.dims, slot_stride)
+        B.check(st, "padra_mtp_experts_launch")
+
+    def silu_activate(self, gate, up, stream=None):
+        st = self.lib.padra_exl3_silu_activate(B.ptr(gate), B.ptr(up), B.ptr(self.table), gate.numel(), B.ptr(self.bad),
+                                               B.stream_handle(stream))
+        B.check(st, "padra_exl3_silu_activate")
+
+    def combine(self, x, down, weights, rows, stream=None):
+        st = self.lib.padra_combine(B.ptr(x), B.ptr(down), B.ptr(weights), B.ptr(self.bad), rows, self.t.hidden,
+                                    B.stream_handle(stream))
+        B.check(st, "padra_combine")
+
+    def combine_packed(self, x, down_bits, weights, tokens, residual=True, stream=None):
+        st = self.lib.padra_combine_packed(B.ptr(x), B.ptr(down_bits), B.ptr(weights), tokens, B.ptr(self.bad),
+                                           int(residual), self.t.hidden, B.stream_handle(stream))
+        B.check(st, "padra_combine_packed")
+
+    # fast_expert::Group + exl3_masked::Schedule
+    def group_and_schedule(self, ids, tokens, stream=None):
+        dev = self.t.device
+        groups = torch.full((EXPERTS * tokens,), -1, dtype=torch.int32, device=dev)
+        counts = torch.zeros(EXPERTS, dtype=torch.int32, device=dev)
+        capacity = (tokens * TOPK + 31) // 32 + EXPERTS
+        tiles = torch.zeros((capacity, 3), dtype=torch.int32, device=dev)
+        tile_count = torch.zeros(1, dtype=torch.int32, device=dev)
+        B.check(self.lib.padra_expert_group(B.ptr(ids), B.ptr(groups), B.ptr(counts), tokens, B.ptr(self.bad),
+                                            B.stream_handle(stream)), "padra_expert_group")
+        B.check(self.lib.padra_exl3_schedule(B.ptr(counts), B.ptr(tiles), B.ptr(tile_count), tokens, B.ptr(self.bad),
+                                             B.stream_handle(stream)), "padra_exl3_schedule")
+        return groups, counts, tiles, tile_count
+
+    # exl3_transport_async64::Launch / exl3_packed_activations::Launch
+    def prefill_launch(self, layer, part, ids, sched, x, output_bits, gate_bits, up_bits, transformed, tokens, stream=None):
+        groups, counts, tiles, tile_count = sched
+        st = self.lib.padra_exl3_prefill_launch(self.t.descriptors.data_ptr(), layer, part, B.ptr(ids), B.ptr(groups),
+                                                B.ptr(counts), B.ptr(tiles), B.ptr(tile_count), B.ptr(x), B.ptr(output_bits),
+                                                B.ptr(gate_bits), B.ptr(up_bits), B.ptr(self.table), B.ptr(transformed),
+                                                tokens, B.ptr(self.bad), B.stream_handle(stream), None, 1, self.t.rate,
+                                                *self.dims)
+        B.check(st, "padra_exl3_prefill_launch")
+
+    def prefill_layer(self, layer, ids, routing, normalized, x, tokens, stream=None):
+        """gate, up, down (SwiGLU inside) and combine with residual for a prefill chunk; x updated in place."""
+        dev, (hidden, inter) = self.t.device, self.dims
+        pairs = tokens * TOPK
+        key = ("prefill", tokens)
+        if key not in self._workspace:
+            self._workspace[key] = (torch.empty((pairs, inter), dtype=torch.uint16, device=dev),
+                                    torch.empty((pairs, inter), dtype=torch.uint16, device=dev),
+                                    torch.empty((pairs, hidden), dtype=torch.uint16, device=dev),
+                                    torch.empty((pairs, max(hidden, inter)), dtype=torch.float16, device=dev))
+        gate, up, down, transformed = self._workspace[key]
+        sched = self.group_and_schedule(ids, tokens, stream)
+        for part, target in ((0, gate), (1, up), (2, down)):
+            self.prefill_launch(layer, part, ids, sched, normalized, target, gate, up, transformed, tokens, stream)
+        self.combine_packed(x, down, routing, tokens, True, stream)
+        return gate, up, down
+
+    # whole decode layer
+    def decode_workspace(self, tokens):
+        key = ("decode", tokens)
+        if key not in self._workspace:
+            n = self.lib.padra_exl3_moe_decode_workspace_bytes(tokens, *self.dims)
+            self._workspace[key] = torch.empty(n, dtype=torch.uint8, device=self.t.device)
+        return self._workspace[key]
+
+    def moe_decode_layer(self, layer, ids, routing, normalized, x, tokens, stream=None):
+        ws = self.decode_workspace(tokens)
+        st = self.lib.padra_exl3_moe_decode_layer(self.t.descriptors.data_ptr(), layer, B.ptr(ids), B.ptr(routing),
+                                                  B.ptr(normalized), B.ptr(x), tokens, self.t.rate, *self.dims,
+                                                  B.ptr(self.table), B.ptr(ws), ws.numel(), B.ptr(self.bad),
+                                                  B.stream_handle(stream))
+        B.check(st, "padra_exl3_moe_decode_layer")
+
+    def decode_weights(self, layer, expert, part, stream=None):
+        rows, cols = self.t.shape(part)
+        out = torch.empty((cols, rows), dtype=torch.uint16, device=self.t.device)
+        st = self.lib.padra_exl3_decode_weights(self.t.descriptor_ptr(layer, expert, part), B.ptr(out), rows, cols, self.t.rate,
+                                                B.ptr(self.bad), B.stream_handle(stream))
+        B.check(st, "padra_exl3_decode_weights")
+        return out
+
+
+# ---- synthetic inputs (seeded; shapes and distributions of the benchmark configurations) --------------------
+def bf16_values(t: torch.Tensor) -> torch.Tensor:
+    """FP32 tensor holding BF16-representable values (the decode-side activation convention)."""
+    return t.to(torch.bfloat16).to(torch.float32)
+
+
+def route_topk(logits: torch.Tensor):
+    """Top-8 of 64 with softmax weights renormalised over the selection, BF16-valued, ascending expert id per
+    token -- the layout the expert kernels expect from the router (reference: src/cuda/inference.cu:482-536).
+    Used to synthesise routing for benchmarks; parity tests take routing from the CPU oracle instead."""
+    p = torch.softmax(logits.float(), dim=-1)
+    w, ids = torch.topk(p, TOPK, dim=-1)
+    w = w / w.sum(dim=-1, keepdim=True)
+    ids, order = torch.sort(ids, dim=-1)
+    w = torch.gather(w, -1, order)
+    return ids.to(torch.int32).contiguous(), bf16_values(w).contiguous()
+
+
+def zipf_routing(tokens: int, seed: int, s: float = 1.1, device="cuda"):
+    """Routing with Zipf(s)-skewed expert popularity: per token, eight distinct experts sampled without
+    replacement with probability proportional to rank^-s, the expert<->rank map a seeded permutation."""
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed)
+    rank = torch.randperm(EXPERTS, generator=g)
+    popularity = torch.empty(EXPERTS)
+    popularity[rank] = torch.arange(1, EXPERTS + 1, dtype=torch.float32) ** (-s)
+    ids = torch.multinomial(popularity.expand(tokens, EXPERTS), TOPK, replacement=False, generator=g)
+    ids, _ = torch.sort(ids, dim=-1)
+    w = torch.rand((tokens, TOPK), generator=g) + 0.1
+    w = w / w.sum(dim=-1, keepdim=True)
+    return ids.to(torch.int32).to(device).contiguous(), bf16_values(w).to(device).contiguous()

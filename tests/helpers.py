@@ -1,0 +1,44 @@
+"""Shared pieces of the GPU parity tests: tolerances and host<->device plumbing."""
+from __future__ import annotations
+
+import numpy as np
+
+# north_star tolerance: expert outputs within 1e-2 relative of the reference's FP32-accumulate result.
+# Two readings are checked: the worst element relative to the largest reference magnitude of its row, and
+# element-wise against max(|ref|, rms/64) so that near-zero elements are not held to an absolute zero.
+REL_TOL = 1e-2
+
+
+def assert_close_rows(actual: np.ndarray, ref: np.ndarray, what: str, tol: float = REL_TOL):
+    actual = np.asarray(actual, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    assert actual.shape == ref.shape, (what, actual.shape, ref.shape)
+    assert np.isfinite(actual).all(), f"{what}: non-finite output"
+    a2 = actual.reshape(-1, actual.shape[-1])
+    r2 = ref.reshape(-1, ref.shape[-1])
+    scale = np.abs(r2).max(axis=1, keepdims=True)
+    scale[scale == 0] = 1.0
+    worst = (np.abs(a2 - r2) / scale).max()
+    assert worst <= tol, f"{what}: max|d|/max|ref| = {worst:.3e} > {tol}"
+    rms = np.sqrt((r2 ** 2).mean(axis=1, keepdims=True))
+    floor = np.maximum(np.abs(r2), rms / 64)
+    elementwise = (np.abs(a2 - r2) / np.maximum(floor, 1e-30)).max()
+    assert elementwise <= tol, f"{what}: element-wise relative error {elementwise:.3e} > {tol}"
+    return worst
+
+
+def u16(t) -> np.ndarray:
+    """uint16 torch tensor -> numpy uint16."""
+    import torch
+
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    assert ((u & 0xFFFF) == 0).all(), "value is not BF16-representable"
+    return (u >> 16).astype(np.uint16)

@@ -1,0 +1,134 @@
+"""GPU parity tests of the prefill-side entry points (grouping, tile schedule, projections, combine)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import exl3_oracle as O
+from tests.helpers import assert_close_rows, bf16_bits_to_f32, u16
+from tests.test_gpu_decode import make, needs_ref, routed_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("tokens", [4, 33, 257, 2048])
+def test_group_and_schedule_match_oracle(oracle, gpu, tokens):
+    from padra_b200.experts import zipf_routing
+
+    _, table, k = make(1, 256, 128, 4, 71, gpu)
+    ids, _ = zipf_routing(tokens, seed=tokens, device=gpu)
+    groups, counts, tiles, tile_count = k.group_and_schedule(ids.reshape(-1), tokens)
+    h_ids = ids.cpu().numpy()
+    og, oc, bad = oracle.group(h_ids, tokens)
+    assert not bad
+    assert (counts.cpu().numpy() == oc).all()
+    g = groups.cpu().numpy().reshape(64, tokens)
+    og = og.reshape(64, tokens)
+    for e in range(64):
+        assert (g[e, : oc[e]] == og[e, : oc[e]]).all()
+    ot, bad = oracle.schedule(oc, tokens)
+    assert not bad
+    n = int(tile_count.item())
+    assert n == len(ot) and (tiles.cpu().numpy()[:n] == ot).all()
+    assert k.bad_flag() == 0
+
+
+def test_group_rejects_duplicate_expert(gpu):
+    _, table, k = make(1, 256, 128, 4, 73, gpu)
+    ids = torch.arange(8, dtype=torch.int32, device=gpu).repeat(4)
+    ids[9] = 0  # token 1 uses expert 0 twice
+    k.group_and_schedule(ids, 4)
+    torch.cuda.synchronize()
+    assert k.bad_flag() == 1
+
+
+@pytest.mark.parametrize("rate", [3, 4, 6])
+@pytest.mark.parametrize("tokens", [4, 37])
+def test_prefill_layer_vs_oracle(oracle, gpu, rate, tokens):
+    hidden, inter = 256, 128
+    host, table, k = make(1, hidden, inter, rate, 79, gpu)
+    x, ids, w = routed_inputs(oracle, tokens, hidden, 15 + tokens)
+    want, bad, (cg, cu, ca, cd) = oracle.moe_layer(host.table, 0, ids, w, x, hidden, inter, capture=True)
+    assert not bad
+    dx = torch.from_numpy(x).to(gpu)
+    xs = dx.clone()
+    gate, up, down = k.prefill_layer(0, torch.from_numpy(ids.reshape(-1)).to(gpu), torch.from_numpy(w.reshape(-1)).to(gpu),
+                                     dx, xs, tokens)
+    torch.cuda.synchronize()
+    assert k.bad_flag() == 0
+    assert_close_rows(bf16_bits_to_f32(u16(gate)), cg, "prefill gate")
+    assert_close_rows(bf16_bits_to_f32(u16(up)), cu, "prefill up")
+    assert_close_rows(bf16_bits_to_f32(u16(down)), cd, "prefill down", tol=2e-2)  # fed by its own gate/up
+    assert_close_rows(xs.cpu().numpy(), want, "prefill layer")
+
+
+def test_prefill_matches_decode_path(oracle, gpu):
+    """The same tokens through the prefill entry points and through the decode layer call."""
+    hidden, inter, tokens = 512, 256, 16
+    host, table, k = make(1, hidden, inter, 4, 83, gpu)
+    x, ids, w = routed_inputs(oracle, tokens, hidden, 17)
+    dids = torch.from_numpy(ids.reshape(-1)).to(gpu)
+    dw = torch.from_numpy(w.reshape(-1)).to(gpu)
+    dx = torch.from_numpy(x).to(gpu)
+    a, b = dx.clone(), dx.clone()
+    k.prefill_layer(0, dids, dw, dx, a, tokens)
+    k.moe_decode_layer(0, dids, dw, dx, b, tokens)
+    assert_close_rows(a.cpu().numpy(), b.cpu().numpy(), "prefill vs decode path")
+    assert k.bad_flag() == 0
+
+
+def test_prefill_refuses_fewer_than_four_tokens(gpu):
+    from padra_b200 import binding as B
+
+    _, table, k = make(1, 256, 128, 4, 89, gpu)
+    st = k.lib.padra_exl3_prefill_launch(table.descriptors.data_ptr(), 0, 0, *([None] * 11), 3, None, None, None, 0, 4, 256, 128)
+    assert st == B.INVALID_ARGUMENT
+
+
+@needs_ref
+@pytest.mark.parametrize("rate", [3, 4, 6])
+def test_against_reference_prefill_kernels_mellum_dims(oracle, gpu, rate):
+    """Reference launchers (K4: exl3_transport_async64::Launch, K3/K6: exl3_packed_activations::Launch) with the
+    reference's Group/Schedule, vs this library, at hidden 2304 / intermediate 896, 64 tokens, Zipf routing."""
+    from padra_b200 import binding as B
+    from padra_b200.experts import ExpertKernels, ExpertTable, bf16_values, zipf_routing
+
+    hidden, inter, tokens = 2304, 896, 64
+    pairs = tokens * 8
+    table = ExpertTable(1, hidden, inter, rate, gpu).fill_random(200 + rate)
+    k = ExpertKernels(table)
+    ref = O.RefKernels()
+    ids, w = zipf_routing(tokens, seed=5, device=gpu)
+    g = torch.Generator(device=gpu)
+    g.manual_seed(1)
+    dx = bf16_values(torch.randn((tokens, hidden), device=gpu, generator=g))
+    bad = torch.zeros(1, dtype=torch.int32, device=gpu)
+    s = B.stream_handle()
+    D = table.descriptors.data_ptr()
+    groups = torch.zeros(64 * tokens, dtype=torch.int32, device=gpu)
+    counts = torch.zeros(64, dtype=torch.int32, device=gpu)
+    tiles = torch.zeros((pairs // 32 + 65, 3), dtype=torch.int32, device=gpu)
+    tile_count = torch.zeros(1, dtype=torch.int32, device=gpu)
+    ref.ref_group(B.ptr(ids), B.ptr(groups), B.ptr(counts), tokens, B.ptr(bad), s)
+    ref.ref_schedule(B.ptr(counts), B.ptr(tiles), B.ptr(tile_count), tokens, B.ptr(bad), s)
+    ours = k.group_and_schedule(ids.reshape(-1), tokens)
+    n = int(tile_count.item())
+    assert torch.equal(ours[1], counts) and int(ours[3].item()) == n and torch.equal(ours[2][:n], tiles[:n])
+    rgate = torch.zeros((pairs, inter), dtype=torch.int16, device=gpu)
+    rup = torch.zeros((pairs, inter), dtype=torch.int16, device=gpu)
+    rdown = torch.zeros((pairs, hidden), dtype=torch.int16, device=gpu)
+    work = torch.zeros((pairs, hidden), dtype=torch.float16, device=gpu)
+    for part, target in ((0, rgate), (1, rup), (2, rdown)):
+        ref.ref_prefill_launch(D, 0, part, B.ptr(ids), B.ptr(groups), B.ptr(counts), B.ptr(tiles), B.ptr(tile_count), B.ptr(dx),
+                               B.ptr(target), B.ptr(rgate), B.ptr(rup), B.ptr(k.table), B.ptr(work), tokens, B.ptr(bad), s, rate)
+    rx = dx.clone()
+    ref.ref_combine_packed(B.ptr(rx), B.ptr(rdown), B.ptr(w), tokens, B.ptr(bad), 1, s)
+    torch.cuda.synchronize()
+    assert int(bad.item()) == 0
+    xs = dx.clone()
+    gate, up, down = k.prefill_layer(0, ids.reshape(-1), w.reshape(-1), dx, xs, tokens)
+    torch.cuda.synchronize()
+    assert k.bad_flag() == 0
+    assert_close_rows(bf16_bits_to_f32(u16(gate)), bf16_bits_to_f32(u16(rgate)), "gate vs reference prefill")
+    assert_close_rows(bf16_bits_to_f32(u16(up)), bf16_bits_to_f32(u16(rup)), "up vs reference prefill")
+    assert_close_rows(bf16_bits_to_f32(u16(down)), bf16_bits_to_f32(u16(rdown)), "down vs reference prefill", tol=2e-2)
+    assert_close_rows(xs.cpu().numpy(), rx.cpu().numpy(), "layer vs reference prefill")
