@@ -36,8 +36,8 @@ static inline float bits_f32(uint32_t u) {
 /* B(): round FP32 to BF16 (nearest even) and widen back.  src/cuda/inference.cu:52-54 */
 float exl3_bf16_round(float x) {
   uint32_t u = f32_bits(x);
-  if ((u & 0x7fffffffu) > 0x7f800000u) /* NaN stays NaN */
-    return bits_f32((u | 0x00400000u) & 0xffff0000u);
+  if ((u & 0x7fffffffu) > 0x7f800000u) /* every NaN becomes the canonical BF16 NaN 0x7fff, as __float2bfloat16_rn does */
+    return bits_f32(0x7fff0000u);
   u += 0x7fffu + ((u >> 16) & 1u);
   return bits_f32(u & 0xffff0000u);
 }

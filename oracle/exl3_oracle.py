@@ -51,7 +51,7 @@ def bf16_round(x: np.ndarray) -> np.ndarray:
     u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
     nan = (u & 0x7FFFFFFF) > 0x7F800000
     r = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
-    r = np.where(nan, (u | 0x00400000) & 0xFFFF0000, r)
+    r = np.where(nan, 0x7FFF0000, r)  # canonical NaN, as __float2bfloat16_rn
     return r.astype(np.uint32).view(np.float32).reshape(np.shape(x))
 
 

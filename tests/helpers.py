@@ -5,11 +5,15 @@ import numpy as np
 
 # north_star tolerance: expert outputs within 1e-2 relative of the reference's FP32-accumulate result.
 # Two readings are checked: the worst element relative to the largest reference magnitude of its row, and
-# element-wise against max(|ref|, rms/64) so that near-zero elements are not held to an absolute zero.
+# element-wise against max(|ref|, floor).  For one operation on identical inputs the floor is rms/64, so only
+# elements that nearly cancel are excused.  For CHAINED results (a down projection fed by its own gate/up, a
+# whole layer) every stage ends in a BF16 rounding whose step is 2^-8 of the value's own magnitude, so an element
+# that nearly cancels carries an absolute error of about one BF16 step of a typical element; there the floor is
+# the row's rms.
 REL_TOL = 1e-2
 
 
-def assert_close_rows(actual: np.ndarray, ref: np.ndarray, what: str, tol: float = REL_TOL):
+def assert_close_rows(actual: np.ndarray, ref: np.ndarray, what: str, tol: float = REL_TOL, chained: bool = False):
     actual = np.asarray(actual, dtype=np.float64)
     ref = np.asarray(ref, dtype=np.float64)
     assert actual.shape == ref.shape, (what, actual.shape, ref.shape)
@@ -21,7 +25,7 @@ def assert_close_rows(actual: np.ndarray, ref: np.ndarray, what: str, tol: float
     worst = (np.abs(a2 - r2) / scale).max()
     assert worst <= tol, f"{what}: max|d|/max|ref| = {worst:.3e} > {tol}"
     rms = np.sqrt((r2 ** 2).mean(axis=1, keepdims=True))
-    floor = np.maximum(np.abs(r2), rms / 64)
+    floor = np.maximum(np.abs(r2), rms if chained else rms / 64)
     elementwise = (np.abs(a2 - r2) / np.maximum(floor, 1e-30)).max()
     assert elementwise <= tol, f"{what}: element-wise relative error {elementwise:.3e} > {tol}"
     return worst

@@ -81,7 +81,7 @@ def test_single_token_projections_and_layer(oracle, gpu, rate):
     # whole layer in one call
     xs = dx.clone()
     k.moe_decode_layer(1, dids, torch.from_numpy(w.reshape(-1)).to(gpu), dx, xs, 1)
-    assert_close_rows(xs.cpu().numpy(), want, "layer")
+    assert_close_rows(xs.cpu().numpy(), want, "layer", chained=True)
     assert k.bad_flag() == 0
 
 
@@ -96,7 +96,7 @@ def test_multi_token_layer(oracle, gpu, rate, tokens):
     dx = torch.from_numpy(x).to(gpu)
     xs = dx.clone()
     k.moe_decode_layer(0, torch.from_numpy(ids.reshape(-1)).to(gpu), torch.from_numpy(w.reshape(-1)).to(gpu), dx, xs, tokens)
-    assert_close_rows(xs.cpu().numpy(), want, f"layer M={tokens}")
+    assert_close_rows(xs.cpu().numpy(), want, f"layer M={tokens}", chained=True)
     assert k.bad_flag() == 0
 
 
@@ -124,7 +124,7 @@ def test_config1_layer_k4(oracle, gpu):
     dx = torch.from_numpy(x).to(gpu)
     xs = dx.clone()
     k.moe_decode_layer(0, torch.from_numpy(ids.reshape(-1)).to(gpu), torch.from_numpy(w.reshape(-1)).to(gpu), dx, xs, 1)
-    assert_close_rows(xs.cpu().numpy(), want, "config-1 layer")
+    assert_close_rows(xs.cpu().numpy(), want, "config-1 layer", chained=True)
     assert k.bad_flag() == 0
 
 
@@ -291,7 +291,7 @@ def test_against_reference_decode_kernels_mellum_dims(oracle, gpu, rate):
     assert torch.equal(ox, rx), "combine differs from the reference kernel on identical inputs"
     full = dx.clone()
     k.moe_decode_layer(0, dids, dw, dx, full, 1)
-    assert_close_rows(full.cpu().numpy(), rx.cpu().numpy(), "layer vs reference kernels")
+    assert_close_rows(full.cpu().numpy(), rx.cpu().numpy(), "layer vs reference kernels", chained=True)
     assert int(bad.item()) == 0 and k.bad_flag() == 0
 
 
