@@ -35,6 +35,9 @@ sys.path.insert(0, str(ROOT))
 
 HIDDEN, INTER, EXPERTS, TOPK, RATE, LAYERS, TOKENS = 2048, 1024, 64, 8, 4, 28, 1
 METRIC = "exl3_k4_moe_layer_decode_hbm_gbs"
+# dram__bytes_read.sum + dram__bytes_write.sum of one layer-kernel launch from the ncu capture summarised under
+# profiles/ (None until a capture of the current kernel exists)
+TRAFFIC_PER_LAUNCH = None
 WORKLOAD = "configs[1]: K4 MoE layer decode, 1 token, 64 experts top-8, hidden 2048, intermediate 1024"
 
 
@@ -202,7 +205,7 @@ def run_ours(args):
         for s in slots[:2]:
             layer_call(s, stream)
     stream.synchronize()
-    kernels_per_step = 4  # gate/up projection, SwiGLU, down projection, combine
+    kernels_per_step = 1  # the whole layer is one persistent kernel
     for s in slots:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(stream):
@@ -232,20 +235,30 @@ def run_ours(args):
             slots[i % len(slots)]["graph"].replay()
     with ClockSampler(local) as clocks:
         seconds = timed(args.steps, lambda i: slots[i % len(slots)]["graph"].replay())
-        # dominant kernel alone: the gate/up projection of the step (16.0 MiB of the 24 MiB packed words)
-        gate = torch.empty((TOPK, INTER), device=dev)
-        up = torch.empty((TOPK, INTER), device=dev)
+        # the layer kernel alone: one launch per step outside any graph, each bracketed by events
         kernel_ms = []
         with torch.cuda.stream(stream):
             for i in range(args.warmup + min(args.steps, 200)):
                 s = slots[i % len(slots)]
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record(stream)
-                k.decode_launch(s["layer"], 0, s["ids"], s["normalized"], gate, up, stream=stream)
-                b.record(stream)
-                kernel_ms.append((a, b))
+                ev_a, ev_b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev_a.record(stream)
+                layer_call(s, stream)
+                ev_b.record(stream)
+                kernel_ms.append((ev_a, ev_b))
         stream.synchronize()
-        kernel_ms = [a.elapsed_time(b) for a, b in kernel_ms[args.warmup:]]
+        kernel_ms = [x.elapsed_time(y) for x, y in kernel_ms[args.warmup:]]
+        # for comparison: the same layer as the reference's call sequence of separate launches (per-part entry points)
+        unfused_graphs = []
+        for s in slots[:min(len(slots), 28)]:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(stream):
+                k.moe_decode_layer_unfused(s["layer"], s["ids"], s["w"], s["normalized"], s["x"], TOKENS, stream=stream)
+                stream.synchronize()
+                with torch.cuda.graph(graph, stream=stream):
+                    k.moe_decode_layer_unfused(s["layer"], s["ids"], s["w"], s["normalized"], s["x"], TOKENS, stream=stream)
+            unfused_graphs.append(graph)
+        unfused_steps = min(args.steps, 280)
+        unfused_seconds = timed(unfused_steps, lambda i: unfused_graphs[i % len(unfused_graphs)].replay())
     clock_info = clocks.summary()
     assert k.bad_flag() == 0, "the sticky error flag was raised during the benchmark"
 
@@ -289,9 +302,8 @@ def run_ours(args):
     total_bytes = bytes_per_step * args.steps * world
     value = total_bytes / seconds / 1e9
     peak, peak_source = peaks()
-    gateup_bytes = TOPK * (2 * HIDDEN * INTER * RATE // 8 + 2 * 2 * (HIDDEN + INTER)) + TOKENS * HIDDEN * 4 + 2 * TOPK * INTER * 4
     kernel_s = statistics.mean(kernel_ms) / 1e3
-    achieved = gateup_bytes / kernel_s / 1e9
+    achieved = bytes_per_step / kernel_s / 1e9
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -300,9 +312,11 @@ def run_ours(args):
                    "l2": f"inputs larger than L2: {layers} layers x 203 MB of expert weights rotate, 126 MB L2",
                    "bytes_per_step": bytes_per_step, "multi_gpu": "independent replicas (decode does not shard)"},
         "frac_of_hbm_peak": value / world / peak,
-        "roofline": {"bound": "hbm", "kernel": "gate/up projection (ProjectionKernel<4,1,pairs>)", "achieved": achieved,
-                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_source,
-                     "bytes_per_launch": gateup_bytes, "us_per_launch": kernel_s * 1e6, "traffic": None},
+        "roofline": {"bound": "hbm", "kernel": "FusedDecodeLayerKernel<4,1> (whole layer, one launch per step)",
+                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_source,
+                     "bytes_per_launch": bytes_per_step, "us_per_launch": kernel_s * 1e6, "traffic": TRAFFIC_PER_LAUNCH},
+        "unfused_call_sequence": {"value": bytes_per_step * unfused_steps / unfused_seconds / 1e9, "unit": "GB/s",
+                                  "ms_per_step": unfused_seconds / unfused_steps * 1e3, "kernels_per_step": 4},
         "e2e": {"value": total_bytes / e2e_seconds / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_seconds / args.steps * 1e3},
         "gpu_launches": kernels_per_step * args.steps,

@@ -138,11 +138,15 @@ PADRA_API int padra_exl3_expert_launch(const padra_matrix *matrices, int layer, 
 
 /* ---- whole expert layer at decode (M = 1..16), one call ------------------------------------------------
  * The call order of the reference's decode layer (src/cuda/inference.cu:2963-2975: gate/up projection,
- * SwiGLU, down projection, combine with residual) behind one entry point.  ids/routing are [tokens][8]
- * (ascending expert id per token, BF16-valued weights), normalized [tokens][hidden] is the post-norm input,
- * x [tokens][hidden] the residual stream updated in place.  workspace must hold
- * padra_exl3_moe_decode_workspace_bytes() bytes and need not be initialised. */
+ * SwiGLU, down projection, combine with residual) as ONE persistent cooperative kernel.  ids/routing are
+ * [tokens][8] (eight distinct experts per token, BF16-valued weights), normalized [tokens][hidden] is the
+ * post-norm input, x [tokens][hidden] the residual stream updated in place.  workspace must hold
+ * padra_exl3_moe_decode_workspace_bytes() bytes; its leading control words must be zero before the first
+ * layer call (padra_exl3_moe_decode_workspace_init, once after allocation) and every layer call leaves them
+ * zero again.  One workspace serves one stream at a time.  The kernel occupies every SM (one CTA each) and
+ * needs the device to be otherwise idle on that stream's turn, like any cooperative launch. */
 PADRA_API size_t padra_exl3_moe_decode_workspace_bytes(int tokens, int hidden, int inter);
+PADRA_API int padra_exl3_moe_decode_workspace_init(void *workspace, size_t workspace_bytes, padra_stream stream);
 PADRA_API int padra_exl3_moe_decode_layer(const padra_matrix *matrices, int layer, const int *ids,
                                           const float *routing, const float *normalized, float *x, int tokens,
                                           int rate, int hidden, int inter, const unsigned short *table,

@@ -10,25 +10,6 @@ cudaStream_t S(padra_stream s) {
 bool RateOk(int rate) {
   return rate == 3 || rate == 4 || rate == 6;
 }
-size_t Align256(size_t n) {
-  return (n + 255) & ~static_cast<size_t>(255);
-}
-// Layout of the decode-layer workspace: three activation planes, then the row-union tables.
-struct DecodeWorkspace {
-  size_t gate, up, down, masks, slots, active, count, total;
-  DecodeWorkspace(int tokens, int hidden, int inter) {
-    const size_t pairs = static_cast<size_t>(tokens) * kTopK;
-    size_t at = 0;
-    gate = at, at += Align256(pairs * inter * sizeof(float));
-    up = at, at += Align256(pairs * inter * sizeof(float));
-    down = at, at += Align256(pairs * hidden * sizeof(float));
-    masks = at, at += Align256(kExperts * sizeof(unsigned));
-    slots = at, at += Align256(static_cast<size_t>(kExperts) * kMaxDecodeRows * sizeof(int));
-    active = at, at += Align256(kExperts * sizeof(int));
-    count = at, at += Align256(sizeof(int));
-    total = at;
-  }
-};
 } // namespace
 
 extern "C" {
@@ -152,9 +133,13 @@ int padra_exl3_expert_launch(const padra_matrix *matrices, int layer, int part, 
 }
 
 size_t padra_exl3_moe_decode_workspace_bytes(int tokens, int hidden, int inter) {
-  if (tokens < 1 || tokens > kMaxDecodeRows || hidden < 128 || inter < 128)
+  if (tokens < 1 || tokens > kMaxDecodeRows || hidden < 128 || inter < 128 || (hidden % 128) || (inter % 128))
     return 0;
-  return DecodeWorkspace(tokens, hidden, inter).total;
+  return FusedDecodeWorkspaceBytes(tokens, hidden, inter);
+}
+
+int padra_exl3_moe_decode_workspace_init(void *workspace, size_t workspace_bytes, padra_stream stream) {
+  return InitFusedDecodeWorkspace(workspace, workspace_bytes, S(stream));
 }
 
 int padra_exl3_moe_decode_layer(const padra_matrix *matrices, int layer, const int *ids, const float *routing,
@@ -164,39 +149,10 @@ int padra_exl3_moe_decode_layer(const padra_matrix *matrices, int layer, const i
   if (!RateOk(rate))
     return PADRA_UNSUPPORTED;
   if (!matrices || !ids || !routing || !normalized || !x || !table || !workspace || !bad || tokens < 1 ||
-      tokens > kMaxDecodeRows || hidden < 128 || inter < 128 || (hidden % 128) || (inter % 128))
+      tokens > kMaxDecodeRows || hidden < 128 || inter < 128 || (hidden % 128) || (inter % 128) || layer < 0)
     return PADRA_INVALID_ARGUMENT;
-  const DecodeWorkspace w(tokens, hidden, inter);
-  if (workspace_bytes < w.total)
-    return PADRA_RESOURCE_EXHAUSTED;
-  auto *base = static_cast<unsigned char *>(workspace);
-  auto *gate = reinterpret_cast<float *>(base + w.gate), *up = reinterpret_cast<float *>(base + w.up),
-       *down = reinterpret_cast<float *>(base + w.down);
-  const int pairs = tokens * kTopK;
-  int status;
-  if (tokens == 1) {
-    status = LaunchPairProjection(matrices, layer, 0, ids, normalized, gate, up, pairs, bad, S(stream), rate, hidden, inter);
-    if (status == PADRA_OK)
-      status = LaunchSiluActivate(gate, up, table, pairs * inter, bad, S(stream));
-    if (status == PADRA_OK)
-      status = LaunchPairProjection(matrices, layer, 2, ids, gate, down, nullptr, pairs, bad, S(stream), rate, hidden, inter);
-  } else {
-    auto *masks = reinterpret_cast<unsigned *>(base + w.masks);
-    auto *slots = reinterpret_cast<int *>(base + w.slots), *active = reinterpret_cast<int *>(base + w.active),
-         *count = reinterpret_cast<int *>(base + w.count);
-    status = LaunchBuildUnion(ids, masks, slots, tokens, kMaxDecodeRows, bad, active, count, S(stream));
-    if (status == PADRA_OK)
-      status = LaunchUnionProjection(matrices, layer, 0, masks, slots, kMaxDecodeRows, tokens, normalized, gate, up, bad,
-                                     S(stream), active, count, rate, hidden, inter);
-    if (status == PADRA_OK)
-      status = LaunchSiluActivate(gate, up, table, pairs * inter, bad, S(stream));
-    if (status == PADRA_OK)
-      status = LaunchUnionProjection(matrices, layer, 2, masks, slots, kMaxDecodeRows, tokens, gate, down, nullptr, bad,
-                                     S(stream), active, count, rate, hidden, inter);
-  }
-  if (status == PADRA_OK)
-    status = LaunchCombine(x, down, routing, bad, tokens, hidden, S(stream));
-  return status;
+  return LaunchFusedDecodeLayer(matrices, layer, ids, routing, normalized, x, tokens, rate, hidden, inter, table, workspace,
+                                workspace_bytes, bad, S(stream));
 }
 
 int padra_exl3_decode_weights(const padra_matrix *matrix, unsigned short *out, int rows, int cols, int rate, int *bad,

@@ -23,6 +23,11 @@ int LaunchCombinePacked(float *x, const unsigned short *down, const float *weigh
 int LaunchDecodeWeights(const Matrix *matrix, unsigned short *out, int rows, int cols, int rate, int *bad,
                         cudaStream_t stream);
 
+size_t FusedDecodeWorkspaceBytes(int tokens, int hidden, int inter);
+int InitFusedDecodeWorkspace(void *workspace, size_t bytes, cudaStream_t stream);
+int LaunchFusedDecodeLayer(const Matrix *matrices, int layer, const int *ids, const float *routing, const float *normalized,
+                           float *x, int tokens, int rate, int hidden, int inter, const unsigned short *table,
+                           void *workspace, size_t workspace_bytes, int *bad, cudaStream_t stream);
 int LaunchTileProjection(const Matrix *matrices, int layer, int part, const int *groups, const padra_tile *tiles,
                          const int *tile_count, const float *input, unsigned short *output,
                          const unsigned short *gate, const unsigned short *up, const unsigned short *table, int tokens,

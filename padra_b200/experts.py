@@ -252,8 +252,31 @@ class ExpertKernels:
         key = ("decode", tokens)
         if key not in self._workspace:
             n = self.lib.padra_exl3_moe_decode_workspace_bytes(tokens, *self.dims)
-            self._workspace[key] = torch.empty(n, dtype=torch.uint8, device=self.t.device)
+            ws = torch.empty(n, dtype=torch.uint8, device=self.t.device)
+            B.check(self.lib.padra_exl3_moe_decode_workspace_init(B.ptr(ws), n, B.stream_handle()),
+                    "padra_exl3_moe_decode_workspace_init")
+            self._workspace[key] = ws
         return self._workspace[key]
+
+    def moe_decode_layer_unfused(self, layer, ids, routing, normalized, x, tokens, stream=None):
+        """The same layer as separate launches through the per-part entry points (the reference's own call
+        sequence: src/cuda/inference.cu:2963-2975 for one row, :3375-3392 for several)."""
+        dev, (hidden, inter) = self.t.device, self.dims
+        key = ("unfused", tokens)
+        if key not in self._workspace:
+            self._workspace[key] = (torch.empty((tokens * TOPK, inter), device=dev), torch.empty((tokens * TOPK, inter), device=dev),
+                                    torch.empty((tokens * TOPK, hidden), device=dev))
+        gate, up, down = self._workspace[key]
+        if tokens == 1:
+            self.decode_launch(layer, 0, ids, normalized, gate, up, stream)
+            self.silu_activate(gate, up, stream)
+            self.decode_launch(layer, 2, ids, gate, down, None, stream)
+        else:
+            union = self.build_union(ids, tokens, stream=stream)
+            self.mtp_launch(layer, 0, union, tokens, normalized, gate, up, stream=stream)
+            self.silu_activate(gate, up, stream)
+            self.mtp_launch(layer, 2, union, tokens, gate, down, stream=stream)
+        self.combine(x, down, routing, tokens, stream)
 
     def moe_decode_layer(self, layer, ids, routing, normalized, x, tokens, stream=None):
         ws = self.decode_workspace(tokens)

@@ -9,8 +9,12 @@ import numpy as np
 # elements that nearly cancel are excused.  For CHAINED results (a down projection fed by its own gate/up, a
 # whole layer) every stage ends in a BF16 rounding whose step is 2^-8 of the value's own magnitude, so an element
 # that nearly cancels carries an absolute error of about one BF16 step of a typical element; there the floor is
-# the row's rms.
+# the row's rms and the bound 3e-2: the reference's own two arithmetic forms (the compensated scalar path and the
+# FP16-input / FP32-sequential tensor-core form, both restated by the oracle) differ element-wise by up to 1.9e-2
+# on such chained results while agreeing within 7e-3 in the row-norm sense, so that is the noise floor of the
+# comparison, not an error of either side.
 REL_TOL = 1e-2
+CHAINED_ELEMENT_TOL = 3e-2
 
 
 def assert_close_rows(actual: np.ndarray, ref: np.ndarray, what: str, tol: float = REL_TOL, chained: bool = False):
@@ -27,7 +31,8 @@ def assert_close_rows(actual: np.ndarray, ref: np.ndarray, what: str, tol: float
     rms = np.sqrt((r2 ** 2).mean(axis=1, keepdims=True))
     floor = np.maximum(np.abs(r2), rms if chained else rms / 64)
     elementwise = (np.abs(a2 - r2) / np.maximum(floor, 1e-30)).max()
-    assert elementwise <= tol, f"{what}: element-wise relative error {elementwise:.3e} > {tol}"
+    bound = max(tol, CHAINED_ELEMENT_TOL) if chained else tol
+    assert elementwise <= bound, f"{what}: element-wise relative error {elementwise:.3e} > {bound}"
     return worst
 
 

@@ -100,6 +100,69 @@ def test_multi_token_layer(oracle, gpu, rate, tokens):
     assert k.bad_flag() == 0
 
 
+@pytest.mark.parametrize("rate", RATES)
+@pytest.mark.parametrize("tokens", [1, 3, 8, 13])
+def test_fused_layer_matches_separate_launches(oracle, gpu, rate, tokens):
+    """The persistent layer kernel against the per-part entry points launched one after another."""
+    hidden, inter = 512, 384
+    host, table, k = make(1, hidden, inter, rate, 97, gpu)
+    x, ids, w = routed_inputs(oracle, tokens, hidden, 40 + tokens)
+    dids = torch.from_numpy(ids.reshape(-1)).to(gpu)
+    dw = torch.from_numpy(w.reshape(-1)).to(gpu)
+    dx = torch.from_numpy(x).to(gpu)
+    fused, separate = dx.clone(), dx.clone()
+    k.moe_decode_layer(0, dids, dw, dx, fused, tokens)
+    k.moe_decode_layer_unfused(0, dids, dw, dx, separate, tokens)
+    assert_close_rows(fused.cpu().numpy(), separate.cpu().numpy(), "fused vs separate launches", chained=True)
+    again = dx.clone()
+    k.moe_decode_layer(0, dids, dw, dx, again, tokens)  # control words were left clean: a second call works
+    assert torch.equal(again, fused)
+    assert k.bad_flag() == 0
+
+
+def test_fused_layer_mellum_dims(oracle, gpu):
+    """Hidden 2304 / intermediate 896 (18 and 7 blocks of 128): non-power-of-two chunk bookkeeping."""
+    from padra_b200.experts import ExpertKernels, ExpertTable
+
+    hidden, inter = 2304, 896
+    table = ExpertTable(1, hidden, inter, 4, gpu).fill_random(9)
+    k = ExpertKernels(table)
+    x, ids, w = routed_inputs(oracle, 5, hidden, 50)
+    dids = torch.from_numpy(ids.reshape(-1)).to(gpu)
+    dw = torch.from_numpy(w.reshape(-1)).to(gpu)
+    dx = torch.from_numpy(x).to(gpu)
+    fused, separate = dx.clone(), dx.clone()
+    k.moe_decode_layer(0, dids, dw, dx, fused, 5)
+    k.moe_decode_layer_unfused(0, dids, dw, dx, separate, 5)
+    assert_close_rows(fused.cpu().numpy(), separate.cpu().numpy(), "fused vs separate launches, 2304/896", chained=True)
+    assert k.bad_flag() == 0
+
+
+def test_fused_layer_rejects_bad_ids_and_descriptors(gpu):
+    _, table, k = make(1, 256, 128, 4, 101, gpu)
+    x = torch.ones((1, 256), device=gpu)
+    w = torch.full((8,), 0.125, device=gpu)
+    out = x.clone()
+    k.moe_decode_layer(0, torch.tensor([0, 1, 2, 64, 4, 5, 6, 7], dtype=torch.int32, device=gpu), w, x, out, 1)
+    torch.cuda.synchronize()
+    assert k.bad_flag() == 1 and torch.equal(out, x)  # refused before any work
+    k.reset_bad()
+    # a table of another rate: every chunk's descriptor check fails, the step completes and is flagged
+    from padra_b200 import binding as B
+    ws = k.decode_workspace(1)
+    st = k.lib.padra_exl3_moe_decode_layer(table.descriptors.data_ptr(), 0, B.ptr(torch.arange(8, dtype=torch.int32, device=gpu)),
+                                           B.ptr(w), B.ptr(x), B.ptr(out), 1, 6, 256, 128, B.ptr(k.table), B.ptr(ws), ws.numel(),
+                                           B.ptr(k.bad), B.stream_handle())
+    assert st == 0
+    torch.cuda.synchronize()
+    assert k.bad_flag() == 1
+    k.reset_bad()
+    good = x.clone()
+    k.moe_decode_layer(0, torch.arange(8, dtype=torch.int32, device=gpu), w, x, good, 1)  # and the workspace is reusable
+    torch.cuda.synchronize()
+    assert k.bad_flag() == 0 and not torch.equal(good, x)
+
+
 def test_config1_layer_k4(oracle, gpu):
     """The benchmark's decode configuration: 64 experts, hidden 2048, intermediate 1024, one token."""
     hidden, inter = 2048, 1024
