@@ -147,6 +147,11 @@ PADRA_API int padra_exl3_expert_launch(const padra_matrix *matrices, int layer, 
  * needs the device to be otherwise idle on that stream's turn, like any cooperative launch. */
 PADRA_API size_t padra_exl3_moe_decode_workspace_bytes(int tokens, int hidden, int inter);
 PADRA_API int padra_exl3_moe_decode_workspace_init(void *workspace, size_t workspace_bytes, padra_stream stream);
+/* Diagnostic timeline of the layer kernel, off by default (the reference's counterpart is its capture_trace
+ * option, src/cuda/inference.cu:608-624).  buffer: device memory of 64 * 8 bytes per SM, or NULL to switch the
+ * trace off.  While set, every layer call makes each CTA record %globaltimer at fixed points (start, set-up
+ * done, streaming done, counting done, end, and per chunk); a host-side setting, not stream-ordered. */
+PADRA_API int padra_exl3_moe_decode_set_trace(void *buffer, size_t bytes);
 PADRA_API int padra_exl3_moe_decode_layer(const padra_matrix *matrices, int layer, const int *ids,
                                           const float *routing, const float *normalized, float *x, int tokens,
                                           int rate, int hidden, int inter, const unsigned short *table,

@@ -142,6 +142,10 @@ int padra_exl3_moe_decode_workspace_init(void *workspace, size_t workspace_bytes
   return InitFusedDecodeWorkspace(workspace, workspace_bytes, S(stream));
 }
 
+int padra_exl3_moe_decode_set_trace(void *buffer, size_t bytes) {
+  return SetFusedDecodeTrace(buffer, bytes);
+}
+
 int padra_exl3_moe_decode_layer(const padra_matrix *matrices, int layer, const int *ids, const float *routing,
                                 const float *normalized, float *x, int tokens, int rate, int hidden, int inter,
                                 const unsigned short *table, void *workspace, size_t workspace_bytes, int *bad,

@@ -8,7 +8,7 @@
 // reduction, output Hadamard, SwiGLU, the down projection's input transform, combine) are done by whichever CTA
 // delivers the last chunk of a unit, off the streaming warps' critical path.
 //
-// Roles inside a CTA (18 warps):
+// Roles inside a CTA (19 warps):
 //   * two streaming groups of 8 warps.  A group owns every (2*gridDim)-th chunk; warp w of the group owns tile
 //     column w of the chunk (16 outputs) and both of its K-rounds.  Packed words are register-prefetched two
 //     chunks ahead, decoded in registers (codec.cuh) and multiplied with mma.m16n8k16 against the chunk's
@@ -16,9 +16,10 @@
 //     stages its own activation tiles one chunk ahead, the rows dealt round-robin over its warps: the input
 //     Hadamard of x * suh for a gate/up chunk, a copy of the published SwiGLU output for a down chunk.
 //   * one counting warp per group.  It learns from a shared-memory counter that the group has stored the partial
-//     sums of one or more chunks, counts them against their units in the workspace (one lane per chunk, so the
-//     round trips of a batch overlap), and runs a unit's epilogue when its count completes.  It never waits on
-//     anything but that counter.
+//     sums of one or more chunks and counts them against their units in the workspace (one lane per chunk, so
+//     the round trips of a batch overlap).  A chunk that completes its unit is queued for the epilogue warp.
+//   * one epilogue warp.  It takes completed units from the queue and runs their epilogue, so that counting is
+//     never held up behind an epilogue.  Counting and epilogue warps wait on shared memory of their own CTA only.
 //
 // Determinism: chunk -> CTA assignment and every summation order are fixed by the shapes alone, so results are
 // bit-identical run to run and under CUDA-graph replay.
@@ -40,13 +41,17 @@ constexpr int kGroups = 2;
 constexpr int kGroupWarps = 8;
 constexpr int kStreamWarps = kGroups * kGroupWarps;
 constexpr int kCountWarps = 1;                                    // per group
-constexpr int kWarps = kStreamWarps + kGroups * kCountWarps;      // 18
-constexpr int kFusedThreads = kWarps * 32;                        // 576
+constexpr int kFinishWarp = kStreamWarps + kGroups * kCountWarps; // index of the CTA's epilogue warp
+constexpr int kWarps = kFinishWarp + 1;                           // 19
+constexpr int kFusedThreads = kWarps * 32;                        // 608
+constexpr int kQueue = 16;                                        // completed units waiting for their epilogue
+constexpr unsigned kEmpty = 0xffffffffu;
 constexpr int kTileBuffers = 3;
 constexpr int kXsStride = 128 + 8; // halves per staged activation row (+16 B against bank conflicts)
 constexpr int kGroupThreads = kGroupWarps * 32;
 constexpr int kMaxBlocks = 64; // 128-wide blocks per dimension the control words provide for
 constexpr unsigned kPollLimit = 1u << 20;
+constexpr int kChunkTable = 64; // chunks per group described up front; later ones are described on the fly
 
 // Control words at the start of the workspace.  All zero between launches: the last CTA to finish clears them.
 struct Control {
@@ -71,7 +76,21 @@ struct FusedArgs {
   __half *xdown;   // [pairs][inter], permuted K16 order
   float *partials; // gate/up partial sums, then down partial sums
   int *bad;
+  unsigned long long *trace; // optional timeline, kTraceSlots words per CTA (nullptr: off)
 };
+
+constexpr int kTraceSlots = 64;
+__device__ __forceinline__ unsigned long long GlobalTimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Timeline slots per CTA: 0 start, 1 set-up done, 2 group-0 streaming done, 3 group-0 counting done, 4 end,
+// 8.. time after the tile barrier of each chunk of group 0 (warp 0), 36.. time of each counting batch of group 0.
+__device__ __forceinline__ void Trace(const FusedArgs &a, int slot) {
+  if (a.trace && slot < kTraceSlots)
+    a.trace[static_cast<size_t>(blockIdx.x) * kTraceSlots + slot] = GlobalTimer();
+}
 
 __device__ __forceinline__ void GroupBarrier(int group) {
   asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(kGroupThreads) : "memory");
@@ -201,16 +220,24 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
   __shared__ int s_active_count, s_invalid, s_last;
   __shared__ unsigned s_warp_votes[2];
   __shared__ unsigned s_stored[kGroups]; // warp-chunks whose partial sums are stored, per group
+  __shared__ unsigned s_chunks[kGroups][kChunkTable]; // this CTA's chunks, described once (PackChunk)
+  __shared__ unsigned s_queue[kQueue];                // completed units (PackChunk of the completing chunk) or kEmpty
+  __shared__ unsigned s_queue_tail, s_counting_done;
   __shared__ __align__(16) __half s_xs[kGroups][kTileBuffers][kRows * kXsStride];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   Control *ctl = a.control;
+  if (tid == 0)
+    Trace(a, 0);
 
   // ---- which rows use which expert (every CTA builds the same tables) -----------------------------------
   if (tid == 0) {
     s_invalid = 0;
     s_stored[0] = s_stored[1] = 0;
+    s_queue_tail = s_counting_done = 0;
   }
+  if (tid < kQueue)
+    s_queue[tid] = kEmpty;
   __syncthreads();
   if (tid < kExperts) {
     const int expert = tid;
@@ -283,9 +310,25 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
   }
   __syncthreads();
 
-  const int group = warp < kStreamWarps ? warp / kGroupWarps : (warp - kStreamWarps) / kCountWarps;
+  const int group = warp < kStreamWarps ? warp / kGroupWarps : (warp < kFinishWarp ? (warp - kStreamWarps) / kCountWarps : 0);
   const int first = blockIdx.x * kGroups + group, stride = gridDim.x * kGroups;
   const int mine = first < geo.chunks_total ? (geo.chunks_total - first + stride - 1) / stride : 0;
+  // the chunk list of both groups, described once instead of once per warp and use
+  for (int i = tid; i < kGroups * kChunkTable; i += kFusedThreads) {
+    const int grp = i / kChunkTable, j = i - grp * kChunkTable;
+    const int idx = blockIdx.x * kGroups + grp + j * stride;
+    if (idx < geo.chunks_total)
+      s_chunks[grp][j] = PackChunk(Describe<NG>(idx, geo, tab));
+  }
+  __syncthreads();
+  if (tid == 0)
+    Trace(a, 1);
+  auto j_packed = [&](int j) {
+    return j < kChunkTable ? s_chunks[group][j] : PackChunk(Describe<NG>(first + j * stride, geo, tab));
+  };
+  auto chunk_at = [&](int j) {
+    return j < kChunkTable ? UnpackChunk(s_chunks[group][j]) : Describe<NG>(first + j * stride, geo, tab);
+  };
   const int my_gateup = first < geo.chunks_gateup ? (geo.chunks_gateup - first + stride - 1) / stride : 0;
   // Permuted K16 position of this lane's four consecutive inputs inside a 128-input block.
   const int permuted = (lane >> 2) * 16 + 8 * (lane & 1) + 2 * ((lane >> 1) & 1);
@@ -294,11 +337,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
     // =============================== streaming warps ===============================
     const int col = warp % kGroupWarps, g = lane >> 2, t = lane & 3;
 
-    auto fetch = [&](int j, uint32_t (&w)[2][Rate], unsigned &packed) {
-      if (j >= mine)
-        return;
-      const Chunk c = Describe<NG>(first + j * stride, geo, tab);
-      packed = PackChunk(c);
+    // Packed words of chunk `c` for this lane: two rounds of four K16 steps.
+    auto fetch = [&](const Chunk &c, uint32_t (&w)[2][Rate]) {
       const unsigned char *data = tab.data[c.expert][c.part];
       const size_t tiles_per_kstep = (c.part == 2 ? a.hidden : a.inter) / 16;
 #pragma unroll
@@ -326,11 +366,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
       const int unit_last = c.order * geo.per_expert_gateup + (c.kc + 1) * 2 * geo.blocks_hidden - 1;
       return unit_last < geo.chunks_gateup - 2 * stride;
     };
-    auto tile_load = [&](int j, TileRegs<NG> &regs, bool synchronous) {
+    auto tile_load = [&](int j, const Chunk &c, TileRegs<NG> &regs, bool synchronous) {
       regs.state = 0;
-      if (j >= mine)
-        return;
-      const Chunk c = Describe<NG>(first + j * stride, geo, tab);
       const int n0 = (col - j % kGroupWarps + kGroupWarps) % kGroupWarps; // rows n0, n0+8 are this warp's
       if (n0 >= c.count)
         return;
@@ -344,8 +381,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
           }
         regs.state = 1;
       } else {
-        if (!synchronous && !poll_is_safe(c))
-          return; // loaded later, once this group holds no gate/up work
+        if (!synchronous && !poll_is_safe(c)) {
+          regs.state = 3; // to be fetched later, once this group holds no gate/up work
+          return;
+        }
         poll_ready(c);
 #pragma unroll
         for (int u = 0; u < NG; ++u)
@@ -358,10 +397,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
         regs.state = 2;
       }
     };
-    auto tile_store = [&](int j, const TileRegs<NG> &regs) {
-      if (regs.state == 0)
-        return;
-      const Chunk c = Describe<NG>(first + j * stride, geo, tab);
+    auto tile_store = [&](int j, const Chunk &c, const TileRegs<NG> &regs) {
       const int n0 = (col - j % kGroupWarps + kGroupWarps) % kGroupWarps;
       __half *xs = s_xs[group][j % kTileBuffers];
       if (regs.state == 1) {
@@ -386,7 +422,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
             *reinterpret_cast<__half2 *>(dst) = __halves2half2(hv[0], hv[1]);
             *reinterpret_cast<__half2 *>(dst + 4) = __halves2half2(hv[2], hv[3]);
           }
-      } else {
+      } else if (regs.state == 2) {
 #pragma unroll
         for (int u = 0; u < NG; ++u)
           if (n0 + 8 * u < c.count)
@@ -395,7 +431,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
       }
     };
 
-    auto stream = [&](int j, uint32_t (&slot)[2][Rate], unsigned &slot_chunk, TileRegs<NG> &next_tile, TileRegs<NG> &later_tile) {
+    // One chunk.  `slot`/`slot_chunk` hold chunk j on entry and chunk j+2 on exit; `other_chunk` is chunk j+1;
+    // `next_tile` holds this warp's rows of tile j+1 (loaded one chunk ago), `later_tile` receives tile j+2.
+    auto stream = [&](int j, uint32_t (&slot)[2][Rate], unsigned &slot_chunk, unsigned other_chunk, TileRegs<NG> &next_tile,
+                      TileRegs<NG> &later_tile) {
       const Chunk c = UnpackChunk(slot_chunk);
       uint32_t words[2][Rate];
 #pragma unroll
@@ -403,9 +442,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
 #pragma unroll
         for (int i = 0; i < Rate; ++i)
           words[r][i] = slot[r][i];
-      fetch(j + 2, slot, slot_chunk);
-      const bool staged_early = next_tile.state != 0;
-      tile_store(j + 1, next_tile); // buffer (j+1)%3 was last read by chunk j-2, which every warp has left
+      later_tile.state = 0;
+      if (j + 2 < mine) {
+        const Chunk ahead = chunk_at(j + 2);
+        slot_chunk = PackChunk(ahead);
+        fetch(ahead, slot);
+        tile_load(j + 2, ahead, later_tile, /*synchronous=*/false);
+      }
       // round 0 is decoded before the barrier (it needs no activations), round 1 after its MMAs were issued
       uint32_t frag[4][4];
       {
@@ -413,6 +456,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
         codec::Decode32<Rate>(words[0], previous, frag);
       }
       GroupBarrier(group); // tile j is complete in shared memory
+      if (warp == 0 && lane == 0 && j < 12)
+        Trace(a, 8 + j);
       const __half *xs = s_xs[group][j % kTileBuffers];
       float acc[NG][4];
       const __half *xrow[NG];
@@ -455,37 +500,95 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
       __syncwarp();
       if (lane == 0)
         atomicAdd(&s_stored[group], 1u); // this warp's share of chunk j is in the workspace
-      // A down tile whose unit was not safe to poll ahead of time is fetched now: the group has stored all of its
-      // gate/up chunks by the time this one's successor is a down chunk.
-      if (!staged_early && j + 1 < mine) {
-        TileRegs<NG> now;
-        tile_load(j + 1, now, /*synchronous=*/true);
-        tile_store(j + 1, now);
+      // Tile j+1 goes to buffer (j+1)%3, last read by chunk j-2, which every warp of the group has left.  Its
+      // inputs were loaded a whole chunk ago -- except for a down tile whose unit was not safe to poll ahead of
+      // time: that one is fetched now, when the group has stored every gate/up chunk it owns.
+      if (j + 1 < mine) {
+        const Chunk next = UnpackChunk(other_chunk);
+        if (next_tile.state == 3)
+          tile_load(j + 1, next, next_tile, /*synchronous=*/true);
+        tile_store(j + 1, next, next_tile);
       }
-      tile_load(j + 2, later_tile, /*synchronous=*/false);
     };
 
     uint32_t slot0[2][Rate], slot1[2][Rate];
     unsigned chunk0 = 0, chunk1 = 0;
     TileRegs<NG> tile0, tile1;
-    fetch(0, slot0, chunk0);
-    fetch(1, slot1, chunk1);
-    tile_load(0, tile0, /*synchronous=*/true); // nothing of this group is pending yet
-    tile_store(0, tile0);
-    tile_load(1, tile1, /*synchronous=*/my_gateup == 0);
-    tile0.state = 0;
-    for (int j = 0; j < mine; j += 2) {
-      // stream(j) stores tile j+1 from the registers loaded one chunk earlier and loads tile j+2
-      stream(j, slot0, chunk0, tile1, tile0);
-      if (j + 1 < mine)
-        stream(j + 1, slot1, chunk1, tile0, tile1);
+    tile0.state = tile1.state = 0;
+    if (mine > 0) {
+      const Chunk c0 = chunk_at(0);
+      chunk0 = PackChunk(c0);
+      fetch(c0, slot0);
+      tile_load(0, c0, tile0, /*synchronous=*/true); // nothing of this group is pending yet
+      tile_store(0, c0, tile0);
     }
-  } else {
+    if (mine > 1) {
+      const Chunk c1 = chunk_at(1);
+      chunk1 = PackChunk(c1);
+      fetch(c1, slot1);
+      tile_load(1, c1, tile1, /*synchronous=*/my_gateup == 0);
+    }
+    for (int j = 0; j < mine; j += 2) {
+      stream(j, slot0, chunk0, chunk1, tile1, tile0);
+      if (j + 1 < mine)
+        stream(j + 1, slot1, chunk1, chunk0, tile0, tile1);
+    }
+    if (warp == 0 && lane == 0)
+      Trace(a, 2);
+  } else if (warp < kFinishWarp) {
     // =============================== counting warps ===============================
+    int counted = 0; // chunks of this group already counted against their units
+    while (counted < mine) {
+      // wait (within this CTA only) until all eight warps of the group have stored at least one more chunk
+      unsigned stored = 0, polls = 0;
+      while ((stored = *reinterpret_cast<volatile unsigned *>(&s_stored[group]) / kGroupWarps) <= static_cast<unsigned>(counted)) {
+        if (++polls > 16 * kPollLimit) {
+          atomicOr(&ctl->error, 4u);
+          stored = mine; // count the rest regardless; the step is rejected
+          break;
+        }
+        __nanosleep(40);
+      }
+      const int batch = min(static_cast<int>(stored) - counted, 32);
+      // one lane per chunk of the batch: release the group's stores, count the chunk, queue a completed unit
+      if (lane < batch) {
+        const unsigned packed = j_packed(counted + lane);
+        const Chunk c = UnpackChunk(packed);
+        unsigned *counter = c.part < 2 ? &ctl->unit_gateup[c.expert * kMaxBlocks + c.nb] : &ctl->unit_down[c.nb];
+        const unsigned needed = c.part < 2 ? 2u * geo.blocks_hidden : static_cast<unsigned>(geo.active) * geo.blocks_inter;
+        __threadfence();
+        if (atomicAdd(counter, 1u) == needed - 1) {
+          __threadfence();
+          const unsigned slot = atomicAdd(&s_queue_tail, 1u) % kQueue;
+          unsigned waits = 0;
+          while (*reinterpret_cast<volatile unsigned *>(&s_queue[slot]) != kEmpty) { // the epilogue warp is behind
+            if (++waits > kPollLimit) {
+              atomicOr(&ctl->error, 8u);
+              break;
+            }
+            __nanosleep(100);
+          }
+          *reinterpret_cast<volatile unsigned *>(&s_queue[slot]) = packed;
+        }
+      }
+      __syncwarp();
+      counted += batch;
+      if (group == 0 && lane == 0)
+        Trace(a, 36 + (counted < 28 ? counted : 27));
+    }
+    __threadfence_block();
+    __syncwarp();
+    if (lane == 0)
+      atomicAdd(&s_counting_done, 1u);
+    if (group == 0 && lane == 0)
+      Trace(a, 3);
+  } else {
+    // =============================== epilogue warp ===============================
     auto note_nonfinite = [&](float v) {
       if (!isfinite(v))
         atomicOr(&ctl->error, 1u);
     };
+    int trace_unit = 0;
 
     // gate/up epilogue for (expert, block nb): split-K sums -> output Hadamard, svh -> SwiGLU -> the down
     // projection's input transform (x suh, Hadamard, BF16, FP16), published for the down chunks.
@@ -501,21 +604,23 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
         float gsum[4] = {0.f, 0.f, 0.f, 0.f}, usum[4] = {0.f, 0.f, 0.f, 0.f};
         const float *pg = a.partials + PartialOffset(0, c.nb, 0, pair, geo) + lane * 4;
         const float *pu = a.partials + PartialOffset(1, c.nb, 0, pair, geo) + lane * 4;
-        for (int kc0 = 0; kc0 < geo.blocks_hidden; kc0 += 4) { // ascending K, four blocks of loads in flight
-          float4 vg[4], vu[4];
+        for (int kc0 = 0; kc0 < geo.blocks_hidden; kc0 += 8) { // ascending K, sixteen loads in flight
+          float4 vg[8], vu[8];
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
+          for (int u = 0; u < 8; ++u)
             if (kc0 + u < geo.blocks_hidden) {
               vg[u] = LoadL2(pg + (kc0 + u) * 128);
               vu[u] = LoadL2(pu + (kc0 + u) * 128);
             }
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
+          for (int u = 0; u < 8; ++u)
             if (kc0 + u < geo.blocks_hidden) {
               gsum[0] += vg[u].x, gsum[1] += vg[u].y, gsum[2] += vg[u].z, gsum[3] += vg[u].w;
               usum[0] += vu[u].x, usum[1] += vu[u].y, usum[2] += vu[u].z, usum[3] += vu[u].w;
             }
         }
+        if (lane == 0 && n == 0)
+          Trace(a, 20 + 3 * trace_unit + 1);
         WarpHadamard128(gsum);
         WarpHadamard128(usum);
         float v[4];
@@ -525,7 +630,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
           const float up = RoundBF16(__fmul_rn(usum[i], svu[i]));
           note_nonfinite(gate);
           note_nonfinite(up);
-          const float silu = FromBF16Bits(a.table[__float_as_uint(gate) >> 16]);
+          const float silu = FromBF16Bits(__ldg(a.table + (__float_as_uint(gate) >> 16)));
           const float act = RoundBF16(__fmul_rn(silu, up));
           note_nonfinite(act);
           v[i] = __fmul_rn(act, shd[i]);
@@ -563,14 +668,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
           Unpack4(__ldg(reinterpret_cast<const uint2 *>(tab.svh[expert][2] + out)), sc);
           const float *pd = a.partials + PartialOffset(2, nb, 0, pair, geo) + lane * 4;
           float d[4] = {0.f, 0.f, 0.f, 0.f};
-          for (int kc0 = 0; kc0 < geo.blocks_inter; kc0 += 4) {
-            float4 vd[4];
+          for (int kc0 = 0; kc0 < geo.blocks_inter; kc0 += 8) {
+            float4 vd[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < 8; ++u)
               if (kc0 + u < geo.blocks_inter)
                 vd[u] = LoadL2(pd + (kc0 + u) * 128);
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < 8; ++u)
               if (kc0 + u < geo.blocks_inter)
                 d[0] += vd[u].x, d[1] += vd[u].y, d[2] += vd[u].z, d[3] += vd[u].w;
           }
@@ -593,41 +698,37 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
       }
     };
 
-    int counted = 0; // chunks of this group already counted against their units
-    while (counted < mine) {
-      // wait (within this CTA only) until all eight warps of the group have stored at least one more chunk
-      unsigned stored = 0, polls = 0;
-      while ((stored = *reinterpret_cast<volatile unsigned *>(&s_stored[group]) / kGroupWarps) <= static_cast<unsigned>(counted)) {
-        if (++polls > 16 * kPollLimit) {
-          atomicOr(&ctl->error, 4u);
-          stored = mine; // count the rest regardless; the step is rejected
-          break;
-        }
-        __nanosleep(40);
-      }
-      const int batch = min(static_cast<int>(stored) - counted, 32);
-      // one lane per chunk of the batch: release the group's stores, then count the chunk
-      bool completes = false;
-      if (lane < batch) {
-        const Chunk c = Describe<NG>(first + (counted + lane) * stride, geo, tab);
-        unsigned *counter = c.part < 2 ? &ctl->unit_gateup[c.expert * kMaxBlocks + c.nb] : &ctl->unit_down[c.nb];
-        const unsigned needed = c.part < 2 ? 2u * geo.blocks_hidden : static_cast<unsigned>(geo.active) * geo.blocks_inter;
-        __threadfence();
-        completes = atomicAdd(counter, 1u) == needed - 1;
-      }
-      __syncwarp();
-      unsigned finishing = __ballot_sync(0xffffffffu, completes);
-      __threadfence();
-      while (finishing) { // the whole warp runs the epilogue of every unit a chunk of this batch completed
-        const int which = __ffs(finishing) - 1;
-        finishing &= finishing - 1;
-        const Chunk c = Describe<NG>(first + (counted + which) * stride, geo, tab);
+    unsigned head = 0, idle = 0;
+    for (;;) {
+      trace_unit = head < 5 ? head : 4;
+      const unsigned done = *reinterpret_cast<volatile unsigned *>(&s_counting_done); // read before the queue slot
+      const unsigned entry = *reinterpret_cast<volatile unsigned *>(&s_queue[head % kQueue]);
+      if (entry != kEmpty) {
+        if (lane == 0)
+          Trace(a, 20 + 3 * trace_unit);
+        __threadfence(); // the counting lane saw the unit complete; order this warp's loads after that
+        const Chunk c = UnpackChunk(entry);
         if (c.part < 2)
           finalize_gateup(c);
         else
           finalize_down(c.nb);
+        __syncwarp();
+        if (lane == 0)
+          Trace(a, 20 + 3 * trace_unit + 2);
+        if (lane == 0)
+          *reinterpret_cast<volatile unsigned *>(&s_queue[head % kQueue]) = kEmpty;
+        __syncwarp();
+        ++head;
+        idle = 0;
+      } else if (done == static_cast<unsigned>(kGroups * kCountWarps)) {
+        break; // both counting warps have finished and queued everything they completed
+      } else {
+        if (++idle > 64 * kPollLimit) {
+          atomicOr(&ctl->error, 16u);
+          break;
+        }
+        __nanosleep(100);
       }
-      counted += batch;
     }
   }
 
@@ -647,6 +748,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
     for (int i = tid; i < static_cast<int>(sizeof(Control) / sizeof(unsigned)); i += kFusedThreads)
       words[i] = 0u;
   }
+  if (tid == 0)
+    Trace(a, 4);
 }
 
 struct FusedWorkspace {
@@ -663,6 +766,8 @@ struct FusedWorkspace {
     total = at;
   }
 };
+
+unsigned long long *g_trace = nullptr; // set by SetFusedDecodeTrace; host-side only
 
 int SmCount() {
   static int cached = 0;
@@ -685,6 +790,14 @@ template <int Rate, int NG> int LaunchFused(FusedArgs &args, cudaStream_t stream
 }
 
 } // namespace
+
+int SetFusedDecodeTrace(void *buffer, size_t bytes) {
+  const int sms = SmCount();
+  if (buffer && (sms < 1 || bytes < static_cast<size_t>(sms) * kTraceSlots * sizeof(unsigned long long)))
+    return PADRA_INVALID_ARGUMENT;
+  g_trace = static_cast<unsigned long long *>(buffer);
+  return PADRA_OK;
+}
 
 size_t FusedDecodeWorkspaceBytes(int tokens, int hidden, int inter) {
   return FusedWorkspace(tokens, hidden, inter).total;
@@ -712,6 +825,7 @@ int LaunchFusedDecodeLayer(const Matrix *matrices, int layer, const int *ids, co
   args.xdown = reinterpret_cast<__half *>(base + w.xdown);
   args.partials = reinterpret_cast<float *>(base + w.partials);
   args.bad = bad;
+  args.trace = g_trace;
   const bool wide = tokens > 8;
   switch (rate) {
   case 3:

@@ -23,6 +23,7 @@ int LaunchCombinePacked(float *x, const unsigned short *down, const float *weigh
 int LaunchDecodeWeights(const Matrix *matrix, unsigned short *out, int rows, int cols, int rate, int *bad,
                         cudaStream_t stream);
 
+int SetFusedDecodeTrace(void *buffer, size_t bytes);
 size_t FusedDecodeWorkspaceBytes(int tokens, int hidden, int inter);
 int InitFusedDecodeWorkspace(void *workspace, size_t bytes, cudaStream_t stream);
 int LaunchFusedDecodeLayer(const Matrix *matrices, int layer, const int *ids, const float *routing, const float *normalized,
