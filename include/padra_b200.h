@@ -138,24 +138,44 @@ PADRA_API int padra_exl3_expert_launch(const padra_matrix *matrices, int layer, 
 
 /* ---- whole expert layer at decode (M = 1..16), one call ------------------------------------------------
  * The call order of the reference's decode layer (src/cuda/inference.cu:2963-2975: gate/up projection,
- * SwiGLU, down projection, combine with residual) as ONE persistent cooperative kernel.  ids/routing are
- * [tokens][8] (eight distinct experts per token, BF16-valued weights), normalized [tokens][hidden] is the
- * post-norm input, x [tokens][hidden] the residual stream updated in place.  workspace must hold
- * padra_exl3_moe_decode_workspace_bytes() bytes; its leading control words must be zero before the first
- * layer call (padra_exl3_moe_decode_workspace_init, once after allocation) and every layer call leaves them
- * zero again.  One workspace serves one stream at a time.  The kernel occupies every SM (one CTA each) and
- * needs the device to be otherwise idle on that stream's turn, like any cooperative launch. */
+ * SwiGLU, down projection, combine with residual) behind one entry point.  ids/routing are [tokens][8] (eight
+ * distinct experts per token, BF16-valued weights), normalized [tokens][hidden] is the post-norm input,
+ * x [tokens][hidden] the residual stream updated in place.  workspace must hold
+ * padra_exl3_moe_decode_workspace_bytes() bytes; one workspace serves one stream at a time.
+ *
+ * padra_exl3_moe_decode_layer enqueues four launches (split-K projection of gate+up, their epilogue with
+ * SwiGLU and the down input transform, split-K projection of down, its epilogue with combine); its workspace
+ * needs no initialisation.
+ * padra_exl3_moe_decode_layer_persistent does the same work in ONE persistent cooperative kernel (one CTA per
+ * SM, needs the device otherwise idle on that stream's turn); tokens must be 1 (PADRA_UNSUPPORTED otherwise).  The leading control words of its workspace must
+ * be zero before the first call (padra_exl3_moe_decode_workspace_init, once after allocation); every call
+ * leaves them zero again. */
 PADRA_API size_t padra_exl3_moe_decode_workspace_bytes(int tokens, int hidden, int inter);
 PADRA_API int padra_exl3_moe_decode_workspace_init(void *workspace, size_t workspace_bytes, padra_stream stream);
+PADRA_API int padra_exl3_moe_decode_layer(const padra_matrix *matrices, int layer, const int *ids,
+                                          const float *routing, const float *normalized, float *x, int tokens,
+                                          int rate, int hidden, int inter, const unsigned short *table,
+                                          void *workspace, size_t workspace_bytes, int *bad, padra_stream stream);
+/* Diagnostic: the same pipeline with only the selected launches enqueued (bit 0 gate+up projection, 1 its
+ * epilogue, 2 down projection, 3 its epilogue), so that one kernel can be timed or profiled alone on buffers a
+ * complete call has filled before. */
+PADRA_API int padra_exl3_moe_decode_layer_launches(const padra_matrix *matrices, int layer, const int *ids,
+                                                   const float *routing, const float *normalized, float *x,
+                                                   int tokens, int rate, int hidden, int inter,
+                                                   const unsigned short *table, void *workspace,
+                                                   size_t workspace_bytes, int *bad, padra_stream stream,
+                                                   unsigned launches);
+PADRA_API int padra_exl3_moe_decode_layer_persistent(const padra_matrix *matrices, int layer, const int *ids,
+                                                     const float *routing, const float *normalized, float *x,
+                                                     int tokens, int rate, int hidden, int inter,
+                                                     const unsigned short *table, void *workspace,
+                                                     size_t workspace_bytes, int *bad, padra_stream stream);
 /* Diagnostic timeline of the layer kernel, off by default (the reference's counterpart is its capture_trace
  * option, src/cuda/inference.cu:608-624).  buffer: device memory of 64 * 8 bytes per SM, or NULL to switch the
  * trace off.  While set, every layer call makes each CTA record %globaltimer at fixed points (start, set-up
  * done, streaming done, counting done, end, and per chunk); a host-side setting, not stream-ordered. */
 PADRA_API int padra_exl3_moe_decode_set_trace(void *buffer, size_t bytes);
-PADRA_API int padra_exl3_moe_decode_layer(const padra_matrix *matrices, int layer, const int *ids,
-                                          const float *routing, const float *normalized, float *x, int tokens,
-                                          int rate, int hidden, int inter, const unsigned short *table,
-                                          void *workspace, size_t workspace_bytes, int *bad, padra_stream stream);
+
 
 /* ---- utilities ------------------------------------------------------------------------------------------
  * Full FP16 decode of one matrix through the same codec the kernels use: out[input*rows + output].

@@ -135,7 +135,8 @@ int padra_exl3_expert_launch(const padra_matrix *matrices, int layer, int part, 
 size_t padra_exl3_moe_decode_workspace_bytes(int tokens, int hidden, int inter) {
   if (tokens < 1 || tokens > kMaxDecodeRows || hidden < 128 || inter < 128 || (hidden % 128) || (inter % 128))
     return 0;
-  return FusedDecodeWorkspaceBytes(tokens, hidden, inter);
+  const size_t persistent = FusedDecodeWorkspaceBytes(tokens, hidden, inter), split = SplitDecodeWorkspaceBytes(tokens, hidden, inter);
+  return persistent > split ? persistent : split; // one workspace serves either form of the layer call
 }
 
 int padra_exl3_moe_decode_workspace_init(void *workspace, size_t workspace_bytes, padra_stream stream) {
@@ -155,6 +156,34 @@ int padra_exl3_moe_decode_layer(const padra_matrix *matrices, int layer, const i
   if (!matrices || !ids || !routing || !normalized || !x || !table || !workspace || !bad || tokens < 1 ||
       tokens > kMaxDecodeRows || hidden < 128 || inter < 128 || (hidden % 128) || (inter % 128) || layer < 0)
     return PADRA_INVALID_ARGUMENT;
+  return LaunchSplitDecodeLayer(matrices, layer, ids, routing, normalized, x, tokens, rate, hidden, inter, table, workspace,
+                                workspace_bytes, bad, S(stream));
+}
+
+int padra_exl3_moe_decode_layer_launches(const padra_matrix *matrices, int layer, const int *ids, const float *routing,
+                                         const float *normalized, float *x, int tokens, int rate, int hidden, int inter,
+                                         const unsigned short *table, void *workspace, size_t workspace_bytes, int *bad,
+                                         padra_stream stream, unsigned launches) {
+  if (!RateOk(rate))
+    return PADRA_UNSUPPORTED;
+  if (!matrices || !ids || !routing || !normalized || !x || !table || !workspace || !bad || tokens < 1 ||
+      tokens > kMaxDecodeRows || hidden < 128 || inter < 128 || (hidden % 128) || (inter % 128) || layer < 0 || launches > 15u)
+    return PADRA_INVALID_ARGUMENT;
+  return LaunchSplitDecodeLayer(matrices, layer, ids, routing, normalized, x, tokens, rate, hidden, inter, table, workspace,
+                                workspace_bytes, bad, S(stream), launches);
+}
+
+int padra_exl3_moe_decode_layer_persistent(const padra_matrix *matrices, int layer, const int *ids, const float *routing,
+                                           const float *normalized, float *x, int tokens, int rate, int hidden, int inter,
+                                           const unsigned short *table, void *workspace, size_t workspace_bytes, int *bad,
+                                           padra_stream stream) {
+  if (!RateOk(rate))
+    return PADRA_UNSUPPORTED;
+  if (!matrices || !ids || !routing || !normalized || !x || !table || !workspace || !bad || tokens < 1 ||
+      tokens > kMaxDecodeRows || hidden < 128 || inter < 128 || (hidden % 128) || (inter % 128) || layer < 0)
+    return PADRA_INVALID_ARGUMENT;
+  if (tokens != 1)
+    return PADRA_UNSUPPORTED; // the persistent form is released for single-token steps only
   return LaunchFusedDecodeLayer(matrices, layer, ids, routing, normalized, x, tokens, rate, hidden, inter, table, workspace,
                                 workspace_bytes, bad, S(stream));
 }

@@ -55,10 +55,39 @@ PADRA_HD uint32_t HashedHalfBits(uint32_t state) {
 #endif
 }
 
+// (x >> 8) & 0xffff in one byte-permute (the second source is zero).
+PADRA_HD uint32_t MiddleHalf(uint32_t x) {
+#if defined(__CUDA_ARCH__)
+  return __byte_perm(x, 0u, 0x4421);
+#else
+  return (x >> 8) & 0xffffu;
+#endif
+}
+
+// The eight states of one K4 word, MSB-first: state j ends at bit 4*(j+1) of the 64-bit value previous:word, i.e.
+// s_j = ((previous:word) >> (28 - 4j)) & 0xffff.  Three funnel shifts bring every state to bit 0, 8 or 16 of some
+// register, where one instruction (mask, byte-permute with zero, or plain shift) isolates it: 11 operations for
+// 8 states instead of 15 with a shift and a mask each.
+PADRA_HD void StatesK4(uint32_t word, uint32_t previous, uint32_t (&s)[8]) {
+  const uint32_t by4 = FunnelRight(word, previous, 4), by16 = FunnelRight(word, previous, 16),
+                 by20 = FunnelRight(word, previous, 20);
+  s[7] = word & 0xffffu;
+  s[5] = MiddleHalf(word);
+  s[3] = word >> 16;
+  s[1] = MiddleHalf(by16);
+  s[6] = by4 & 0xffffu;
+  s[4] = MiddleHalf(by4);
+  s[2] = by4 >> 16;
+  s[0] = MiddleHalf(by20);
+}
+
 #if defined(__CUDACC__)
-// Two states -> two FP16 weights: one packed fused multiply-add (1024+s)*0x1eee + 0xc931, rounded once.
+// Two states -> two FP16 weights: one packed fused multiply-add (1024+s)*0x1eee + 0xc931, rounded once.  The two
+// 16-bit patterns are packed with a multiply-add (odd*65536 + even) so that the packing runs on the FMA pipe; the
+// integer ALU pipe is the scarcer one in these kernels.
 __device__ __forceinline__ uint32_t PairToHalf2(uint32_t even_state, uint32_t odd_state) {
-  const uint32_t packed = __byte_perm(HashedHalfBits(even_state), HashedHalfBits(odd_state), 0x5410);
+  uint32_t packed;
+  asm("mad.lo.u32 %0, %1, 65536, %2;" : "=r"(packed) : "r"(HashedHalfBits(odd_state)), "r"(HashedHalfBits(even_state)));
   const __half2 scale = __halves2half2(__ushort_as_half(0x1eee), __ushort_as_half(0x1eee));
   const __half2 shift = __halves2half2(__ushort_as_half(0xc931), __ushort_as_half(0xc931));
   const __half2 w = __hfma2(*reinterpret_cast<const __half2 *>(&packed), scale, shift);
@@ -103,6 +132,17 @@ __device__ __forceinline__ uint32_t DecodePair(const uint32_t (&words)[Rate], ui
 // All 32 weights of the lane.
 template <int Rate>
 __device__ __forceinline__ void Decode32(const uint32_t (&words)[Rate], uint32_t previous, uint32_t (&a)[4][4]) {
+  if constexpr (Rate == 4) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t s[8];
+      StatesK4(words[c], c ? words[c > 0 ? c - 1 : 0] : previous, s);
+#pragma unroll
+      for (int m = 0; m < 4; ++m)
+        a[c][FragmentOfPair(m)] = PairToHalf2(s[2 * m], s[2 * m + 1]);
+    }
+    return;
+  }
 #define PADRA_DECODE_GROUP(C)                                            \
   a[C][FragmentOfPair(0)] = DecodePair<Rate, C, 0>(words, previous);     \
   a[C][FragmentOfPair(1)] = DecodePair<Rate, C, 1>(words, previous);     \

@@ -741,12 +741,16 @@ __global__ void __launch_bounds__(kFusedThreads, 1) FusedDecodeLayerKernel(Fused
   __syncthreads();
   if (s_last) {
     __threadfence();
-    if (tid == 0 && LoadAcquire(&ctl->error) != 0u)
+    const unsigned error = LoadAcquire(&ctl->error);
+    if (tid == 0 && error != 0u)
       Raise(a.bad);
     __syncthreads();
     unsigned *words = reinterpret_cast<unsigned *>(ctl);
     for (int i = tid; i < static_cast<int>(sizeof(Control) / sizeof(unsigned)); i += kFusedThreads)
-      words[i] = 0u;
+      if (i != 3)
+        words[i] = 0u;
+    if (tid == 0)
+      ctl->pad[1] |= error; // sticky record of what went wrong (1 value, 2 ready poll, 4 store poll, 8 queue, 16 epilogue)
   }
   if (tid == 0)
     Trace(a, 4);

@@ -23,6 +23,10 @@ int LaunchCombinePacked(float *x, const unsigned short *down, const float *weigh
 int LaunchDecodeWeights(const Matrix *matrix, unsigned short *out, int rows, int cols, int rate, int *bad,
                         cudaStream_t stream);
 
+size_t SplitDecodeWorkspaceBytes(int tokens, int hidden, int inter);
+int LaunchSplitDecodeLayer(const Matrix *matrices, int layer, const int *ids, const float *routing, const float *normalized,
+                           float *x, int tokens, int rate, int hidden, int inter, const unsigned short *table, void *workspace,
+                           size_t workspace_bytes, int *bad, cudaStream_t stream, unsigned launches = 15u);
 int SetFusedDecodeTrace(void *buffer, size_t bytes);
 size_t FusedDecodeWorkspaceBytes(int tokens, int hidden, int inter);
 int InitFusedDecodeWorkspace(void *workspace, size_t bytes, cudaStream_t stream);

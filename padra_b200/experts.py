@@ -278,6 +278,22 @@ class ExpertKernels:
             self.mtp_launch(layer, 2, union, tokens, gate, down, stream=stream)
         self.combine(x, down, routing, tokens, stream)
 
+    def moe_decode_layer_launches(self, layer, ids, routing, normalized, x, tokens, launches, stream=None):
+        ws = self.decode_workspace(tokens)
+        st = self.lib.padra_exl3_moe_decode_layer_launches(self.t.descriptors.data_ptr(), layer, B.ptr(ids), B.ptr(routing),
+                                                           B.ptr(normalized), B.ptr(x), tokens, self.t.rate, *self.dims,
+                                                           B.ptr(self.table), B.ptr(ws), ws.numel(), B.ptr(self.bad),
+                                                           B.stream_handle(stream), launches)
+        B.check(st, "padra_exl3_moe_decode_layer_launches")
+
+    def moe_decode_layer_persistent(self, layer, ids, routing, normalized, x, tokens, stream=None):
+        ws = self.decode_workspace(tokens)
+        st = self.lib.padra_exl3_moe_decode_layer_persistent(self.t.descriptors.data_ptr(), layer, B.ptr(ids), B.ptr(routing),
+                                                             B.ptr(normalized), B.ptr(x), tokens, self.t.rate, *self.dims,
+                                                             B.ptr(self.table), B.ptr(ws), ws.numel(), B.ptr(self.bad),
+                                                             B.stream_handle(stream))
+        B.check(st, "padra_exl3_moe_decode_layer_persistent")
+
     def moe_decode_layer(self, layer, ids, routing, normalized, x, tokens, stream=None):
         ws = self.decode_workspace(tokens)
         st = self.lib.padra_exl3_moe_decode_layer(self.t.descriptors.data_ptr(), layer, B.ptr(ids), B.ptr(routing),

@@ -100,10 +100,17 @@ def test_multi_token_layer(oracle, gpu, rate, tokens):
     assert k.bad_flag() == 0
 
 
+FORMS = ["moe_decode_layer", "moe_decode_layer_persistent"]
+
+
+@pytest.mark.parametrize("form", FORMS)
 @pytest.mark.parametrize("rate", RATES)
 @pytest.mark.parametrize("tokens", [1, 3, 8, 13])
-def test_fused_layer_matches_separate_launches(oracle, gpu, rate, tokens):
-    """The persistent layer kernel against the per-part entry points launched one after another."""
+def test_layer_call_matches_separate_launches(oracle, gpu, rate, tokens, form):
+    """Both forms of the whole-layer call (four-launch pipeline, persistent kernel) against the per-part entry
+    points launched one after another."""
+    if form.endswith("persistent") and tokens != 1:
+        pytest.skip("the persistent form takes single-token steps only")
     hidden, inter = 512, 384
     host, table, k = make(1, hidden, inter, rate, 97, gpu)
     x, ids, w = routed_inputs(oracle, tokens, hidden, 40 + tokens)
@@ -111,56 +118,94 @@ def test_fused_layer_matches_separate_launches(oracle, gpu, rate, tokens):
     dw = torch.from_numpy(w.reshape(-1)).to(gpu)
     dx = torch.from_numpy(x).to(gpu)
     fused, separate = dx.clone(), dx.clone()
-    k.moe_decode_layer(0, dids, dw, dx, fused, tokens)
+    getattr(k, form)(0, dids, dw, dx, fused, tokens)
     k.moe_decode_layer_unfused(0, dids, dw, dx, separate, tokens)
-    assert_close_rows(fused.cpu().numpy(), separate.cpu().numpy(), "fused vs separate launches", chained=True)
+    assert_close_rows(fused.cpu().numpy(), separate.cpu().numpy(), "layer call vs separate launches", chained=True)
     again = dx.clone()
-    k.moe_decode_layer(0, dids, dw, dx, again, tokens)  # control words were left clean: a second call works
+    getattr(k, form)(0, dids, dw, dx, again, tokens)  # the workspace was left clean: a second call gives the same bits
     assert torch.equal(again, fused)
     assert k.bad_flag() == 0
 
 
-def test_fused_layer_mellum_dims(oracle, gpu):
-    """Hidden 2304 / intermediate 896 (18 and 7 blocks of 128): non-power-of-two chunk bookkeeping."""
+@pytest.mark.parametrize("form", FORMS)
+def test_layer_call_mellum_dims(oracle, gpu, form):
+    """Hidden 2304 / intermediate 896 (18 and 7 blocks of 128): non-power-of-two chunk and slice bookkeeping."""
     from padra_b200.experts import ExpertKernels, ExpertTable
 
     hidden, inter = 2304, 896
+    tokens = 1 if form.endswith("persistent") else 5
     table = ExpertTable(1, hidden, inter, 4, gpu).fill_random(9)
     k = ExpertKernels(table)
-    x, ids, w = routed_inputs(oracle, 5, hidden, 50)
+    x, ids, w = routed_inputs(oracle, tokens, hidden, 50)
     dids = torch.from_numpy(ids.reshape(-1)).to(gpu)
     dw = torch.from_numpy(w.reshape(-1)).to(gpu)
     dx = torch.from_numpy(x).to(gpu)
     fused, separate = dx.clone(), dx.clone()
-    k.moe_decode_layer(0, dids, dw, dx, fused, 5)
-    k.moe_decode_layer_unfused(0, dids, dw, dx, separate, 5)
+    getattr(k, form)(0, dids, dw, dx, fused, tokens)
+    k.moe_decode_layer_unfused(0, dids, dw, dx, separate, tokens)
     assert_close_rows(fused.cpu().numpy(), separate.cpu().numpy(), "fused vs separate launches, 2304/896", chained=True)
     assert k.bad_flag() == 0
 
 
-def test_fused_layer_rejects_bad_ids_and_descriptors(gpu):
+@pytest.mark.parametrize("form", FORMS)
+def test_layer_call_rejects_bad_ids_and_descriptors(gpu, form):
     _, table, k = make(1, 256, 128, 4, 101, gpu)
     x = torch.ones((1, 256), device=gpu)
     w = torch.full((8,), 0.125, device=gpu)
     out = x.clone()
-    k.moe_decode_layer(0, torch.tensor([0, 1, 2, 64, 4, 5, 6, 7], dtype=torch.int32, device=gpu), w, x, out, 1)
+    getattr(k, form)(0, torch.tensor([0, 1, 2, 64, 4, 5, 6, 7], dtype=torch.int32, device=gpu), w, x, out, 1)
     torch.cuda.synchronize()
     assert k.bad_flag() == 1 and torch.equal(out, x)  # refused before any work
     k.reset_bad()
     # a table of another rate: every chunk's descriptor check fails, the step completes and is flagged
     from padra_b200 import binding as B
     ws = k.decode_workspace(1)
-    st = k.lib.padra_exl3_moe_decode_layer(table.descriptors.data_ptr(), 0, B.ptr(torch.arange(8, dtype=torch.int32, device=gpu)),
-                                           B.ptr(w), B.ptr(x), B.ptr(out), 1, 6, 256, 128, B.ptr(k.table), B.ptr(ws), ws.numel(),
-                                           B.ptr(k.bad), B.stream_handle())
+    entry = getattr(k.lib, "padra_exl3_" + form)
+    st = entry(table.descriptors.data_ptr(), 0, B.ptr(torch.arange(8, dtype=torch.int32, device=gpu)),
+               B.ptr(w), B.ptr(x), B.ptr(out), 1, 6, 256, 128, B.ptr(k.table), B.ptr(ws), ws.numel(), B.ptr(k.bad), B.stream_handle())
     assert st == 0
     torch.cuda.synchronize()
     assert k.bad_flag() == 1
     k.reset_bad()
     good = x.clone()
-    k.moe_decode_layer(0, torch.arange(8, dtype=torch.int32, device=gpu), w, x, good, 1)  # and the workspace is reusable
+    getattr(k, form)(0, torch.arange(8, dtype=torch.int32, device=gpu), w, x, good, 1)  # and the workspace is reusable
     torch.cuda.synchronize()
     assert k.bad_flag() == 0 and not torch.equal(good, x)
+
+
+def test_persistent_form_is_single_token_only(gpu):
+    from padra_b200 import binding as B
+
+    _, table, k = make(1, 256, 128, 4, 103, gpu)
+    ws = k.decode_workspace(2)
+    x = torch.ones((2, 256), device=gpu)
+    ids = torch.arange(16, dtype=torch.int32, device=gpu)
+    w = torch.full((16,), 0.125, device=gpu)
+    st = k.lib.padra_exl3_moe_decode_layer_persistent(table.descriptors.data_ptr(), 0, B.ptr(ids), B.ptr(w), B.ptr(x), B.ptr(x), 2, 4,
+                                                      256, 128, B.ptr(k.table), B.ptr(ws), ws.numel(), B.ptr(k.bad), B.stream_handle())
+    assert st == B.UNSUPPORTED
+
+
+@pytest.mark.parametrize("form", FORMS)
+def test_layer_call_repeated_many_times_single_token(oracle, gpu, form):
+    """Forty back-to-back single-token steps over two layers of the benchmark shape: every one must agree with the
+    per-part launches and leave the error flag down (guards the hand-shakes inside the persistent kernel)."""
+    from padra_b200.experts import ExpertKernels, ExpertTable, bf16_values, route_topk
+
+    hidden, inter = 2048, 1024
+    table = ExpertTable(2, hidden, inter, 4, gpu).fill_random(5)
+    k = ExpertKernels(table)
+    g = torch.Generator(device=gpu)
+    g.manual_seed(77)
+    for it in range(40):
+        ids, w = route_topk(bf16_values(torch.randn((1, 64), device=gpu, generator=g)))
+        n = bf16_values(torch.randn((1, hidden), device=gpu, generator=g))
+        x = bf16_values(torch.randn((1, hidden), device=gpu, generator=g))
+        a, b = x.clone(), x.clone()
+        getattr(k, form)(it % 2, ids.reshape(-1), w.reshape(-1), n, a, 1)
+        k.moe_decode_layer_unfused(it % 2, ids.reshape(-1), w.reshape(-1), n, b, 1)
+        assert_close_rows(a.cpu().numpy(), b.cpu().numpy(), f"step {it}", chained=True)
+    assert k.bad_flag() == 0
 
 
 def test_config1_layer_k4(oracle, gpu):
@@ -278,23 +323,25 @@ def test_overflowing_activation_sets_flag(gpu):
     assert k.bad_flag() == 1
 
 
-def test_layer_call_is_graph_capturable_and_deterministic(oracle, gpu):
+@pytest.mark.parametrize("form", FORMS)
+def test_layer_call_is_graph_capturable_and_deterministic(oracle, gpu, form):
     hidden, inter = 512, 256
+    tokens = 1 if form.endswith("persistent") else 5
     _, table, k = make(1, hidden, inter, 4, 59, gpu)
-    x, ids, w = routed_inputs(oracle, 5, hidden, 8)
+    x, ids, w = routed_inputs(oracle, tokens, hidden, 8)
     dids = torch.from_numpy(ids.reshape(-1)).to(gpu)
     dw = torch.from_numpy(w.reshape(-1)).to(gpu)
     dx = torch.from_numpy(x).to(gpu)
-    k.decode_workspace(5)
+    k.decode_workspace(tokens)
     eager = dx.clone()
-    k.moe_decode_layer(0, dids, dw, dx, eager, 5)
+    getattr(k, form)(0, dids, dw, dx, eager, tokens)
     static = dx.clone()
     stream = torch.cuda.Stream()
     stream.wait_stream(torch.cuda.current_stream())
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(stream):
         with torch.cuda.graph(graph, stream=stream):
-            k.moe_decode_layer(0, dids, dw, dx, static, 5, stream=stream)
+            getattr(k, form)(0, dids, dw, dx, static, tokens, stream=stream)
     results = []
     for _ in range(3):
         static.copy_(dx)
