@@ -235,19 +235,24 @@ def run_ours(args):
             slots[i % len(slots)]["graph"].replay()
     with ClockSampler(local) as clocks:
         seconds = timed(args.steps, lambda i: slots[i % len(slots)]["graph"].replay())
-        # the dominant kernel alone (gate+up split-K projection: 16.0 MiB of the step's 24 MiB of packed words),
-        # one launch per step outside any graph, each bracketed by events on the launching stream
-        kernel_ms = []
+        # the dominant kernel alone (gate+up split-K projection: 16.0 MiB of the step's 24 MiB of packed words): a CUDA
+        # graph of one such launch per layer, so that the GPU and not the launching thread sets the pace; CUDA events
+        # on the launching stream around whole replays, divided by the launches they contain
+        kernel_graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(stream):
-            for i in range(args.warmup + min(args.steps, 200)):
-                s = slots[i % len(slots)]
-                ev_a, ev_b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                ev_a.record(stream)
-                k.moe_decode_layer_launches(s["layer"], s["ids"], s["w"], s["normalized"], s["x"], TOKENS, 1, stream=stream)
-                ev_b.record(stream)
-                kernel_ms.append((ev_a, ev_b))
-        stream.synchronize()
-        kernel_ms = [x.elapsed_time(y) for x, y in kernel_ms[args.warmup:]]
+            with torch.cuda.graph(kernel_graph, stream=stream):
+                for s in slots[:layers]:
+                    k.moe_decode_layer_launches(s["layer"], s["ids"], s["w"], s["normalized"], s["x"], TOKENS, 1, stream=stream)
+            for _ in range(3):
+                kernel_graph.replay()
+            ev_a, ev_b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            kernel_reps = max(3, min(args.steps, 560) // layers)
+            ev_a.record(stream)
+            for _ in range(kernel_reps):
+                kernel_graph.replay()
+            ev_b.record(stream)
+        ev_b.synchronize()
+        kernel_ms = [ev_a.elapsed_time(ev_b) / (kernel_reps * layers)]
         # for comparison: the persistent single-kernel form of the layer call
         persistent_graphs = []
         for s in slots[:min(len(slots), 28)]:

@@ -35,6 +35,17 @@ __device__ __forceinline__ void Unpack4(uint2 bits, float (&f)[4]) {
   f[3] = HalfBitsToFloat(bits.y >> 16);
 }
 
+// Programmatic dependent launch: each kernel of the pipeline is launched with programmatic stream serialization,
+// lets its successor start launching at once and itself waits for its predecessor right before the first access
+// to data the predecessor produces.  What comes before the wait (unit lookup, descriptor checks, the first packed
+// words in flight) overlaps the predecessor's tail.  Without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void LetSuccessorLaunch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void WaitForPredecessor() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 struct SplitArgs {
   const Matrix *matrices;
   int layer, phase; // phase 0: gate and up from `normalized`; phase 1: down from `xdown`
@@ -117,11 +128,12 @@ __global__ void __launch_bounds__(kThreads) SplitProjectionKernel(SplitArgs a) {
   using L = codec::Lane<Rate>;
   extern __shared__ __align__(16) unsigned char smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (*a.bad)
-    return;
+  LetSuccessorLaunch();
   int expert, count, rows[8 * NG];
-  if (!ResolveUnit<NG>(a.ids, a.tokens, blockIdx.y, expert, count, rows, a.bad))
+  if (!ResolveUnit<NG>(a.ids, a.tokens, blockIdx.y, expert, count, rows, a.bad)) {
+    WaitForPredecessor();
     return;
+  }
   const int part = a.phase ? 2 : static_cast<int>(blockIdx.z) / a.slices;
   const int slice = static_cast<int>(blockIdx.z) % a.slices;
   const Matrix m = a.matrices[(static_cast<size_t>(a.layer) * kExperts + expert) * 3 + part];
@@ -129,6 +141,7 @@ __global__ void __launch_bounds__(kThreads) SplitProjectionKernel(SplitArgs a) {
   const int base = blockIdx.x * 128;
   if (m.format != FormatOfRate(Rate) || m.rows != want_rows || m.cols != want_cols || base + 128 > m.rows || !m.data ||
       !m.suh || !m.svh) {
+    WaitForPredecessor();
     if (!threadIdx.x)
       Raise(a.bad);
     return;
@@ -136,6 +149,22 @@ __global__ void __launch_bounds__(kThreads) SplitProjectionKernel(SplitArgs a) {
   const int span = m.cols / a.slices, k_begin = slice * span; // inputs of this slice, a multiple of 128
   const int stride = span + 8;
   __half *xs = reinterpret_cast<__half *>(smem);
+
+  // ---- the first packed words go in flight before anything else is touched ----
+  const int g = lane >> 2, t = lane & 3;
+  const int tiles_per_kstep = m.rows / 16, column = blockIdx.x * 8 + warp;
+  const unsigned char *lane_base =
+      m.data + (static_cast<size_t>(k_begin / 16 + t) * tiles_per_kstep + column) * L::kTileBytes + g * L::kBytes;
+  const size_t round_bytes = static_cast<size_t>(4) * tiles_per_kstep * L::kTileBytes;
+  const int rounds = span / 64; // even: a slice is a whole number of 128-input blocks
+  uint32_t fetched[4][Rate];   // four rounds in flight; short slices re-read their last pair instead of branching
+#pragma unroll
+  for (int d = 0; d < 4; ++d)
+    codec::LoadWords<Rate>(lane_base + static_cast<size_t>(d < rounds ? d : rounds - 2 + (d & 1)) * round_bytes, fetched[d]);
+
+  WaitForPredecessor(); // from here on: the activations the predecessor wrote, and this kernel's own stores
+  if (*a.bad)
+    return;
 
   // ---- activation rows of the slice, permuted K16 order ----
   if (a.phase == 0) {
@@ -165,18 +194,12 @@ __global__ void __launch_bounds__(kThreads) SplitProjectionKernel(SplitArgs a) {
     for (int n = 0; n < count; ++n) {
       const __half *x = a.xdown + static_cast<size_t>(rows[n]) * m.cols + k_begin;
       for (int i = threadIdx.x; i < span / 8; i += kThreads)
-        *reinterpret_cast<uint4 *>(xs + n * stride + i * 8) = __ldg(reinterpret_cast<const uint4 *>(x + i * 8));
+        *reinterpret_cast<uint4 *>(xs + n * stride + i * 8) = __ldcg(reinterpret_cast<const uint4 *>(x + i * 8));
     }
   }
   __syncthreads();
 
   // ---- stream, decode, multiply (lane ownership as in decode.cu) ----
-  const int g = lane >> 2, t = lane & 3;
-  const int tiles_per_kstep = m.rows / 16, column = blockIdx.x * 8 + warp;
-  const unsigned char *lane_base =
-      m.data + (static_cast<size_t>(k_begin / 16 + t) * tiles_per_kstep + column) * L::kTileBytes + g * L::kBytes;
-  const size_t round_bytes = static_cast<size_t>(4) * tiles_per_kstep * L::kTileBytes;
-  const int rounds = span / 64; // even: a slice is a whole number of 128-input blocks
   float acc[NG][4];
   const __half *xrow[NG];
 #pragma unroll
@@ -187,11 +210,6 @@ __global__ void __launch_bounds__(kThreads) SplitProjectionKernel(SplitArgs a) {
     const int n = g + 8 * ng;
     xrow[ng] = xs + (n < count ? n : count - 1) * stride + t * 16;
   }
-  // Two rounds per iteration, the packed words of the next iteration already in flight.  The prefetch address is
-  // clamped to the last pair of rounds instead of branching: the final iteration re-reads words it already holds.
-  uint32_t even[Rate], odd[Rate];
-  codec::LoadWords<Rate>(lane_base, even);
-  codec::LoadWords<Rate>(lane_base + round_bytes, odd);
   auto multiply = [&](const uint32_t (&words)[Rate], int round) {
     const uint32_t previous = __shfl_sync(0xffffffffu, words[Rate - 1], (lane + 28) & 31);
     uint32_t frag[4][4];
@@ -206,18 +224,26 @@ __global__ void __launch_bounds__(kThreads) SplitProjectionKernel(SplitArgs a) {
       MmaF16(frag[3], hi.z, hi.w, acc[ng]);
     }
   };
-  for (int round = 0; round < rounds; round += 2) {
-    uint32_t now_even[Rate], now_odd[Rate];
+  // Two rounds per half-iteration; while one pair is multiplied the pair four rounds ahead is requested.  The
+  // prefetch index is clamped to the slice's last pair, so the tail re-reads words instead of branching.
+  for (int round = 0; round < rounds; round += 4) {
 #pragma unroll
-    for (int i = 0; i < Rate; ++i) {
-      now_even[i] = even[i];
-      now_odd[i] = odd[i];
+    for (int half = 0; half < 2; ++half) {
+      const int r = round + 2 * half;
+      if (r < rounds) { // warp-uniform
+        uint32_t now_even[Rate], now_odd[Rate];
+#pragma unroll
+        for (int i = 0; i < Rate; ++i) {
+          now_even[i] = fetched[2 * half][i];
+          now_odd[i] = fetched[2 * half + 1][i];
+        }
+        const int ahead = r + 4 < rounds ? r + 4 : rounds - 2;
+        codec::LoadWords<Rate>(lane_base + static_cast<size_t>(ahead) * round_bytes, fetched[2 * half]);
+        codec::LoadWords<Rate>(lane_base + static_cast<size_t>(ahead + 1) * round_bytes, fetched[2 * half + 1]);
+        multiply(now_even, r);
+        multiply(now_odd, r + 1);
+      }
     }
-    const int ahead = round + 2 < rounds ? round + 2 : rounds - 2;
-    codec::LoadWords<Rate>(lane_base + static_cast<size_t>(ahead) * round_bytes, even);
-    codec::LoadWords<Rate>(lane_base + static_cast<size_t>(ahead + 1) * round_bytes, odd);
-    multiply(now_even, round);
-    multiply(now_odd, round + 1);
   }
   // accumulator (row g | g+8, column 2t | 2t+1) -> this slice's sums of the warp's 16 outputs
 #pragma unroll
@@ -242,6 +268,8 @@ __global__ void __launch_bounds__(128) GateUpEpilogueKernel(const Matrix *matric
                                                             const unsigned short *table, __half *xdown, int *bad) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int pair = blockIdx.y, nb = blockIdx.x * 4 + warp;
+  LetSuccessorLaunch();
+  WaitForPredecessor();
   if (*bad || pair >= pairs || nb >= inter / 128)
     return;
   const int expert = ids[pair];
@@ -309,6 +337,8 @@ __global__ void __launch_bounds__(256) DownEpilogueKernel(const Matrix *matrices
   __shared__ float s_down[kTopK][128];
   const int lane = threadIdx.x & 31, slot = threadIdx.x >> 5;
   const int token = blockIdx.y, nb = blockIdx.x;
+  LetSuccessorLaunch();
+  WaitForPredecessor();
   if (*bad || token >= tokens)
     return;
   const int pair = token * kTopK + slot, out = nb * 128 + lane * 4;
@@ -376,6 +406,21 @@ struct SplitWorkspace {
   }
 };
 
+// `programmatic` = the kernel may start before its predecessor in the stream has finished and waits for it itself.
+// The first kernel of the pipeline is launched without it: what precedes it is the caller's work (router, norm),
+// whose results it reads from its first instruction on.
+template <typename... KernelArgs, typename... Args>
+int LaunchDependent(bool programmatic, void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                    Args... args) {
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = programmatic ? 1 : 0;
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid, config.blockDim = block, config.dynamicSmemBytes = smem, config.stream = stream;
+  config.attrs = &attribute, config.numAttrs = 1;
+  return CudaStatus(cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...));
+}
+
 // K-slices: enough CTAs to fill the machine about four deep, slices of whole 128-input blocks.
 int PickSlices(int cols, int base_ctas) {
   int slices = kMaxSlices;
@@ -392,8 +437,7 @@ template <int Rate, int NG> int LaunchSplit(const SplitArgs &a, dim3 grid, size_
       return PADRA_RESOURCE_EXHAUSTED;
     configured = smem;
   }
-  SplitProjectionKernel<Rate, NG><<<grid, kThreads, smem, stream>>>(a);
-  return CudaStatus(cudaGetLastError());
+  return LaunchDependent(a.phase != 0, SplitProjectionKernel<Rate, NG>, grid, dim3(kThreads), smem, stream, a);
 }
 
 int DispatchSplit(const SplitArgs &a, int rate, bool wide, dim3 grid, size_t smem, cudaStream_t stream) {
@@ -440,9 +484,9 @@ int LaunchSplitDecodeLayer(const Matrix *matrices, int layer, const int *ids, co
   if (status != PADRA_OK)
     return status;
   if (launches & 2u)
-    GateUpEpilogueKernel<<<dim3((inter / 128 + 3) / 4, pairs), 128, 0, stream>>>(matrices, layer, ids, pairs, hidden, inter,
-                                                                                 a.slices, gateup, table, xdown, bad);
-  if ((status = CudaStatus(cudaGetLastError())) != PADRA_OK)
+    status = LaunchDependent(true, GateUpEpilogueKernel, dim3((inter / 128 + 3) / 4, pairs), dim3(128), 0, stream, matrices, layer, ids,
+                             pairs, hidden, inter, a.slices, static_cast<const float *>(gateup), table, xdown, bad);
+  if (status != PADRA_OK)
     return status;
   // down
   a.phase = 1, a.partials = down, a.slices = PickSlices(inter, (hidden / 128) * units);
@@ -450,9 +494,9 @@ int LaunchSplitDecodeLayer(const Matrix *matrices, int layer, const int *ids, co
   if ((launches & 4u) && (status = DispatchSplit(a, rate, wide, dim3(hidden / 128, units, a.slices), smem, stream)) != PADRA_OK)
     return status;
   if (launches & 8u)
-    DownEpilogueKernel<<<dim3(hidden / 128, tokens), 256, 0, stream>>>(matrices, layer, ids, routing, tokens, hidden, a.slices,
-                                                                       down, x, bad);
-  return CudaStatus(cudaGetLastError());
+    status = LaunchDependent(true, DownEpilogueKernel, dim3(hidden / 128, tokens), dim3(256), 0, stream, matrices, layer, ids, routing,
+                             tokens, hidden, a.slices, static_cast<const float *>(down), x, bad);
+  return status;
 }
 
 } // namespace padra
