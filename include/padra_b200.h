@@ -119,7 +119,9 @@ PADRA_API int padra_exl3_schedule(const int *counts, padra_tile *tiles, int *til
  * one argument list for all three rates.  input is FP32-held BF16 [tokens][hidden] (parts 0, 1); gate/up are
  * BF16-bit [pairs][inter] (part 2, SwiGLU applied while building the down input); output is BF16-bit
  * [pairs][rows]; transformed is workspace of pairs*cols halves.  tiles/tile_count/counts/ids are read only
- * through `groups` and `counts` here; stats and wide_input are accepted and unused.
+ * through `groups` and `counts` here; stats is accepted and unused.  wide_input (set by the reference's
+ * selected server options) selects the tensor-memory grouped GEMM (tcgen05, 128 outputs x up to 256 tokens per
+ * CTA); 0 selects the small-tile kernel (32 pairs per CTA).
  * Returns PADRA_INVALID_ARGUMENT for tokens < 4, where the reference throws. */
 PADRA_API int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer, int part, const int *ids,
                                         const int *groups, const int *counts, const padra_tile *tiles,

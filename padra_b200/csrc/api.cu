@@ -103,10 +103,7 @@ int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer, int part,
                               const unsigned short *table, void *transformed, int tokens, int *bad, padra_stream stream,
                               unsigned *stats, int wide_input, int rate, int hidden, int inter) {
   (void)stats;
-  (void)wide_input;
   (void)ids;
-  (void)counts;
-  (void)transformed;
   if (!RateOk(rate))
     return PADRA_UNSUPPORTED;
   if (tokens < 4 || tokens > 2048 || part < 0 || part > 2) // the reference throws below four tokens
@@ -114,6 +111,12 @@ int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer, int part,
   if (!matrices || !groups || !tiles || !tile_count || !output || !bad || hidden < 128 || inter < 128 ||
       (hidden % 128) || (inter % 128) || (part == 2 ? (!gate || !up || !table) : !input))
     return PADRA_INVALID_ARGUMENT;
+  // wide_input: 0 = the 32-pair tile kernel on the tensor-core fragments path, 1 = the tensor-memory grouped GEMM
+  // (needs `transformed` and `counts`), which is what a caller with the reference's selected options passes
+  // (src/runtime/model_runtime.cpp:22-34 sets exl3_wide_input).
+  if (wide_input && transformed && counts)
+    return LaunchPrefillTensorMemory(matrices, layer, part, groups, counts, input, output, gate, up, table, transformed, tokens, bad,
+                                     S(stream), rate, hidden, inter);
   return LaunchTileProjection(matrices, layer, part, groups, tiles, tile_count, input, output, gate, up, table, tokens,
                               bad, S(stream), rate, hidden, inter);
 }

@@ -37,6 +37,10 @@ int LaunchTileProjection(const Matrix *matrices, int layer, int part, const int 
                          const int *tile_count, const float *input, unsigned short *output,
                          const unsigned short *gate, const unsigned short *up, const unsigned short *table, int tokens,
                          int *bad, cudaStream_t stream, int rate, int hidden, int inter);
+int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, const float *input,
+                              unsigned short *output, const unsigned short *gate, const unsigned short *up,
+                              const unsigned short *table, void *transformed, int tokens, int *bad, cudaStream_t stream, int rate,
+                              int hidden, int inter);
 int LaunchGroup(const int *ids, int *groups, int *counts, int tokens, int *bad, cudaStream_t stream);
 int LaunchSchedule(const int *counts, padra_tile *tiles, int *tile_count, int tokens, int *bad, cudaStream_t stream);
 int LaunchPrefill(const Matrix *matrices, int layer, int part, const int *ids, const int *groups, const int *counts,

@@ -1,0 +1,461 @@
+// Prefill: the grouped per-expert projection on the 5th-generation tensor cores (tcgen05.mma, accumulators in
+// tensor memory), with the trellis decode fused into the producer side of the pipeline.
+//
+// One CTA computes a 128-output x N-token tile (N <= 256) of one expert:  D[o][n] = sum_k W[k][o] * x~[n][k].
+//   * operand A = weights.  Eight producer warps (one per 16-output tile column) read packed words, decode 32
+//     weights per lane in registers (codec.cuh) and store them as 16-byte rows of 8x8 FP16 core matrices into the
+//     canonical K-major, no-swizzle shared-memory layout: with the lane <-> (row pair, K-step) ownership of the
+//     codec the four 16-byte stores of a quarter-warp are 128 contiguous bytes.
+//   * operand B = the expert's transformed activation rows (FP16, written in expert-grouped order by
+//     PrefillInputKernel), copied with cp.async into the same canonical layout.
+//   * one elected thread issues tcgen05.mma (M = 128, N = tile tokens rounded up to 16, K = 16), four per 64-input
+//     stage, and commits each stage back to the producers; a 4-stage ring of (16 KB A + up to 32 KB B).
+//   * four epilogue warps read the FP32 accumulators from tensor memory (one output row per thread), run the 128-point
+//     output Hadamard ACROSS the 128 outputs (five shuffle stages inside a warp, two through shared memory), apply
+//     svh, round to BF16 and scatter the rows to their (token, slot) pairs.
+// Every wait on an mbarrier is bounded: on expiry the CTA raises the sticky error flag, skips the rest of its work,
+// frees its tensor memory and leaves.
+#include "codec.cuh"
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace padra {
+namespace {
+
+constexpr int kStages = 4;
+constexpr int kStageK = 64;   // inputs per pipeline stage (four K16 steps)
+constexpr int kTileM = 128;   // outputs per CTA
+constexpr int kMaxTileN = 256; // tokens per CTA
+constexpr int kStageABytes = kTileM * kStageK * 2;    // 16 KB
+constexpr int kStageBBytes = kMaxTileN * kStageK * 2; // 32 KB
+constexpr int kEpilogueWarps = 4, kProducerWarps = 8;
+constexpr int kMmaWarp = kEpilogueWarps;
+constexpr int kFirstProducerWarp = kMmaWarp + 1;
+constexpr int kPrefillThreads = (kEpilogueWarps + 1 + kProducerWarps) * 32; // 416
+constexpr int kProducerThreads = kProducerWarps * 32;
+constexpr int kTmemColumns = 256;
+constexpr unsigned kWaitLimit = 1u << 24;
+constexpr int kMaxTokensPrefill = 2048;
+
+struct PrefillSmem {
+  alignas(1024) unsigned char a[kStages][kStageABytes];
+  alignas(1024) unsigned char b[kStages][kStageBBytes];
+  alignas(16) float exchange[kEpilogueWarps][16][32]; // cross-warp Hadamard stages of one 16-token chunk
+  alignas(8) unsigned long long full[kStages], empty[kStages], accumulator_ready;
+  int pairs[kMaxTileN]; // (token*8+slot) of the tile's rows
+  unsigned tmem_base;
+  int abort, expert, begin, valid, row_base;
+};
+
+struct PrefillArgs {
+  const Matrix *matrices;
+  int layer, part;
+  const int *groups, *counts;
+  const __half *transformed; // [pairs][cols] in expert-grouped order
+  unsigned short *output;    // [pairs][rows] BF16 bits, pair order
+  int tokens, hidden, inter;
+  int *bad;
+};
+
+__device__ __forceinline__ unsigned SmemAddress(const void *p) {
+  return static_cast<unsigned>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void BarrierInit(unsigned long long *bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(SmemAddress(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void BarrierArrive(unsigned long long *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(SmemAddress(bar)) : "memory");
+}
+// Bounded wait for the phase of parity `parity`; false if it did not complete in time or the CTA is aborting.
+__device__ __forceinline__ bool BarrierWait(unsigned long long *bar, unsigned parity, const volatile int *abort) {
+  const unsigned addr = SmemAddress(bar);
+  for (unsigned spins = 0; spins < kWaitLimit; ++spins) {
+    unsigned done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done)
+                 : "r"(addr), "r"(parity)
+                 : "memory");
+    if (done)
+      return true;
+    if ((spins & 1023u) == 1023u && *abort)
+      return false;
+  }
+  return false;
+}
+__device__ __forceinline__ unsigned long long OperandDescriptor(unsigned smem_address, unsigned leading_bytes, unsigned stride_bytes) {
+  // K-major, no swizzle: 8x8 core matrices of 128 contiguous bytes; `leading` = distance between the two 16-byte
+  // K halves of a K16 step, `stride` = distance between 8-row groups.  Bits: [0,14) address>>4, [16,30) leading>>4,
+  // [32,46) stride>>4, [46,48) descriptor version 1 (sm_100), [61,64) layout 0 = no swizzle.
+  return static_cast<unsigned long long>((smem_address & 0x3ffffu) >> 4) | (static_cast<unsigned long long>(leading_bytes >> 4) << 16) |
+         (static_cast<unsigned long long>(stride_bytes >> 4) << 32) | (1ull << 46);
+}
+__device__ __forceinline__ unsigned InstructionDescriptor(int n) {
+  // kind::f16: FP32 accumulate (bits 4-5 = 1), A and B FP16 (0), both K-major (0), N>>3 at [17,23), M>>4 at [24,29)
+  return (1u << 4) | (static_cast<unsigned>(n >> 3) << 17) | (static_cast<unsigned>(kTileM >> 4) << 24);
+}
+__device__ __forceinline__ void MmaSS(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc, unsigned idesc, bool accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1u : 0u)
+               : "memory");
+}
+__device__ __forceinline__ void MmaCommit(unsigned long long *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(SmemAddress(bar)) : "memory");
+}
+__device__ __forceinline__ void TmemLoad16(unsigned taddr, float (&v)[16]) {
+  unsigned r[16];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                 "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr)
+               : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    v[i] = __uint_as_float(r[i]);
+}
+
+template <int Rate>
+__global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillArgs a) {
+  using L = codec::Lane<Rate>;
+  extern __shared__ unsigned char raw_smem[];
+  PrefillSmem &sm = *reinterpret_cast<PrefillSmem *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rows = a.part == 2 ? a.hidden : a.inter, cols = a.part == 2 ? a.inter : a.hidden;
+  const int pairs_total = a.tokens * kTopK;
+
+  // ---- which (expert, token tile) is this CTA's; leave before touching anything if there is none ----
+  if (tid == 0) {
+    sm.abort = 0;
+    sm.expert = -1;
+    int tile = blockIdx.y, base = 0, invalid = *a.bad != 0;
+    for (int e = 0; e < kExperts && !invalid; ++e) {
+      const int n = a.counts[e];
+      if (n < 0 || n > a.tokens || base + n > pairs_total) {
+        invalid = 1;
+        break;
+      }
+      const int tiles = (n + kMaxTileN - 1) / kMaxTileN;
+      if (tile < tiles) {
+        sm.expert = e;
+        sm.begin = tile * kMaxTileN;
+        sm.valid = n - sm.begin < kMaxTileN ? n - sm.begin : kMaxTileN;
+        sm.row_base = base + sm.begin;
+        break;
+      }
+      tile -= tiles;
+      base += n;
+    }
+    if (invalid && !*a.bad)
+      Raise(a.bad);
+    if (sm.expert >= 0) {
+      const Matrix &m = a.matrices[(static_cast<size_t>(a.layer) * kExperts + sm.expert) * 3 + a.part];
+      if (m.format != FormatOfRate(Rate) || m.rows != rows || m.cols != cols || (cols % kStageK) || (rows % kTileM) || !m.data ||
+          !m.svh) {
+        Raise(a.bad);
+        sm.expert = -1;
+      }
+    }
+  }
+  __syncthreads();
+  if (sm.expert < 0)
+    return;
+  const int expert = sm.expert, valid = sm.valid;
+  const int tile_n = (valid + 15) & ~15; // MMA N: a multiple of 16 for M = 128
+  const Matrix m = a.matrices[(static_cast<size_t>(a.layer) * kExperts + expert) * 3 + a.part];
+  const int stages = cols / kStageK;
+
+  for (int n = tid; n < valid; n += kPrefillThreads) {
+    const int pair = a.groups[expert * a.tokens + sm.begin + n];
+    sm.pairs[n] = pair;
+    if (pair < 0 || pair >= pairs_total) {
+      Raise(a.bad);
+      sm.abort = 1;
+    }
+  }
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      BarrierInit(&sm.full[s], kProducerWarps);
+      BarrierInit(&sm.empty[s], 1);
+    }
+    BarrierInit(&sm.accumulator_ready, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kMmaWarp) { // one warp allocates the accumulator columns and gives the permit back
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddress(&sm.tmem_base)), "r"(kTmemColumns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem = sm.tmem_base;
+  const volatile int *abort = &sm.abort;
+
+  if (warp >= kFirstProducerWarp) {
+    // =============================== producers ===============================
+    const int column = warp - kFirstProducerWarp; // 16-output tile column inside the 128-output block
+    const int ptid = tid - kFirstProducerWarp * 32;
+    const int g = lane & 7, kstep = lane >> 3; // row pair, K16 step inside the stage
+    const size_t tiles_per_kstep = rows / 16;
+    const unsigned char *lane_base = m.data + (static_cast<size_t>(kstep) * tiles_per_kstep + blockIdx.x * 8 + column) * L::kTileBytes + g * L::kBytes;
+    const size_t stage_bytes = static_cast<size_t>(4) * tiles_per_kstep * L::kTileBytes;
+    const __half *b_rows = a.transformed + static_cast<size_t>(sm.row_base) * cols;
+    uint32_t ahead0[Rate], ahead1[Rate]; // packed words of the next two stages
+    codec::LoadWords<Rate>(lane_base, ahead0);
+    codec::LoadWords<Rate>(lane_base + (stages > 1 ? stage_bytes : 0), ahead1);
+    bool alive = !*abort;
+    for (int i = 0; i < stages && alive; ++i) {
+      const int s = i % kStages;
+      uint32_t words[Rate];
+#pragma unroll
+      for (int w = 0; w < Rate; ++w) {
+        words[w] = ahead0[w];
+        ahead0[w] = ahead1[w];
+      }
+      codec::LoadWords<Rate>(lane_base + static_cast<size_t>(i + 2 < stages ? i + 2 : stages - 1) * stage_bytes, ahead1);
+      const uint32_t previous = __shfl_sync(0xffffffffu, words[Rate - 1], (lane & 24) | ((lane + 7) & 7));
+      uint32_t frag[4][4];
+      codec::Decode32<Rate>(words, previous, frag);
+      // the stage's buffers are free once the MMAs that read them four stages ago have completed
+      alive = BarrierWait(&sm.empty[s], ((i / kStages) & 1) ^ 1, abort);
+      if (!alive)
+        break;
+      // B: tile_n rows x 64 inputs as 16-byte pieces, piece q = (row, K piece): canonical layout [K piece][row/8][row%8]
+      unsigned char *b_stage = sm.b[s];
+      for (int q = ptid; q < tile_n * 8; q += kProducerThreads) {
+        const int n = q >> 3, piece = q & 7;
+        const __half *src = b_rows + static_cast<size_t>(n < valid ? n : valid - 1) * cols + i * kStageK + piece * 8;
+        const unsigned dst = SmemAddress(b_stage + piece * (tile_n * 16) + (n >> 3) * 128 + (n & 7) * 16);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      // A: this lane's four 16-byte core-matrix rows (fragment f: K half f>>1, output group f&1)
+      unsigned char *a_stage = sm.a[s];
+#pragma unroll
+      for (int f = 0; f < 4; ++f) {
+        const uint4 row = make_uint4(frag[0][f], frag[1][f], frag[2][f], frag[3][f]);
+        *reinterpret_cast<uint4 *>(a_stage + (2 * kstep + (f >> 1)) * 2048 + (2 * column + (f & 1)) * 128 + g * 16) = row;
+      }
+      // publish the PREVIOUS stage: its cp.async group has had a whole iteration to land
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (i > 0 && lane == 0)
+        BarrierArrive(&sm.full[(i - 1) % kStages]);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (alive && lane == 0)
+      BarrierArrive(&sm.full[(stages - 1) % kStages]);
+  } else if (warp == kMmaWarp) {
+    // =============================== MMA issue ===============================
+    if (lane == 0) {
+      const unsigned idesc = InstructionDescriptor(tile_n);
+      bool alive = !*abort;
+      for (int i = 0; i < stages && alive; ++i) {
+        const int s = i % kStages;
+        alive = BarrierWait(&sm.full[s], (i / kStages) & 1, abort);
+        if (!alive)
+          break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned a_base = SmemAddress(sm.a[s]), b_base = SmemAddress(sm.b[s]);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const unsigned long long a_desc = OperandDescriptor(a_base + ks * 4096, 2048, 128);
+          const unsigned long long b_desc = OperandDescriptor(b_base + ks * 2 * (tile_n * 16), tile_n * 16, 128);
+          MmaSS(tmem, a_desc, b_desc, idesc, i > 0 || ks > 0);
+        }
+        MmaCommit(&sm.empty[s]); // arrives when the MMAs above have finished reading the stage
+      }
+      if (alive)
+        MmaCommit(&sm.accumulator_ready);
+      else {
+        sm.abort = 1;
+        Raise(a.bad);
+      }
+    }
+    __syncwarp();
+  } else {
+    // =============================== epilogue ===============================
+    const int o = warp * 32 + lane; // output row of this thread = tensor-memory lane
+    const float scale = HalfBitsToFloat(m.svh[blockIdx.x * kTileM + o]);
+    const bool ready = BarrierWait(&sm.accumulator_ready, 0, abort);
+    if (!ready) {
+      sm.abort = 1;
+      Raise(a.bad);
+    } else {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      unsigned short *out = a.output + blockIdx.x * kTileM + o;
+      for (int n0 = 0; n0 < tile_n; n0 += 16) {
+        float v[16];
+        TmemLoad16(tmem + (static_cast<unsigned>(warp * 32) << 16) + n0, v);
+        // output Hadamard across the 128 outputs, stages d = 1..64 in ascending order like the reference
+        // (src/cuda/expert_exl3.cuh:102-109): d = 1..16 between lanes, d = 32, 64 between warps
+#pragma unroll
+        for (int mask = 1; mask < 32; mask *= 2)
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[c], mask);
+            v[c] = (lane & mask) ? __fsub_rn(other, v[c]) : __fadd_rn(v[c], other);
+          }
+#pragma unroll
+        for (int bit = 1; bit <= 2; bit *= 2) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c)
+            sm.exchange[warp][c][lane] = v[c];
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const float other = sm.exchange[warp ^ bit][c][lane];
+            v[c] = (warp & bit) ? __fsub_rn(other, v[c]) : __fadd_rn(v[c], other);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const int n = n0 + c;
+          if (n < valid) {
+            const float y = RoundBF16(__fmul_rn(__fmul_rn(v[c], kHadamardScale), scale));
+            if (!isfinite(y))
+              Raise(a.bad);
+            out[static_cast<size_t>(sm.pairs[n]) * rows] = BF16Bits(y);
+          }
+        }
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
+  }
+}
+
+// x~ rows in expert-grouped order: row (offset of expert e) + i holds the transform of the i-th pair routed to e.
+// Parts 0/1: x~ = fp16(B(H128(x[token] * suh)))  (reference: src/cuda/expert_exl3_prefill_warp.cuh:14-57);
+// part 2: x = SwiGLU(gate[pair], up[pair]) first (expert_exl3_prefill_packed_activations.cuh:17-73).
+__global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices, int layer, int part, const int *groups, const int *counts,
+                                                          const float *input, const unsigned short *gate, const unsigned short *up,
+                                                          const unsigned short *table, __half *transformed, int tokens, int hidden,
+                                                          int inter, int *bad) {
+  __shared__ int s_offset[kExperts + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int cols = part == 2 ? inter : hidden, blocks = cols / 128, pairs = tokens * kTopK;
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < kExperts; ++e) {
+      s_offset[e] = at;
+      const int n = counts[e];
+      at += (n < 0 || n > tokens) ? 0 : n;
+    }
+    s_offset[kExperts] = at;
+  }
+  __syncthreads();
+  if (*bad)
+    return;
+  const long long item = static_cast<long long>(blockIdx.x) * 8 + warp;
+  const int row = static_cast<int>(item / blocks), h = static_cast<int>(item % blocks);
+  if (row >= pairs || row >= s_offset[kExperts])
+    return;
+  int expert = 0; // the expert whose group holds grouped row `row`
+  for (int step = 32; step; step >>= 1)
+    if (expert + step < kExperts && s_offset[expert + step] <= row)
+      expert += step;
+  const int pair = groups[expert * tokens + (row - s_offset[expert])];
+  if (pair < 0 || pair >= pairs) {
+    if (!lane)
+      Raise(bad);
+    return;
+  }
+  const Matrix *m = matrices + (static_cast<size_t>(layer) * kExperts + expert) * 3 + part;
+  const int k = h * 128 + lane * 4;
+  const uint2 sign = __ldg(reinterpret_cast<const uint2 *>(m->suh + k));
+  float src[4];
+  if (part == 2) {
+    const uint2 gb = *reinterpret_cast<const uint2 *>(gate + static_cast<size_t>(pair) * cols + k);
+    const uint2 ub = *reinterpret_cast<const uint2 *>(up + static_cast<size_t>(pair) * cols + k);
+    const unsigned short gs[4] = {static_cast<unsigned short>(gb.x & 0xffffu), static_cast<unsigned short>(gb.x >> 16),
+                                  static_cast<unsigned short>(gb.y & 0xffffu), static_cast<unsigned short>(gb.y >> 16)};
+    const unsigned short us[4] = {static_cast<unsigned short>(ub.x & 0xffffu), static_cast<unsigned short>(ub.x >> 16),
+                                  static_cast<unsigned short>(ub.y & 0xffffu), static_cast<unsigned short>(ub.y >> 16)};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float gv = FromBF16Bits(gs[j]), uv = FromBF16Bits(us[j]);
+      if (!isfinite(gv) || !isfinite(uv)) {
+        Raise(bad);
+        src[j] = 0.f;
+      } else {
+        src[j] = RoundBF16(__fmul_rn(FromBF16Bits(__ldg(table + gs[j])), uv));
+        if (!isfinite(src[j]))
+          Raise(bad);
+      }
+    }
+  } else {
+    const float4 x = *reinterpret_cast<const float4 *>(input + static_cast<size_t>(pair >> 3) * cols + k);
+    src[0] = x.x, src[1] = x.y, src[2] = x.z, src[3] = x.w;
+  }
+  float v[4] = {__fmul_rn(src[0], HalfBitsToFloat(sign.x & 0xffffu)), __fmul_rn(src[1], HalfBitsToFloat(sign.x >> 16)),
+                __fmul_rn(src[2], HalfBitsToFloat(sign.y & 0xffffu)), __fmul_rn(src[3], HalfBitsToFloat(sign.y >> 16))};
+  WarpHadamard128(v);
+  __half hv[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float r = RoundBF16(v[j]);
+    hv[j] = __float2half_rn(r);
+    if (!isfinite(r) || (__half_as_ushort(hv[j]) & 0x7c00) == 0x7c00)
+      Raise(bad);
+  }
+  uint2 packed;
+  packed.x = static_cast<unsigned>(__half_as_ushort(hv[0])) | (static_cast<unsigned>(__half_as_ushort(hv[1])) << 16);
+  packed.y = static_cast<unsigned>(__half_as_ushort(hv[2])) | (static_cast<unsigned>(__half_as_ushort(hv[3])) << 16);
+  *reinterpret_cast<uint2 *>(transformed + static_cast<size_t>(row) * cols + k) = packed;
+}
+
+template <int Rate> int LaunchGemm(const PrefillArgs &a, dim3 grid, cudaStream_t stream) {
+  const size_t smem = sizeof(PrefillSmem) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(PrefillGemmKernel<Rate>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+      return PADRA_RESOURCE_EXHAUSTED;
+    configured = true;
+  }
+  PrefillGemmKernel<Rate><<<grid, kPrefillThreads, smem, stream>>>(a);
+  return CudaStatus(cudaGetLastError());
+}
+
+} // namespace
+
+int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, const float *input,
+                              unsigned short *output, const unsigned short *gate, const unsigned short *up,
+                              const unsigned short *table, void *transformed, int tokens, int *bad, cudaStream_t stream, int rate,
+                              int hidden, int inter) {
+  if (tokens < 1 || tokens > kMaxTokensPrefill || !transformed)
+    return PADRA_INVALID_ARGUMENT;
+  const int rows = part == 2 ? hidden : inter, cols = part == 2 ? inter : hidden, pairs = tokens * kTopK;
+  const long long items = static_cast<long long>(pairs) * (cols / 128);
+  PrefillInputKernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(matrices, layer, part, groups, counts, input, gate, up, table,
+                                                                               static_cast<__half *>(transformed), tokens, hidden, inter,
+                                                                               bad);
+  if (cudaGetLastError() != cudaSuccess)
+    return PADRA_INTERNAL;
+  PrefillArgs a{};
+  a.matrices = matrices, a.layer = layer, a.part = part, a.groups = groups, a.counts = counts;
+  a.transformed = static_cast<const __half *>(transformed), a.output = output, a.tokens = tokens, a.hidden = hidden, a.inter = inter;
+  a.bad = bad;
+  const int tile_capacity = kExperts + pairs / kMaxTileN; // sum over experts of ceil(n_e / 256) never exceeds this
+  const dim3 grid(rows / kTileM, tile_capacity);
+  switch (rate) {
+  case 3:
+    return LaunchGemm<3>(a, grid, stream);
+  case 4:
+    return LaunchGemm<4>(a, grid, stream);
+  case 6:
+    return LaunchGemm<6>(a, grid, stream);
+  default:
+    return PADRA_UNSUPPORTED;
+  }
+}
+
+} // namespace padra

@@ -221,16 +221,17 @@ class ExpertKernels:
         return groups, counts, tiles, tile_count
 
     # exl3_transport_async64::Launch / exl3_packed_activations::Launch
-    def prefill_launch(self, layer, part, ids, sched, x, output_bits, gate_bits, up_bits, transformed, tokens, stream=None):
+    def prefill_launch(self, layer, part, ids, sched, x, output_bits, gate_bits, up_bits, transformed, tokens, stream=None,
+                       tensor_memory=True):
         groups, counts, tiles, tile_count = sched
         st = self.lib.padra_exl3_prefill_launch(self.t.descriptors.data_ptr(), layer, part, B.ptr(ids), B.ptr(groups),
                                                 B.ptr(counts), B.ptr(tiles), B.ptr(tile_count), B.ptr(x), B.ptr(output_bits),
                                                 B.ptr(gate_bits), B.ptr(up_bits), B.ptr(self.table), B.ptr(transformed),
-                                                tokens, B.ptr(self.bad), B.stream_handle(stream), None, 1, self.t.rate,
-                                                *self.dims)
+                                                tokens, B.ptr(self.bad), B.stream_handle(stream), None, int(tensor_memory),
+                                                self.t.rate, *self.dims)
         B.check(st, "padra_exl3_prefill_launch")
 
-    def prefill_layer(self, layer, ids, routing, normalized, x, tokens, stream=None):
+    def prefill_layer(self, layer, ids, routing, normalized, x, tokens, stream=None, tensor_memory=True):
         """gate, up, down (SwiGLU inside) and combine with residual for a prefill chunk; x updated in place."""
         dev, (hidden, inter) = self.t.device, self.dims
         pairs = tokens * TOPK
@@ -243,7 +244,7 @@ class ExpertKernels:
         gate, up, down, transformed = self._workspace[key]
         sched = self.group_and_schedule(ids, tokens, stream)
         for part, target in ((0, gate), (1, up), (2, down)):
-            self.prefill_launch(layer, part, ids, sched, normalized, target, gate, up, transformed, tokens, stream)
+            self.prefill_launch(layer, part, ids, sched, normalized, target, gate, up, transformed, tokens, stream, tensor_memory)
         self.combine_packed(x, down, routing, tokens, True, stream)
         return gate, up, down
 

@@ -41,9 +41,10 @@ def test_group_rejects_duplicate_expert(gpu):
     assert k.bad_flag() == 1
 
 
+@pytest.mark.parametrize("tensor_memory", [False, True])
 @pytest.mark.parametrize("rate", [3, 4, 6])
 @pytest.mark.parametrize("tokens", [4, 37])
-def test_prefill_layer_vs_oracle(oracle, gpu, rate, tokens):
+def test_prefill_layer_vs_oracle(oracle, gpu, rate, tokens, tensor_memory):
     hidden, inter = 256, 128
     host, table, k = make(1, hidden, inter, rate, 79, gpu)
     x, ids, w = routed_inputs(oracle, tokens, hidden, 15 + tokens)
@@ -52,13 +53,42 @@ def test_prefill_layer_vs_oracle(oracle, gpu, rate, tokens):
     dx = torch.from_numpy(x).to(gpu)
     xs = dx.clone()
     gate, up, down = k.prefill_layer(0, torch.from_numpy(ids.reshape(-1)).to(gpu), torch.from_numpy(w.reshape(-1)).to(gpu),
-                                     dx, xs, tokens)
+                                     dx, xs, tokens, tensor_memory=tensor_memory)
     torch.cuda.synchronize()
     assert k.bad_flag() == 0
     assert_close_rows(bf16_bits_to_f32(u16(gate)), cg, "prefill gate")
     assert_close_rows(bf16_bits_to_f32(u16(up)), cu, "prefill up")
     assert_close_rows(bf16_bits_to_f32(u16(down)), cd, "prefill down", chained=True)  # fed by its own gate/up
     assert_close_rows(xs.cpu().numpy(), want, "prefill layer", chained=True)
+
+
+def test_tensor_memory_gemm_large_imbalanced_chunk(oracle, gpu):
+    """600 tokens with Zipf routing: experts with more than 256 pairs (several token tiles) and with very few, both
+    prefill kernels against each other and, for a sample of pairs, against the oracle."""
+    from padra_b200.experts import bf16_values, zipf_routing
+
+    hidden, inter, tokens = 512, 384, 600
+    host, table, k = make(1, hidden, inter, 4, 211, gpu)
+    ids, w = zipf_routing(tokens, seed=3, device=gpu)
+    g = torch.Generator(device=gpu)
+    g.manual_seed(2)
+    dx = bf16_values(torch.randn((tokens, hidden), device=gpu, generator=g))
+    xa, xb = dx.clone(), dx.clone()
+    ga, ua, da = (t.clone() for t in k.prefill_layer(0, ids.reshape(-1), w.reshape(-1), dx, xa, tokens, tensor_memory=True))
+    gb, ub, db = k.prefill_layer(0, ids.reshape(-1), w.reshape(-1), dx, xb, tokens, tensor_memory=False)
+    torch.cuda.synchronize()
+    assert k.bad_flag() == 0
+    assert_close_rows(bf16_bits_to_f32(u16(ga)), bf16_bits_to_f32(u16(gb)), "gate: tensor-memory vs small-tile kernel")
+    assert_close_rows(bf16_bits_to_f32(u16(ua)), bf16_bits_to_f32(u16(ub)), "up: tensor-memory vs small-tile kernel")
+    assert_close_rows(xa.cpu().numpy(), xb.cpu().numpy(), "layer: tensor-memory vs small-tile kernel", chained=True)
+    h_ids, h_x = ids.cpu().numpy(), dx.cpu().numpy()
+    gate = bf16_bits_to_f32(u16(ga))
+    for pair in (0, 777, 4799):
+        e = int(h_ids.reshape(-1)[pair])
+        data, suh, svh = host.get(0, e, 0)
+        want, bad = oracle.linear(oracle.matrix(data, suh, svh, inter, hidden, 4), h_x[pair // 8])
+        assert not bad
+        assert_close_rows(gate[pair][None], want[None], f"gate row of pair {pair} vs oracle")
 
 
 def test_prefill_matches_decode_path(oracle, gpu):
