@@ -27,19 +27,22 @@ constexpr int kStageK = 64;   // inputs per pipeline stage (four K16 steps)
 constexpr int kTileM = 128;   // outputs per CTA
 constexpr int kMaxTileN = 256; // tokens per CTA
 constexpr int kStageABytes = kTileM * kStageK * 2;    // 16 KB
-constexpr int kStageBBytes = kMaxTileN * kStageK * 2; // 32 KB
+// B stage: eight 16-byte K pieces per row; consecutive pieces are (tile_n*16 + 16) bytes apart -- the extra 16 bytes
+// put the eight pieces of one row on eight different bank groups, so the coalesced copy (eight lanes per row) is
+// free of bank conflicts.
+constexpr int kStageBBytes = 8 * (kMaxTileN * 16 + 16) + 896; // 32 KB + padding, kept a multiple of 1 KB
 constexpr int kEpilogueWarps = 4, kProducerWarps = 8;
 constexpr int kMmaWarp = kEpilogueWarps;
 constexpr int kFirstProducerWarp = kMmaWarp + 1;
 constexpr int kPrefillThreads = (kEpilogueWarps + 1 + kProducerWarps) * 32; // 416
 constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kTmemColumns = 256;
-constexpr unsigned kWaitLimit = 1u << 24;
+constexpr unsigned long long kWaitLimitNs = 1000000000ull; // a wait that lasts a second has failed
 constexpr int kMaxTokensPrefill = 2048;
 
 struct PrefillSmem {
-  alignas(1024) unsigned char a[kStages][kStageABytes];
-  alignas(1024) unsigned char b[kStages][kStageBBytes];
+  alignas(128) unsigned char a[kStages][kStageABytes];
+  alignas(128) unsigned char b[kStages][kStageBBytes];
   alignas(16) float exchange[kEpilogueWarps][16][32]; // cross-warp Hadamard stages of one 16-token chunk
   alignas(8) unsigned long long full[kStages], empty[kStages], accumulator_ready;
   int pairs[kMaxTileN]; // (token*8+slot) of the tile's rows
@@ -67,9 +70,12 @@ __device__ __forceinline__ void BarrierArrive(unsigned long long *bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(SmemAddress(bar)) : "memory");
 }
 // Bounded wait for the phase of parity `parity`; false if it did not complete in time or the CTA is aborting.
-__device__ __forceinline__ bool BarrierWait(unsigned long long *bar, unsigned parity, const volatile int *abort) {
+// `backoff` (nanoseconds of sleep after a failed poll) keeps warps with long waits off the issue slots the producers
+// need; the MMA thread polls without sleeping.
+__device__ __forceinline__ bool BarrierWait(unsigned long long *bar, unsigned parity, const volatile int *abort, unsigned backoff) {
   const unsigned addr = SmemAddress(bar);
-  for (unsigned spins = 0; spins < kWaitLimit; ++spins) {
+  unsigned long long started = 0;
+  for (unsigned spins = 0;; ++spins) {
     unsigned done;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(done)
@@ -77,10 +83,19 @@ __device__ __forceinline__ bool BarrierWait(unsigned long long *bar, unsigned pa
                  : "memory");
     if (done)
       return true;
-    if ((spins & 1023u) == 1023u && *abort)
-      return false;
+    if ((spins & 63u) == 63u) {
+      if (*abort)
+        return false;
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (!started)
+        started = now;
+      else if (now - started > kWaitLimitNs)
+        return false;
+    }
+    if (backoff)
+      __nanosleep(backoff);
   }
-  return false;
 }
 __device__ __forceinline__ unsigned long long OperandDescriptor(unsigned smem_address, unsigned leading_bytes, unsigned stride_bytes) {
   // K-major, no swizzle: 8x8 core matrices of 128 contiguous bytes; `leading` = distance between the two 16-byte
@@ -114,17 +129,30 @@ __device__ __forceinline__ void TmemLoad16(unsigned taddr, float (&v)[16]) {
     v[i] = __uint_as_float(r[i]);
 }
 
+#ifdef PADRA_PREFILL_TRACE
+__device__ unsigned long long g_trace[8 * 8192];
+__device__ __forceinline__ unsigned long long Now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define TRACE(slot) g_trace[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (slot)] = Now()
+#else
+#define TRACE(slot)
+#endif
+
 template <int Rate>
 __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillArgs a) {
   using L = codec::Lane<Rate>;
-  extern __shared__ unsigned char raw_smem[];
-  PrefillSmem &sm = *reinterpret_cast<PrefillSmem *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~static_cast<uintptr_t>(1023));
+  extern __shared__ __align__(128) unsigned char raw_smem[];
+  PrefillSmem &sm = *reinterpret_cast<PrefillSmem *>(raw_smem); // no-swizzle operands need 16-byte alignment only
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rows = a.part == 2 ? a.hidden : a.inter, cols = a.part == 2 ? a.inter : a.hidden;
   const int pairs_total = a.tokens * kTopK;
 
   // ---- which (expert, token tile) is this CTA's; leave before touching anything if there is none ----
   if (tid == 0) {
+    TRACE(0);
     sm.abort = 0;
     sm.expert = -1;
     int tile = blockIdx.y, base = 0, invalid = *a.bad != 0;
@@ -190,6 +218,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem = sm.tmem_base;
   const volatile int *abort = &sm.abort;
+#ifdef PADRA_PREFILL_TRACE
+  if (tid == 0)
+    TRACE(1);
+  __syncwarp();
+#endif
 
   if (warp >= kFirstProducerWarp) {
     // =============================== producers ===============================
@@ -200,34 +233,46 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
     const unsigned char *lane_base = m.data + (static_cast<size_t>(kstep) * tiles_per_kstep + blockIdx.x * 8 + column) * L::kTileBytes + g * L::kBytes;
     const size_t stage_bytes = static_cast<size_t>(4) * tiles_per_kstep * L::kTileBytes;
     const __half *b_rows = a.transformed + static_cast<size_t>(sm.row_base) * cols;
-    uint32_t ahead0[Rate], ahead1[Rate]; // packed words of the next two stages
-    codec::LoadWords<Rate>(lane_base, ahead0);
-    codec::LoadWords<Rate>(lane_base + (stages > 1 ? stage_bytes : 0), ahead1);
+    constexpr int kAhead = 4; // stages of packed words in flight per lane
+    uint32_t ahead[kAhead][Rate];
+#pragma unroll
+    for (int d = 0; d < kAhead; ++d)
+      codec::LoadWords<Rate>(lane_base + static_cast<size_t>(d < stages ? d : stages - 1) * stage_bytes, ahead[d]);
+    // this thread copies K piece (ptid & 7) of rows (ptid >> 3) + 32*j
+    const int piece = ptid & 7;
+    int b_source[kMaxTileN / 32];
+#pragma unroll
+    for (int j = 0; j < kMaxTileN / 32; ++j) {
+      const int n = (ptid >> 3) + 32 * j;
+      b_source[j] = (n < valid ? n : valid - 1) * cols + piece * 8;
+    }
+    const int b_piece_bytes = tile_n * 16 + 16;
     bool alive = !*abort;
     for (int i = 0; i < stages && alive; ++i) {
       const int s = i % kStages;
       uint32_t words[Rate];
 #pragma unroll
       for (int w = 0; w < Rate; ++w) {
-        words[w] = ahead0[w];
-        ahead0[w] = ahead1[w];
+        words[w] = ahead[0][w];
+#pragma unroll
+        for (int d = 0; d + 1 < kAhead; ++d)
+          ahead[d][w] = ahead[d + 1][w];
       }
-      codec::LoadWords<Rate>(lane_base + static_cast<size_t>(i + 2 < stages ? i + 2 : stages - 1) * stage_bytes, ahead1);
+      codec::LoadWords<Rate>(lane_base + static_cast<size_t>(i + kAhead < stages ? i + kAhead : stages - 1) * stage_bytes, ahead[kAhead - 1]);
       const uint32_t previous = __shfl_sync(0xffffffffu, words[Rate - 1], (lane & 24) | ((lane + 7) & 7));
       uint32_t frag[4][4];
       codec::Decode32<Rate>(words, previous, frag);
       // the stage's buffers are free once the MMAs that read them four stages ago have completed
-      alive = BarrierWait(&sm.empty[s], ((i / kStages) & 1) ^ 1, abort);
+      alive = BarrierWait(&sm.empty[s], ((i / kStages) & 1) ^ 1, abort, 40);
       if (!alive)
         break;
-      // B: tile_n rows x 64 inputs as 16-byte pieces, piece q = (row, K piece): canonical layout [K piece][row/8][row%8]
-      unsigned char *b_stage = sm.b[s];
-      for (int q = ptid; q < tile_n * 8; q += kProducerThreads) {
-        const int n = q >> 3, piece = q & 7;
-        const __half *src = b_rows + static_cast<size_t>(n < valid ? n : valid - 1) * cols + i * kStageK + piece * 8;
-        const unsigned dst = SmemAddress(b_stage + piece * (tile_n * 16) + (n >> 3) * 128 + (n & 7) * 16);
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-      }
+      // B: tile_n rows x 64 inputs as 16-byte pieces, piece q = (row, K piece): canonical layout [K piece][row]
+      const unsigned b_target = SmemAddress(sm.b[s]) + piece * b_piece_bytes + (ptid >> 3) * 16;
+      const __half *b_stage_rows = b_rows + i * kStageK;
+#pragma unroll
+      for (int j = 0; j < kMaxTileN / 32; ++j)
+        if ((ptid >> 3) + 32 * j < tile_n)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_target + j * 512), "l"(b_stage_rows + b_source[j]) : "memory");
       asm volatile("cp.async.commit_group;" ::: "memory");
       // A: this lane's four 16-byte core-matrix rows (fragment f: K half f>>1, output group f&1)
       unsigned char *a_stage = sm.a[s];
@@ -236,12 +281,20 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
         const uint4 row = make_uint4(frag[0][f], frag[1][f], frag[2][f], frag[3][f]);
         *reinterpret_cast<uint4 *>(a_stage + (2 * kstep + (f >> 1)) * 2048 + (2 * column + (f & 1)) * 128 + g * 16) = row;
       }
-      // publish the PREVIOUS stage: its cp.async group has had a whole iteration to land
+      // publish the stage issued TWO iterations ago: its cp.async group has had two iterations to land, so three
+      // stages of activation rows are in flight per CTA and the copy latency stays off the critical path
+      asm volatile("cp.async.wait_group 2;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (i > 1 && lane == 0)
+        BarrierArrive(&sm.full[(i - 2) % kStages]);
+    }
+    if (alive) {
       asm volatile("cp.async.wait_group 1;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (i > 0 && lane == 0)
-        BarrierArrive(&sm.full[(i - 1) % kStages]);
+      if (stages > 1 && lane == 0)
+        BarrierArrive(&sm.full[(stages - 2) % kStages]);
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -255,15 +308,19 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
       bool alive = !*abort;
       for (int i = 0; i < stages && alive; ++i) {
         const int s = i % kStages;
-        alive = BarrierWait(&sm.full[s], (i / kStages) & 1, abort);
+        alive = BarrierWait(&sm.full[s], (i / kStages) & 1, abort, 0);
         if (!alive)
           break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (i == 0)
+          TRACE(2);
+        if (i == stages - 1)
+          TRACE(3);
         const unsigned a_base = SmemAddress(sm.a[s]), b_base = SmemAddress(sm.b[s]);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
           const unsigned long long a_desc = OperandDescriptor(a_base + ks * 4096, 2048, 128);
-          const unsigned long long b_desc = OperandDescriptor(b_base + ks * 2 * (tile_n * 16), tile_n * 16, 128);
+          const unsigned long long b_desc = OperandDescriptor(b_base + ks * 2 * (tile_n * 16 + 16), tile_n * 16 + 16, 128);
           MmaSS(tmem, a_desc, b_desc, idesc, i > 0 || ks > 0);
         }
         MmaCommit(&sm.empty[s]); // arrives when the MMAs above have finished reading the stage
@@ -280,12 +337,17 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
     // =============================== epilogue ===============================
     const int o = warp * 32 + lane; // output row of this thread = tensor-memory lane
     const float scale = HalfBitsToFloat(m.svh[blockIdx.x * kTileM + o]);
-    const bool ready = BarrierWait(&sm.accumulator_ready, 0, abort);
+    const bool ready = __all_sync(0xffffffffu, BarrierWait(&sm.accumulator_ready, 0, abort, 200)); // also reconverges the warp
     if (!ready) {
       sm.abort = 1;
       Raise(a.bad);
     } else {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#ifdef PADRA_PREFILL_TRACE
+      if (tid == 0)
+        TRACE(4);
+      __syncwarp();
+#endif
       unsigned short *out = a.output + blockIdx.x * kTileM + o;
       for (int n0 = 0; n0 < tile_n; n0 += 16) {
         float v[16];
@@ -327,6 +389,15 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
   __syncthreads();
+  if (tid == 0) {
+    TRACE(5);
+#ifdef PADRA_PREFILL_TRACE
+    unsigned smid;
+    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+    g_trace[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + 6] = smid;
+    g_trace[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + 7] = tile_n;
+#endif
+  }
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
@@ -340,25 +411,35 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
                                                           const float *input, const unsigned short *gate, const unsigned short *up,
                                                           const unsigned short *table, __half *transformed, int tokens, int hidden,
                                                           int inter, int *bad) {
-  __shared__ int s_offset[kExperts + 1];
+  __shared__ int s_offset[kExperts + 1], s_half;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int cols = part == 2 ? inter : hidden, blocks = cols / 128, pairs = tokens * kTopK;
-  if (threadIdx.x == 0) {
-    int at = 0;
-    for (int e = 0; e < kExperts; ++e) {
-      s_offset[e] = at;
-      const int n = counts[e];
-      at += (n < 0 || n > tokens) ? 0 : n;
+  if (threadIdx.x < kExperts) { // exclusive prefix sum of the 64 group sizes: two warp scans
+    int n = counts[threadIdx.x];
+    n = (n < 0 || n > tokens) ? 0 : n;
+    int inclusive = n;
+#pragma unroll
+    for (int d = 1; d < 32; d *= 2) {
+      const int other = __shfl_up_sync(0xffffffffu, inclusive, d);
+      if (lane >= d)
+        inclusive += other;
     }
-    s_offset[kExperts] = at;
+    if (threadIdx.x == 31)
+      s_half = inclusive;
+    asm volatile("bar.sync 1, 64;" ::: "memory");
+    const int base = warp ? s_half : 0;
+    s_offset[threadIdx.x] = base + inclusive - n;
+    if (threadIdx.x == kExperts - 1)
+      s_offset[kExperts] = base + inclusive;
   }
   __syncthreads();
   if (*bad)
     return;
-  const long long item = static_cast<long long>(blockIdx.x) * 8 + warp;
+  const long long items = static_cast<long long>(pairs) * blocks;
+  for (long long item = static_cast<long long>(blockIdx.x) * 8 + warp; item < items; item += static_cast<long long>(gridDim.x) * 8) {
   const int row = static_cast<int>(item / blocks), h = static_cast<int>(item % blocks);
-  if (row >= pairs || row >= s_offset[kExperts])
-    return;
+  if (row >= s_offset[kExperts])
+    break;
   int expert = 0; // the expert whose group holds grouped row `row`
   for (int step = 32; step; step >>= 1)
     if (expert + step < kExperts && s_offset[expert + step] <= row)
@@ -367,7 +448,7 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
   if (pair < 0 || pair >= pairs) {
     if (!lane)
       Raise(bad);
-    return;
+    continue;
   }
   const Matrix *m = matrices + (static_cast<size_t>(layer) * kExperts + expert) * 3 + part;
   const int k = h * 128 + lane * 4;
@@ -411,10 +492,11 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
   packed.x = static_cast<unsigned>(__half_as_ushort(hv[0])) | (static_cast<unsigned>(__half_as_ushort(hv[1])) << 16);
   packed.y = static_cast<unsigned>(__half_as_ushort(hv[2])) | (static_cast<unsigned>(__half_as_ushort(hv[3])) << 16);
   *reinterpret_cast<uint2 *>(transformed + static_cast<size_t>(row) * cols + k) = packed;
+  }
 }
 
 template <int Rate> int LaunchGemm(const PrefillArgs &a, dim3 grid, cudaStream_t stream) {
-  const size_t smem = sizeof(PrefillSmem) + 1024;
+  const size_t smem = sizeof(PrefillSmem);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(PrefillGemmKernel<Rate>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
@@ -427,6 +509,12 @@ template <int Rate> int LaunchGemm(const PrefillArgs &a, dim3 grid, cudaStream_t
 
 } // namespace
 
+#ifdef PADRA_PREFILL_TRACE
+extern "C" __attribute__((visibility("default"))) int padra_prefill_trace_read(void *host, size_t bytes) {
+  return cudaMemcpyFromSymbol(host, g_trace, bytes);
+}
+#endif
+
 int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, const float *input,
                               unsigned short *output, const unsigned short *gate, const unsigned short *up,
                               const unsigned short *table, void *transformed, int tokens, int *bad, cudaStream_t stream, int rate,
@@ -435,7 +523,8 @@ int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const
     return PADRA_INVALID_ARGUMENT;
   const int rows = part == 2 ? hidden : inter, cols = part == 2 ? inter : hidden, pairs = tokens * kTopK;
   const long long items = static_cast<long long>(pairs) * (cols / 128);
-  PrefillInputKernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(matrices, layer, part, groups, counts, input, gate, up, table,
+  const long long wanted = (items + 7) / 8;
+  PrefillInputKernel<<<static_cast<unsigned>(wanted < 148 * 16 ? wanted : 148 * 16), 256, 0, stream>>>(matrices, layer, part, groups, counts, input, gate, up, table,
                                                                                static_cast<__half *>(transformed), tokens, hidden, inter,
                                                                                bad);
   if (cudaGetLastError() != cudaSuccess)
