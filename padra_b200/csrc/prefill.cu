@@ -1,20 +1,27 @@
 // Prefill: the grouped per-expert projection on the 5th-generation tensor cores (tcgen05.mma, accumulators in
 // tensor memory), with the trellis decode fused into the producer side of the pipeline.
 //
-// One CTA computes a 128-output x N-token tile (N <= 256) of one expert:  D[o][n] = sum_k W[k][o] * x~[n][k].
-//   * operand A = weights.  Eight producer warps (one per 16-output tile column) read packed words, decode 32
-//     weights per lane in registers (codec.cuh) and store them as 16-byte rows of 8x8 FP16 core matrices into the
-//     canonical K-major, no-swizzle shared-memory layout: with the lane <-> (row pair, K-step) ownership of the
-//     codec the four 16-byte stores of a quarter-warp are 128 contiguous bytes.
+// A work item is a 128-output x N-token tile (N <= 256) of one expert:  D[o][n] = sum_k W[k][o] * x~[n][k].
+// The kernel is persistent: one CTA per SM walks a list of items (token tiles sorted by size, dealt out in snake
+// order so that every CTA gets a similar load; the row blocks of one token tile run at the same time on
+// neighbouring CTAs and share the tile's activation rows through L2).
+//   * operand A = weights.  Two sets of eight producer warps (one warp per 16-output tile column; the sets take
+//     alternate 64-input stages, which gives every warp two stage times to hide its load and decode latencies) read
+//     packed words several stages ahead, decode 32 weights per lane in registers (codec.cuh) and store them as
+//     16-byte rows of 8x8 FP16 core matrices into the canonical K-major, no-swizzle shared-memory layout: with the
+//     lane <-> (row pair, K-step) ownership of the codec the four 16-byte stores of a quarter-warp are 128
+//     contiguous bytes.
 //   * operand B = the expert's transformed activation rows (FP16, written in expert-grouped order by
 //     PrefillInputKernel), copied with cp.async into the same canonical layout.
-//   * one elected thread issues tcgen05.mma (M = 128, N = tile tokens rounded up to 16, K = 16), four per 64-input
-//     stage, and commits each stage back to the producers; a 4-stage ring of (16 KB A + up to 32 KB B).
-//   * four epilogue warps read the FP32 accumulators from tensor memory (one output row per thread), run the 128-point
-//     output Hadamard ACROSS the 128 outputs (five shuffle stages inside a warp, two through shared memory), apply
-//     svh, round to BF16 and scatter the rows to their (token, slot) pairs.
-// Every wait on an mbarrier is bounded: on expiry the CTA raises the sticky error flag, skips the rest of its work,
-// frees its tensor memory and leaves.
+//   * one elected thread issues tcgen05.mma (M = 128, N = tile tokens rounded up to 16, K = 16), four per stage, and
+//     commits each stage back to the producers; a 4-stage ring of (16 KB A + up to 32 KB B) that runs on across
+//     items.
+//   * the 512 tensor-memory columns hold TWO accumulators: four epilogue warps drain item i (one output row per
+//     thread: the 128-point output Hadamard ACROSS the 128 outputs, five shuffle stages inside a warp and two
+//     through shared memory, then svh, BF16 rounding and the scatter to (token, slot) rows) while the producers and
+//     the MMA thread already work on item i+1.
+// Every wait on an mbarrier is bounded in time: on expiry the CTA raises the sticky error flag, skips the rest of
+// its work, frees its tensor memory and leaves.
 #include "codec.cuh"
 #include "common.cuh"
 #include "kernels.cuh"
@@ -23,31 +30,38 @@ namespace padra {
 namespace {
 
 constexpr int kStages = 4;
-constexpr int kStageK = 64;   // inputs per pipeline stage (four K16 steps)
-constexpr int kTileM = 128;   // outputs per CTA
-constexpr int kMaxTileN = 256; // tokens per CTA
-constexpr int kStageABytes = kTileM * kStageK * 2;    // 16 KB
+constexpr int kStageK = 64;    // inputs per pipeline stage (four K16 steps)
+constexpr int kTileM = 128;    // outputs per item
+constexpr int kMaxTileN = 256; // tokens per item
+constexpr int kStageABytes = kTileM * kStageK * 2; // 16 KB
 // B stage: eight 16-byte K pieces per row; consecutive pieces are (tile_n*16 + 16) bytes apart -- the extra 16 bytes
 // put the eight pieces of one row on eight different bank groups, so the coalesced copy (eight lanes per row) is
 // free of bank conflicts.
 constexpr int kStageBBytes = 8 * (kMaxTileN * 16 + 16) + 896; // 32 KB + padding, kept a multiple of 1 KB
-constexpr int kEpilogueWarps = 4, kProducerWarps = 8;
+constexpr int kEpilogueWarps = 4, kProducerSets = 2, kWarpsPerSet = 8;
 constexpr int kMmaWarp = kEpilogueWarps;
 constexpr int kFirstProducerWarp = kMmaWarp + 1;
-constexpr int kPrefillThreads = (kEpilogueWarps + 1 + kProducerWarps) * 32; // 416
-constexpr int kProducerThreads = kProducerWarps * 32;
-constexpr int kTmemColumns = 256;
+constexpr int kPrefillThreads = (kEpilogueWarps + 1 + kProducerSets * kWarpsPerSet) * 32; // 672
+constexpr int kTmemColumns = 512;                   // two accumulators of 256 columns
+constexpr int kMaxTiles = kExperts + 64;            // sum over experts of ceil(n_e / 256) for up to 2048 tokens
+constexpr int kAhead = 3;                           // own stages of packed words in flight per producer lane
 constexpr unsigned long long kWaitLimitNs = 1000000000ull; // a wait that lasts a second has failed
 constexpr int kMaxTokensPrefill = 2048;
+
+struct TileInfo {
+  int expert, valid, row_base, begin; // begin = index of the tile's first pair inside the expert's group
+};
 
 struct PrefillSmem {
   alignas(128) unsigned char a[kStages][kStageABytes];
   alignas(128) unsigned char b[kStages][kStageBBytes];
-  alignas(16) float exchange[kEpilogueWarps][16][32]; // cross-warp Hadamard stages of one 16-token chunk
-  alignas(8) unsigned long long full[kStages], empty[kStages], accumulator_ready;
-  int pairs[kMaxTileN]; // (token*8+slot) of the tile's rows
+  alignas(16) float exchange[2][kEpilogueWarps][16][32]; // cross-warp Hadamard stages, double-buffered
+  alignas(8) unsigned long long full[kStages], empty[kStages], accumulator_ready[2], accumulator_free[2];
+  TileInfo tile[kMaxTiles], unsorted[kMaxTiles];
+  int pairs[2][kMaxTileN]; // (token*8+slot) of the rows of the item being drained / the next one
+  int scan[4];
   unsigned tmem_base;
-  int abort, expert, begin, valid, row_base;
+  int abort, tiles;
 };
 
 struct PrefillArgs {
@@ -129,17 +143,11 @@ __device__ __forceinline__ void TmemLoad16(unsigned taddr, float (&v)[16]) {
     v[i] = __uint_as_float(r[i]);
 }
 
-#ifdef PADRA_PREFILL_TRACE
-__device__ unsigned long long g_trace[8 * 8192];
-__device__ __forceinline__ unsigned long long Now() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
+// Item `sequence` of this CTA: tiles sorted by size are dealt out forwards and backwards in turn.
+__device__ __forceinline__ int ItemIndex(int sequence) {
+  const int g = gridDim.x, c = blockIdx.x;
+  return sequence * g + ((sequence & 1) ? g - 1 - c : c);
 }
-#define TRACE(slot) g_trace[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (slot)] = Now()
-#else
-#define TRACE(slot)
-#endif
 
 template <int Rate>
 __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillArgs a) {
@@ -149,65 +157,86 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rows = a.part == 2 ? a.hidden : a.inter, cols = a.part == 2 ? a.inter : a.hidden;
   const int pairs_total = a.tokens * kTopK;
+  const int row_blocks = rows / kTileM, stages = cols / kStageK;
 
-  // ---- which (expert, token tile) is this CTA's; leave before touching anything if there is none ----
+  // ---- the tile list: every CTA builds the same one ----
   if (tid == 0) {
-    TRACE(0);
-    sm.abort = 0;
-    sm.expert = -1;
-    int tile = blockIdx.y, base = 0, invalid = *a.bad != 0;
-    for (int e = 0; e < kExperts && !invalid; ++e) {
-      const int n = a.counts[e];
-      if (n < 0 || n > a.tokens || base + n > pairs_total) {
-        invalid = 1;
-        break;
-      }
-      const int tiles = (n + kMaxTileN - 1) / kMaxTileN;
-      if (tile < tiles) {
-        sm.expert = e;
-        sm.begin = tile * kMaxTileN;
-        sm.valid = n - sm.begin < kMaxTileN ? n - sm.begin : kMaxTileN;
-        sm.row_base = base + sm.begin;
-        break;
-      }
-      tile -= tiles;
-      base += n;
-    }
-    if (invalid && !*a.bad)
+    sm.abort = *a.bad != 0;
+    sm.tiles = 0;
+  }
+  __syncthreads();
+  int my_count = 0, my_tiles = 0, tile_prefix = 0, pair_prefix = 0;
+  if (tid < kExperts) {
+    my_count = a.counts[tid];
+    if (my_count < 0 || my_count > a.tokens) {
       Raise(a.bad);
-    if (sm.expert >= 0) {
-      const Matrix &m = a.matrices[(static_cast<size_t>(a.layer) * kExperts + sm.expert) * 3 + a.part];
-      if (m.format != FormatOfRate(Rate) || m.rows != rows || m.cols != cols || (cols % kStageK) || (rows % kTileM) || !m.data ||
-          !m.svh) {
+      sm.abort = 1;
+      my_count = 0;
+    }
+    my_tiles = (my_count + kMaxTileN - 1) / kMaxTileN;
+    if (my_count) {
+      const Matrix &m = a.matrices[(static_cast<size_t>(a.layer) * kExperts + tid) * 3 + a.part];
+      if (m.format != FormatOfRate(Rate) || m.rows != rows || m.cols != cols || (cols % 128) || (rows % kTileM) || !m.data || !m.svh) {
         Raise(a.bad);
-        sm.expert = -1;
+        sm.abort = 1;
       }
+    }
+    tile_prefix = my_tiles, pair_prefix = my_count; // inclusive scans inside the warp
+#pragma unroll
+    for (int d = 1; d < 32; d *= 2) {
+      const int t = __shfl_up_sync(0xffffffffu, tile_prefix, d), p = __shfl_up_sync(0xffffffffu, pair_prefix, d);
+      if (lane >= d)
+        tile_prefix += t, pair_prefix += p;
+    }
+    if (lane == 31)
+      sm.scan[2 * warp] = tile_prefix, sm.scan[2 * warp + 1] = pair_prefix;
+  }
+  __syncthreads();
+  if (tid < kExperts) {
+    if (warp == 1)
+      tile_prefix += sm.scan[0], pair_prefix += sm.scan[1];
+    if (tid == kExperts - 1) {
+      sm.tiles = tile_prefix < kMaxTiles ? tile_prefix : kMaxTiles;
+      if (pair_prefix > pairs_total) {
+        Raise(a.bad);
+        sm.abort = 1;
+      }
+    }
+    const int first_tile = tile_prefix - my_tiles, first_pair = pair_prefix - my_count;
+    for (int j = 0; j < my_tiles && first_tile + j < kMaxTiles; ++j) { // more tiles only with counts that are rejected above
+      TileInfo t;
+      t.expert = tid, t.begin = j * kMaxTileN;
+      t.valid = my_count - t.begin < kMaxTileN ? my_count - t.begin : kMaxTileN;
+      t.row_base = first_pair + t.begin;
+      sm.unsorted[first_tile + j] = t;
     }
   }
   __syncthreads();
-  if (sm.expert < 0)
-    return;
-  const int expert = sm.expert, valid = sm.valid;
-  const int tile_n = (valid + 15) & ~15; // MMA N: a multiple of 16 for M = 128
-  const Matrix m = a.matrices[(static_cast<size_t>(a.layer) * kExperts + expert) * 3 + a.part];
-  const int stages = cols / kStageK;
-
-  for (int n = tid; n < valid; n += kPrefillThreads) {
-    const int pair = a.groups[expert * a.tokens + sm.begin + n];
-    sm.pairs[n] = pair;
-    if (pair < 0 || pair >= pairs_total) {
-      Raise(a.bad);
-      sm.abort = 1;
+  const int tiles = sm.tiles;
+  if (tid < tiles) { // rank sort, largest tiles first
+    const TileInfo mine = sm.unsorted[tid];
+    int rank = 0;
+    for (int t = 0; t < tiles; ++t) {
+      const int v = sm.unsorted[t].valid;
+      rank += (v > mine.valid) || (v == mine.valid && t < tid);
     }
+    sm.tile[rank] = mine;
   }
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
-      BarrierInit(&sm.full[s], kProducerWarps);
+      BarrierInit(&sm.full[s], kWarpsPerSet);
       BarrierInit(&sm.empty[s], 1);
     }
-    BarrierInit(&sm.accumulator_ready, 1);
+    for (int b = 0; b < 2; ++b) {
+      BarrierInit(&sm.accumulator_ready[b], 1);
+      BarrierInit(&sm.accumulator_free[b], kEpilogueWarps);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  __syncthreads();
+  const int items = tiles * row_blocks;
+  if (sm.abort || ItemIndex(0) >= items)
+    return; // nothing allocated yet
   if (warp == kMmaWarp) { // one warp allocates the accumulator columns and gives the permit back
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddress(&sm.tmem_base)), "r"(kTmemColumns)
                  : "memory");
@@ -218,116 +247,141 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem = sm.tmem_base;
   const volatile int *abort = &sm.abort;
-#ifdef PADRA_PREFILL_TRACE
-  if (tid == 0)
-    TRACE(1);
-  __syncwarp();
-#endif
 
   if (warp >= kFirstProducerWarp) {
     // =============================== producers ===============================
-    const int column = warp - kFirstProducerWarp; // 16-output tile column inside the 128-output block
-    const int ptid = tid - kFirstProducerWarp * 32;
+    const int set = (warp - kFirstProducerWarp) / kWarpsPerSet;   // takes the stages i with (i & 1) == set
+    const int column = (warp - kFirstProducerWarp) % kWarpsPerSet; // 16-output tile column inside the 128-output block
+    const int ptid = tid - (kFirstProducerWarp + set * kWarpsPerSet) * 32; // 0..255 inside the set
     const int g = lane & 7, kstep = lane >> 3; // row pair, K16 step inside the stage
     const size_t tiles_per_kstep = rows / 16;
-    const unsigned char *lane_base = m.data + (static_cast<size_t>(kstep) * tiles_per_kstep + blockIdx.x * 8 + column) * L::kTileBytes + g * L::kBytes;
     const size_t stage_bytes = static_cast<size_t>(4) * tiles_per_kstep * L::kTileBytes;
-    const __half *b_rows = a.transformed + static_cast<size_t>(sm.row_base) * cols;
-    constexpr int kAhead = 4; // stages of packed words in flight per lane
-    uint32_t ahead[kAhead][Rate];
+    const int piece = ptid & 7; // this thread copies K piece `piece` of rows (ptid >> 3) + 32*j
+    // address of this lane's packed words for stage 0 of an item
+    auto lane_base_of = [&](int index) -> const unsigned char * {
+      const TileInfo t = sm.tile[index / row_blocks];
+      const unsigned char *data = a.matrices[(static_cast<size_t>(a.layer) * kExperts + t.expert) * 3 + a.part].data;
+      return data + (static_cast<size_t>(kstep) * tiles_per_kstep + (index % row_blocks) * 8 + column) * L::kTileBytes + g * L::kBytes;
+    };
+    // The look-ahead runs through the same (item, stage) sequence as the loop below, kAhead own stages in front of
+    // it, across item boundaries; the matrix address of the item after the cursor's is fetched one item early.
+    int ahead_sequence = 0, ahead_stage = set;
+    const unsigned char *ahead_base = lane_base_of(ItemIndex(0));
+    const unsigned char *ahead_next = ItemIndex(1) < items ? lane_base_of(ItemIndex(1)) : nullptr;
+    auto fetch = [&](uint32_t(&into)[Rate]) {
+      if (ahead_base)
+        codec::LoadWords<Rate>(ahead_base + static_cast<size_t>(ahead_stage) * stage_bytes, into);
+      ahead_stage += 2;
+      if (ahead_stage >= stages) {
+        ahead_stage -= stages;
+        ++ahead_sequence;
+        ahead_base = ahead_next;
+        const int following = ItemIndex(ahead_sequence + 1);
+        ahead_next = ahead_base && following < items ? lane_base_of(following) : nullptr;
+      }
+    };
+    uint32_t ahead[kAhead][Rate] = {};
 #pragma unroll
     for (int d = 0; d < kAhead; ++d)
-      codec::LoadWords<Rate>(lane_base + static_cast<size_t>(d < stages ? d : stages - 1) * stage_bytes, ahead[d]);
-    // this thread copies K piece (ptid & 7) of rows (ptid >> 3) + 32*j
-    const int piece = ptid & 7;
-    int b_source[kMaxTileN / 32];
-#pragma unroll
-    for (int j = 0; j < kMaxTileN / 32; ++j) {
-      const int n = (ptid >> 3) + 32 * j;
-      b_source[j] = (n < valid ? n : valid - 1) * cols + piece * 8;
-    }
-    const int b_piece_bytes = tile_n * 16 + 16;
-    bool alive = !*abort;
-    for (int i = 0; i < stages && alive; ++i) {
-      const int s = i % kStages;
-      uint32_t words[Rate];
-#pragma unroll
-      for (int w = 0; w < Rate; ++w) {
-        words[w] = ahead[0][w];
-#pragma unroll
-        for (int d = 0; d + 1 < kAhead; ++d)
-          ahead[d][w] = ahead[d + 1][w];
-      }
-      codec::LoadWords<Rate>(lane_base + static_cast<size_t>(i + kAhead < stages ? i + kAhead : stages - 1) * stage_bytes, ahead[kAhead - 1]);
-      const uint32_t previous = __shfl_sync(0xffffffffu, words[Rate - 1], (lane & 24) | ((lane + 7) & 7));
-      uint32_t frag[4][4];
-      codec::Decode32<Rate>(words, previous, frag);
-      // the stage's buffers are free once the MMAs that read them four stages ago have completed
-      alive = BarrierWait(&sm.empty[s], ((i / kStages) & 1) ^ 1, abort, 40);
-      if (!alive)
+      fetch(ahead[d]);
+    bool alive = true;
+    int pending_slot = -1; // stage written but not yet published
+    unsigned q = 0;        // stages this CTA has been through before the current item
+    for (int sequence = 0; alive; ++sequence, q += stages) {
+      const int index = ItemIndex(sequence);
+      if (index >= items)
         break;
-      // B: tile_n rows x 64 inputs as 16-byte pieces, piece q = (row, K piece): canonical layout [K piece][row]
-      const unsigned b_target = SmemAddress(sm.b[s]) + piece * b_piece_bytes + (ptid >> 3) * 16;
-      const __half *b_stage_rows = b_rows + i * kStageK;
+      const TileInfo t = sm.tile[index / row_blocks];
+      const int valid = t.valid, tile_n = (valid + 15) & ~15;
+      const __half *b_rows = a.transformed + static_cast<size_t>(t.row_base) * cols;
+      int b_source[kMaxTileN / 32];
 #pragma unroll
-      for (int j = 0; j < kMaxTileN / 32; ++j)
-        if ((ptid >> 3) + 32 * j < tile_n)
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_target + j * 512), "l"(b_stage_rows + b_source[j]) : "memory");
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      // A: this lane's four 16-byte core-matrix rows (fragment f: K half f>>1, output group f&1)
-      unsigned char *a_stage = sm.a[s];
-#pragma unroll
-      for (int f = 0; f < 4; ++f) {
-        const uint4 row = make_uint4(frag[0][f], frag[1][f], frag[2][f], frag[3][f]);
-        *reinterpret_cast<uint4 *>(a_stage + (2 * kstep + (f >> 1)) * 2048 + (2 * column + (f & 1)) * 128 + g * 16) = row;
+      for (int j = 0; j < kMaxTileN / 32; ++j) {
+        const int n = (ptid >> 3) + 32 * j;
+        b_source[j] = (n < valid ? n : valid - 1) * cols + piece * 8;
       }
-      // publish the stage issued TWO iterations ago: its cp.async group has had two iterations to land, so three
-      // stages of activation rows are in flight per CTA and the copy latency stays off the critical path
-      asm volatile("cp.async.wait_group 2;" ::: "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (i > 1 && lane == 0)
-        BarrierArrive(&sm.full[(i - 2) % kStages]);
-    }
-    if (alive) {
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (stages > 1 && lane == 0)
-        BarrierArrive(&sm.full[(stages - 2) % kStages]);
+      const int b_piece_bytes = tile_n * 16 + 16;
+      for (int i = set; i < stages; i += 2) {
+        const int s = (q + i) % kStages;
+        uint32_t words[Rate];
+#pragma unroll
+        for (int w = 0; w < Rate; ++w) {
+          words[w] = ahead[0][w];
+#pragma unroll
+          for (int d = 0; d + 1 < kAhead; ++d)
+            ahead[d][w] = ahead[d + 1][w];
+        }
+        fetch(ahead[kAhead - 1]);
+        const uint32_t previous = __shfl_sync(0xffffffffu, words[Rate - 1], (lane & 24) | ((lane + 7) & 7));
+        uint32_t frag[4][4];
+        codec::Decode32<Rate>(words, previous, frag);
+        // the stage's buffers are free once the MMAs that read them four stages ago have completed
+        alive = BarrierWait(&sm.empty[s], (((q + i) / kStages) & 1) ^ 1, abort, 32);
+        if (!alive)
+          break;
+        // B: tile_n rows x 64 inputs as 16-byte pieces: canonical layout [K piece][row]
+        const unsigned b_target = SmemAddress(sm.b[s]) + piece * b_piece_bytes + (ptid >> 3) * 16;
+        const __half *b_stage_rows = b_rows + i * kStageK;
+#pragma unroll
+        for (int j = 0; j < kMaxTileN / 32; ++j)
+          if ((ptid >> 3) + 32 * j < tile_n)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_target + j * 512), "l"(b_stage_rows + b_source[j]) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        // A: this lane's four 16-byte core-matrix rows (fragment f: K half f>>1, output group f&1)
+        unsigned char *a_stage = sm.a[s];
+#pragma unroll
+        for (int f = 0; f < 4; ++f) {
+          const uint4 row = make_uint4(frag[0][f], frag[1][f], frag[2][f], frag[3][f]);
+          *reinterpret_cast<uint4 *>(a_stage + (2 * kstep + (f >> 1)) * 2048 + (2 * column + (f & 1)) * 128 + g * 16) = row;
+        }
+        // publish this set's PREVIOUS stage: its copy group has had a whole stage time to land
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (pending_slot >= 0 && lane == 0)
+          BarrierArrive(&sm.full[pending_slot]);
+        pending_slot = s;
+      }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
-    if (alive && lane == 0)
-      BarrierArrive(&sm.full[(stages - 1) % kStages]);
+    if (alive && pending_slot >= 0 && lane == 0)
+      BarrierArrive(&sm.full[pending_slot]);
   } else if (warp == kMmaWarp) {
     // =============================== MMA issue ===============================
     if (lane == 0) {
-      const unsigned idesc = InstructionDescriptor(tile_n);
-      bool alive = !*abort;
-      for (int i = 0; i < stages && alive; ++i) {
-        const int s = i % kStages;
-        alive = BarrierWait(&sm.full[s], (i / kStages) & 1, abort, 0);
-        if (!alive)
+      bool alive = true;
+      unsigned q = 0;
+      for (int sequence = 0; alive; ++sequence, q += stages) {
+        const int index = ItemIndex(sequence);
+        if (index >= items)
           break;
+        const int valid = sm.tile[index / row_blocks].valid, tile_n = (valid + 15) & ~15;
+        const unsigned idesc = InstructionDescriptor(tile_n);
+        const int buffer = sequence & 1;
+        // the accumulator must have been drained by the epilogue of the item two before
+        alive = BarrierWait(&sm.accumulator_free[buffer], ((sequence >> 1) & 1) ^ 1, abort, 0);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (i == 0)
-          TRACE(2);
-        if (i == stages - 1)
-          TRACE(3);
-        const unsigned a_base = SmemAddress(sm.a[s]), b_base = SmemAddress(sm.b[s]);
+        for (int i = 0; i < stages && alive; ++i) {
+          const int s = (q + i) % kStages;
+          alive = BarrierWait(&sm.full[s], ((q + i) / kStages) & 1, abort, 0);
+          if (!alive)
+            break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const unsigned a_base = SmemAddress(sm.a[s]), b_base = SmemAddress(sm.b[s]);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const unsigned long long a_desc = OperandDescriptor(a_base + ks * 4096, 2048, 128);
-          const unsigned long long b_desc = OperandDescriptor(b_base + ks * 2 * (tile_n * 16 + 16), tile_n * 16 + 16, 128);
-          MmaSS(tmem, a_desc, b_desc, idesc, i > 0 || ks > 0);
+          for (int ks = 0; ks < 4; ++ks) {
+            const unsigned long long a_desc = OperandDescriptor(a_base + ks * 4096, 2048, 128);
+            const unsigned long long b_desc = OperandDescriptor(b_base + ks * 2 * (tile_n * 16 + 16), tile_n * 16 + 16, 128);
+            MmaSS(tmem + buffer * kMaxTileN, a_desc, b_desc, idesc, i > 0 || ks > 0);
+          }
+          MmaCommit(&sm.empty[s]); // arrives when the MMAs above have finished reading the stage
         }
-        MmaCommit(&sm.empty[s]); // arrives when the MMAs above have finished reading the stage
+        if (alive)
+          MmaCommit(&sm.accumulator_ready[buffer]);
       }
-      if (alive)
-        MmaCommit(&sm.accumulator_ready);
-      else {
+      if (!alive) {
         sm.abort = 1;
         Raise(a.bad);
       }
@@ -336,24 +390,44 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
   } else {
     // =============================== epilogue ===============================
     const int o = warp * 32 + lane; // output row of this thread = tensor-memory lane
-    const float scale = HalfBitsToFloat(m.svh[blockIdx.x * kTileM + o]);
-    const bool ready = __all_sync(0xffffffffu, BarrierWait(&sm.accumulator_ready, 0, abort, 200)); // also reconverges the warp
-    if (!ready) {
-      sm.abort = 1;
-      Raise(a.bad);
-    } else {
+    int flip = 0;                   // exchange buffer in turn
+    for (int sequence = 0;; ++sequence) {
+      const int index = ItemIndex(sequence);
+      if (index >= items)
+        break;
+      const TileInfo t = sm.tile[index / row_blocks];
+      const int block = index % row_blocks, valid = t.valid, tile_n = (valid + 15) & ~15, buffer = sequence & 1;
+      const Matrix &m = a.matrices[(static_cast<size_t>(a.layer) * kExperts + t.expert) * 3 + a.part];
+      const float scale = HalfBitsToFloat(m.svh[block * kTileM + o]);
+      int *pairs = sm.pairs[buffer];
+      for (int n = o; n < valid; n += kEpilogueWarps * 32) {
+        const int pair = a.groups[t.expert * a.tokens + t.begin + n];
+        pairs[n] = pair;
+        if (pair < 0 || pair >= pairs_total) {
+          Raise(a.bad);
+          sm.abort = 1;
+        }
+      }
+      unsigned failed = 0, any_failed;
+      if (!BarrierWait(&sm.accumulator_ready[buffer], (sequence >> 1) & 1, abort, 200)) {
+        sm.abort = 1;
+        Raise(a.bad);
+        failed = 1;
+      }
+      // pairs[] complete, and ONE decision for all four warps (they meet at barriers inside the loop below)
+      asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                   : "=r"(any_failed)
+                   : "r"(failed | static_cast<unsigned>(*abort))
+                   : "memory");
+      if (any_failed)
+        break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#ifdef PADRA_PREFILL_TRACE
-      if (tid == 0)
-        TRACE(4);
-      __syncwarp();
-#endif
-      unsigned short *out = a.output + blockIdx.x * kTileM + o;
+      unsigned short *out = a.output + block * kTileM + o;
       for (int n0 = 0; n0 < tile_n; n0 += 16) {
         float v[16];
-        TmemLoad16(tmem + (static_cast<unsigned>(warp * 32) << 16) + n0, v);
+        TmemLoad16(tmem + buffer * kMaxTileN + (static_cast<unsigned>(warp * 32) << 16) + n0, v);
         // output Hadamard across the 128 outputs, stages d = 1..64 in ascending order like the reference
-        // (src/cuda/expert_exl3.cuh:102-109): d = 1..16 between lanes, d = 32, 64 between warps
+        // (src/cuda/expert_exl3.cuh:102-109): d = 1..16 between lanes, d = 32 and 64 between warps
 #pragma unroll
         for (int mask = 1; mask < 32; mask *= 2)
 #pragma unroll
@@ -361,18 +435,19 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
             const float other = __shfl_xor_sync(0xffffffffu, v[c], mask);
             v[c] = (lane & mask) ? __fsub_rn(other, v[c]) : __fadd_rn(v[c], other);
           }
+        float(*mine)[16][32] = sm.exchange[flip];
+        flip ^= 1;
 #pragma unroll
-        for (int bit = 1; bit <= 2; bit *= 2) {
+        for (int c = 0; c < 16; ++c)
+          mine[warp][c][lane] = v[c];
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        // each thread redoes its partner's d = 32 butterfly instead of waiting for it: same operations, same order
 #pragma unroll
-          for (int c = 0; c < 16; ++c)
-            sm.exchange[warp][c][lane] = v[c];
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-#pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const float other = sm.exchange[warp ^ bit][c][lane];
-            v[c] = (warp & bit) ? __fsub_rn(other, v[c]) : __fadd_rn(v[c], other);
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
+        for (int c = 0; c < 16; ++c) {
+          const float v1 = mine[warp ^ 1][c][lane], v2 = mine[warp ^ 2][c][lane], v3 = mine[warp ^ 3][c][lane];
+          const float own = (warp & 1) ? __fsub_rn(v1, v[c]) : __fadd_rn(v[c], v1);
+          const float far = (warp & 1) ? __fsub_rn(v3, v2) : __fadd_rn(v2, v3);
+          v[c] = (warp & 2) ? __fsub_rn(far, own) : __fadd_rn(own, far);
         }
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
@@ -381,23 +456,19 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
             const float y = RoundBF16(__fmul_rn(__fmul_rn(v[c], kHadamardScale), scale));
             if (!isfinite(y))
               Raise(a.bad);
-            out[static_cast<size_t>(sm.pairs[n]) * rows] = BF16Bits(y);
+            out[static_cast<size_t>(pairs[n]) * rows] = BF16Bits(y);
           }
         }
       }
+      // hand the accumulator back to the MMA thread
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0)
+        BarrierArrive(&sm.accumulator_free[buffer]);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
   __syncthreads();
-  if (tid == 0) {
-    TRACE(5);
-#ifdef PADRA_PREFILL_TRACE
-    unsigned smid;
-    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
-    g_trace[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + 6] = smid;
-    g_trace[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + 7] = tile_n;
-#endif
-  }
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
@@ -509,12 +580,6 @@ template <int Rate> int LaunchGemm(const PrefillArgs &a, dim3 grid, cudaStream_t
 
 } // namespace
 
-#ifdef PADRA_PREFILL_TRACE
-extern "C" __attribute__((visibility("default"))) int padra_prefill_trace_read(void *host, size_t bytes) {
-  return cudaMemcpyFromSymbol(host, g_trace, bytes);
-}
-#endif
-
 int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, const float *input,
                               unsigned short *output, const unsigned short *gate, const unsigned short *up,
                               const unsigned short *table, void *transformed, int tokens, int *bad, cudaStream_t stream, int rate,
@@ -533,8 +598,10 @@ int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const
   a.matrices = matrices, a.layer = layer, a.part = part, a.groups = groups, a.counts = counts;
   a.transformed = static_cast<const __half *>(transformed), a.output = output, a.tokens = tokens, a.hidden = hidden, a.inter = inter;
   a.bad = bad;
-  const int tile_capacity = kExperts + pairs / kMaxTileN; // sum over experts of ceil(n_e / 256) never exceeds this
-  const dim3 grid(rows / kTileM, tile_capacity);
+  int device = 0, sms = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 1)
+    return PADRA_INTERNAL;
+  const dim3 grid(sms); // persistent: one CTA per SM
   switch (rate) {
   case 3:
     return LaunchGemm<3>(a, grid, stream);
