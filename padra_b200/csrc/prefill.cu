@@ -1,25 +1,27 @@
 // Prefill: the grouped per-expert projection on the 5th-generation tensor cores (tcgen05.mma, accumulators in
 // tensor memory), with the trellis decode fused into the producer side of the pipeline.
 //
-// A work item is a 128-output x N-token tile (N <= 256) of one expert:  D[o][n] = sum_k W[k][o] * x~[n][k].
+// A work item is a 128-output x N-token tile (N <= 256) of one expert:  D[n][o] = sum_k x~[n][k] * W[k][o].
 // The kernel is persistent: one CTA per SM walks a list of items (token tiles sorted by size, dealt out in snake
 // order so that every CTA gets a similar load; the row blocks of one token tile run at the same time on
 // neighbouring CTAs and share the tile's activation rows through L2).
-//   * operand A = weights.  Two sets of eight producer warps (one warp per 16-output tile column; the sets take
-//     alternate 64-input stages, which gives every warp two stage times to hide its load and decode latencies) read
-//     packed words several stages ahead, decode 32 weights per lane in registers (codec.cuh) and store them as
-//     16-byte rows of 8x8 FP16 core matrices into the canonical K-major, no-swizzle shared-memory layout: with the
-//     lane <-> (row pair, K-step) ownership of the codec the four 16-byte stores of a quarter-warp are 128
-//     contiguous bytes.
-//   * operand B = the expert's transformed activation rows (FP16, written in expert-grouped order by
-//     PrefillInputKernel), copied with cp.async into the same canonical layout.
-//   * one elected thread issues tcgen05.mma (M = 128, N = tile tokens rounded up to 16, K = 16), four per stage, and
-//     commits each stage back to the producers; a 4-stage ring of (16 KB A + up to 32 KB B) that runs on across
-//     items.
-//   * the 512 tensor-memory columns hold TWO accumulators: four epilogue warps drain item i (one output row per
-//     thread: the 128-point output Hadamard ACROSS the 128 outputs, five shuffle stages inside a warp and two
-//     through shared memory, then svh, BF16 rounding and the scatter to (token, slot) rows) while the producers and
-//     the MMA thread already work on item i+1.
+//   * the weights are the MMA's N side.  Two sets of eight producer warps (one warp per 16-output tile column; the
+//     sets take alternate 64-input stages, which gives every warp two stage times to hide its load and decode
+//     latencies) read packed words several stages ahead, decode 32 weights per lane in registers (codec.cuh) and
+//     store them as 16-byte rows of 8x8 FP16 core matrices into the canonical K-major, no-swizzle shared-memory
+//     layout: with the lane <-> (row pair, K-step) ownership of the codec the four 16-byte stores of a quarter-warp
+//     are 128 contiguous bytes.
+//   * the tokens are the M side: the expert's transformed activation rows (FP16, written in expert-grouped order by
+//     PrefillInputKernel), copied with cp.async into the same canonical layout, one or two tiles of 128 rows.
+//   * one elected thread issues tcgen05.mma (M = 128 tokens, N = 128 outputs, K = 16), four per stage and token
+//     tile, and commits each stage back to the producers; a 4-stage ring of (16 KB weights + up to 32 KB
+//     activations) that runs on across items.
+//   * a thread of the four epilogue warps owns one TOKEN row of the accumulator, so the 128-point output Hadamard
+//     runs over the columns it reads from tensor memory: stages d = 1..16 in registers on 32-column pieces (written
+//     back in place), stages d = 32, 64 between the four pieces, then svh, BF16 rounding and 16-byte stores to the
+//     row of the (token, slot) pair.  No shuffles, no barriers.
+//   * the 512 tensor-memory columns hold TWO accumulators of two token tiles each: the epilogue drains item i while
+//     the producers and the MMA thread already work on item i+1.
 // Every wait on an mbarrier is bounded in time: on expiry the CTA raises the sticky error flag, skips the rest of
 // its work, frees its tensor memory and leaves.
 #include "codec.cuh"
@@ -31,7 +33,7 @@ namespace {
 
 constexpr int kStages = 4;
 constexpr int kStageK = 64;    // inputs per pipeline stage (four K16 steps)
-constexpr int kTileM = 128;    // outputs per item
+constexpr int kTileM = 128;    // outputs per item (the MMA's N), and token rows per MMA (its M)
 constexpr int kMaxTileN = 256; // tokens per item
 constexpr int kStageABytes = kTileM * kStageK * 2; // 16 KB
 // B stage: eight 16-byte K pieces per row; consecutive pieces are (tile_n*16 + 16) bytes apart -- the extra 16 bytes
@@ -55,7 +57,7 @@ struct TileInfo {
 struct PrefillSmem {
   alignas(128) unsigned char a[kStages][kStageABytes];
   alignas(128) unsigned char b[kStages][kStageBBytes];
-  alignas(16) float exchange[2][kEpilogueWarps][16][32]; // cross-warp Hadamard stages, double-buffered
+  alignas(16) float scale[2][kTileM]; // svh of the item being drained / the next one
   alignas(8) unsigned long long full[kStages], empty[kStages], accumulator_ready[2], accumulator_free[2];
   TileInfo tile[kMaxTiles], unsorted[kMaxTiles];
   int pairs[2][kMaxTileN]; // (token*8+slot) of the rows of the item being drained / the next one
@@ -118,9 +120,9 @@ __device__ __forceinline__ unsigned long long OperandDescriptor(unsigned smem_ad
   return static_cast<unsigned long long>((smem_address & 0x3ffffu) >> 4) | (static_cast<unsigned long long>(leading_bytes >> 4) << 16) |
          (static_cast<unsigned long long>(stride_bytes >> 4) << 32) | (1ull << 46);
 }
-__device__ __forceinline__ unsigned InstructionDescriptor(int n) {
+__device__ __forceinline__ unsigned InstructionDescriptor() {
   // kind::f16: FP32 accumulate (bits 4-5 = 1), A and B FP16 (0), both K-major (0), N>>3 at [17,23), M>>4 at [24,29)
-  return (1u << 4) | (static_cast<unsigned>(n >> 3) << 17) | (static_cast<unsigned>(kTileM >> 4) << 24);
+  return (1u << 4) | (static_cast<unsigned>(kTileM >> 3) << 17) | (static_cast<unsigned>(128 >> 4) << 24);
 }
 __device__ __forceinline__ void MmaSS(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc, unsigned idesc, bool accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
@@ -130,18 +132,65 @@ __device__ __forceinline__ void MmaSS(unsigned tmem_d, unsigned long long a_desc
 __device__ __forceinline__ void MmaCommit(unsigned long long *bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(SmemAddress(bar)) : "memory");
 }
-__device__ __forceinline__ void TmemLoad16(unsigned taddr, float (&v)[16]) {
-  unsigned r[16];
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+// 32 lanes x 32 columns: thread i of the warp gets columns [column, column+32) of its own lane
+__device__ __forceinline__ void TmemLoad32(unsigned taddr, float (&v)[32]) {
+  unsigned r[32];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-                 "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                 "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+                 "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                : "r"(taddr)
                : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-  for (int i = 0; i < 16; ++i)
+  for (int i = 0; i < 32; ++i)
     v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void TmemStore32(unsigned taddr, const float (&v)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+               "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+               "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+               "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+               "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+               "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+               "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+               "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+               "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+               "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+               : "memory");
+}
+// four pieces x 8 columns: v[q][j] = column 32*q + j of the thread's lane, counted from `taddr`
+__device__ __forceinline__ void TmemLoad4x8(unsigned taddr, float (&v)[4][8]) {
+  unsigned r[4][8];
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[q][0]), "=r"(r[q][1]), "=r"(r[q][2]), "=r"(r[q][3]), "=r"(r[q][4]), "=r"(r[q][5]), "=r"(r[q][6]), "=r"(r[q][7])
+                 : "r"(taddr + 32 * q)
+                 : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      v[q][j] = __uint_as_float(r[q][j]);
+}
+
+#ifdef PADRA_PREFILL_TRACE
+__device__ unsigned long long g_trace[8 * 8192];
+__device__ __forceinline__ unsigned long long Now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define TRACE(index, slot) g_trace[(index) * 8 + (slot)] = Now()
+#define TRACE_VALUE(index, slot, value) g_trace[(index) * 8 + (slot)] = (value)
+#else
+#define TRACE(index, slot)
+#define TRACE_VALUE(index, slot, value)
+#endif
 
 // Item `sequence` of this CTA: tiles sorted by size are dealt out forwards and backwards in turn.
 __device__ __forceinline__ int ItemIndex(int sequence) {
@@ -358,24 +407,36 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
         if (index >= items)
           break;
         const int valid = sm.tile[index / row_blocks].valid, tile_n = (valid + 15) & ~15;
-        const unsigned idesc = InstructionDescriptor(tile_n);
+        const int token_tiles = (valid + 127) / 128;
+        const unsigned idesc = InstructionDescriptor();
+        const unsigned piece_bytes = tile_n * 16 + 16;
         const int buffer = sequence & 1;
         // the accumulator must have been drained by the epilogue of the item two before
         alive = BarrierWait(&sm.accumulator_free[buffer], ((sequence >> 1) & 1) ^ 1, abort, 0);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        TRACE(index, 0);
+        TRACE_VALUE(index, 6, blockIdx.x);
+        TRACE_VALUE(index, 7, tile_n);
         for (int i = 0; i < stages && alive; ++i) {
           const int s = (q + i) % kStages;
           alive = BarrierWait(&sm.full[s], ((q + i) / kStages) & 1, abort, 0);
           if (!alive)
             break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const unsigned a_base = SmemAddress(sm.a[s]), b_base = SmemAddress(sm.b[s]);
+          if (i == 0)
+            TRACE(index, 1);
+          if (i == stages - 1)
+            TRACE(index, 2);
+          const unsigned w_base = SmemAddress(sm.a[s]), x_base = SmemAddress(sm.b[s]);
+          // rows of the last token tile past tile_n hold whatever the ring held before: they only reach accumulator
+          // rows that nobody reads
+          for (int mt = 0; mt < token_tiles; ++mt)
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const unsigned long long a_desc = OperandDescriptor(a_base + ks * 4096, 2048, 128);
-            const unsigned long long b_desc = OperandDescriptor(b_base + ks * 2 * (tile_n * 16 + 16), tile_n * 16 + 16, 128);
-            MmaSS(tmem + buffer * kMaxTileN, a_desc, b_desc, idesc, i > 0 || ks > 0);
-          }
+            for (int ks = 0; ks < 4; ++ks) {
+              const unsigned long long x_desc = OperandDescriptor(x_base + ks * 2 * piece_bytes + mt * 2048, piece_bytes, 128);
+              const unsigned long long w_desc = OperandDescriptor(w_base + ks * 4096, 2048, 128);
+              MmaSS(tmem + buffer * kMaxTileN + mt * kTileM, x_desc, w_desc, idesc, i > 0 || ks > 0);
+            }
           MmaCommit(&sm.empty[s]); // arrives when the MMAs above have finished reading the stage
         }
         if (alive)
@@ -389,16 +450,15 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
     __syncwarp();
   } else {
     // =============================== epilogue ===============================
-    const int o = warp * 32 + lane; // output row of this thread = tensor-memory lane
-    int flip = 0;                   // exchange buffer in turn
+    const int o = warp * 32 + lane; // tensor-memory lane of this thread = token row inside a token tile
     for (int sequence = 0;; ++sequence) {
       const int index = ItemIndex(sequence);
       if (index >= items)
         break;
       const TileInfo t = sm.tile[index / row_blocks];
-      const int block = index % row_blocks, valid = t.valid, tile_n = (valid + 15) & ~15, buffer = sequence & 1;
+      const int block = index % row_blocks, valid = t.valid, buffer = sequence & 1;
       const Matrix &m = a.matrices[(static_cast<size_t>(a.layer) * kExperts + t.expert) * 3 + a.part];
-      const float scale = HalfBitsToFloat(m.svh[block * kTileM + o]);
+      sm.scale[buffer][o] = HalfBitsToFloat(m.svh[block * kTileM + o]);
       int *pairs = sm.pairs[buffer];
       for (int n = o; n < valid; n += kEpilogueWarps * 32) {
         const int pair = a.groups[t.expert * a.tokens + t.begin + n];
@@ -414,49 +474,68 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
         Raise(a.bad);
         failed = 1;
       }
-      // pairs[] complete, and ONE decision for all four warps (they meet at barriers inside the loop below)
+      // pairs[] and scale[] complete, and ONE decision for all four warps
       asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                    : "=r"(any_failed)
                    : "r"(failed | static_cast<unsigned>(*abort))
                    : "memory");
       if (any_failed)
         break;
+#ifdef PADRA_PREFILL_TRACE
+      if (tid == 0)
+        TRACE(index, 3);
+      __syncwarp();
+#endif
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      unsigned short *out = a.output + block * kTileM + o;
-      for (int n0 = 0; n0 < tile_n; n0 += 16) {
-        float v[16];
-        TmemLoad16(tmem + buffer * kMaxTileN + (static_cast<unsigned>(warp * 32) << 16) + n0, v);
-        // output Hadamard across the 128 outputs, stages d = 1..64 in ascending order like the reference
-        // (src/cuda/expert_exl3.cuh:102-109): d = 1..16 between lanes, d = 32 and 64 between warps
+      const float *scale = sm.scale[buffer];
+      for (int mt = 0; mt * 128 + warp * 32 < valid; ++mt) { // warp-uniform: token tiles that hold rows of this warp
+        const int n = mt * 128 + o;
+        const unsigned lane_address = tmem + buffer * kMaxTileN + mt * kTileM + (static_cast<unsigned>(warp * 32) << 16);
+        // output Hadamard over the 128 outputs of the row, stages in ascending order like the reference
+        // (src/cuda/expert_exl3.cuh:102-109).  Stages d = 1..16 stay inside a 32-column piece:
+#pragma unroll 1
+        for (int piece = 0; piece < 4; ++piece) {
+          float v[32];
+          TmemLoad32(lane_address + 32 * piece, v);
 #pragma unroll
-        for (int mask = 1; mask < 32; mask *= 2)
+          for (int d = 1; d < 32; d *= 2)
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const float other = __shfl_xor_sync(0xffffffffu, v[c], mask);
-            v[c] = (lane & mask) ? __fsub_rn(other, v[c]) : __fadd_rn(v[c], other);
-          }
-        float(*mine)[16][32] = sm.exchange[flip];
-        flip ^= 1;
-#pragma unroll
-        for (int c = 0; c < 16; ++c)
-          mine[warp][c][lane] = v[c];
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        // each thread redoes its partner's d = 32 butterfly instead of waiting for it: same operations, same order
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const float v1 = mine[warp ^ 1][c][lane], v2 = mine[warp ^ 2][c][lane], v3 = mine[warp ^ 3][c][lane];
-          const float own = (warp & 1) ? __fsub_rn(v1, v[c]) : __fadd_rn(v[c], v1);
-          const float far = (warp & 1) ? __fsub_rn(v3, v2) : __fadd_rn(v2, v3);
-          v[c] = (warp & 2) ? __fsub_rn(far, own) : __fadd_rn(own, far);
+            for (int c = 0; c < 32; ++c)
+              if (!(c & d)) {
+                const float lower = v[c], upper = v[c + d];
+                v[c] = __fadd_rn(lower, upper);
+                v[c + d] = __fsub_rn(lower, upper);
+              }
+          TmemStore32(lane_address + 32 * piece, v);
         }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        // stages d = 32 and 64 combine the four pieces column by column
+        unsigned short *out = a.output + (n < valid ? static_cast<size_t>(pairs[n]) : 0) * rows + block * kTileM;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 32; c0 += 8) {
+          float v[4][8];
+          TmemLoad4x8(lane_address + c0, v);
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const int n = n0 + c;
+          for (int j = 0; j < 8; ++j) {
+            const float a0 = __fadd_rn(v[0][j], v[1][j]), a1 = __fsub_rn(v[0][j], v[1][j]);
+            const float a2 = __fadd_rn(v[2][j], v[3][j]), a3 = __fsub_rn(v[2][j], v[3][j]);
+            v[0][j] = __fadd_rn(a0, a2), v[2][j] = __fsub_rn(a0, a2);
+            v[1][j] = __fadd_rn(a1, a3), v[3][j] = __fsub_rn(a1, a3);
+          }
           if (n < valid) {
-            const float y = RoundBF16(__fmul_rn(__fmul_rn(v[c], kHadamardScale), scale));
-            if (!isfinite(y))
-              Raise(a.bad);
-            out[static_cast<size_t>(pairs[n]) * rows] = BF16Bits(y);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              unsigned packed[4];
+#pragma unroll
+              for (int j = 0; j < 8; j += 2) {
+                const float y0 = RoundBF16(__fmul_rn(__fmul_rn(v[q][j], kHadamardScale), scale[32 * q + c0 + j]));
+                const float y1 = RoundBF16(__fmul_rn(__fmul_rn(v[q][j + 1], kHadamardScale), scale[32 * q + c0 + j + 1]));
+                if (!isfinite(y0) || !isfinite(y1))
+                  Raise(a.bad);
+                packed[j >> 1] = static_cast<unsigned>(BF16Bits(y0)) | (static_cast<unsigned>(BF16Bits(y1)) << 16);
+              }
+              *reinterpret_cast<uint4 *>(out + 32 * q + c0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
           }
         }
       }
@@ -465,6 +544,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
       __syncwarp();
       if (lane == 0)
         BarrierArrive(&sm.accumulator_free[buffer]);
+#ifdef PADRA_PREFILL_TRACE
+      if (tid == 0)
+        TRACE(index, 4);
+      __syncwarp();
+#endif
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
@@ -506,11 +590,8 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
   __syncthreads();
   if (*bad)
     return;
-  const long long items = static_cast<long long>(pairs) * blocks;
-  for (long long item = static_cast<long long>(blockIdx.x) * 8 + warp; item < items; item += static_cast<long long>(gridDim.x) * 8) {
-  const int row = static_cast<int>(item / blocks), h = static_cast<int>(item % blocks);
-  if (row >= s_offset[kExperts])
-    break;
+  // one warp per grouped row: the row's expert, pair and sidecar address are looked up once for all its blocks
+  for (int row = blockIdx.x * 8 + warp; row < s_offset[kExperts]; row += gridDim.x * 8) {
   int expert = 0; // the expert whose group holds grouped row `row`
   for (int step = 32; step; step >>= 1)
     if (expert + step < kExperts && s_offset[expert + step] <= row)
@@ -521,9 +602,11 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
       Raise(bad);
     continue;
   }
-  const Matrix *m = matrices + (static_cast<size_t>(layer) * kExperts + expert) * 3 + part;
+  const uint16_t *suh = matrices[(static_cast<size_t>(layer) * kExperts + expert) * 3 + part].suh;
+#pragma unroll 4
+  for (int h = 0; h < blocks; ++h) {
   const int k = h * 128 + lane * 4;
-  const uint2 sign = __ldg(reinterpret_cast<const uint2 *>(m->suh + k));
+  const uint2 sign = __ldg(reinterpret_cast<const uint2 *>(suh + k));
   float src[4];
   if (part == 2) {
     const uint2 gb = *reinterpret_cast<const uint2 *>(gate + static_cast<size_t>(pair) * cols + k);
@@ -564,6 +647,7 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
   packed.y = static_cast<unsigned>(__half_as_ushort(hv[2])) | (static_cast<unsigned>(__half_as_ushort(hv[3])) << 16);
   *reinterpret_cast<uint2 *>(transformed + static_cast<size_t>(row) * cols + k) = packed;
   }
+  }
 }
 
 template <int Rate> int LaunchGemm(const PrefillArgs &a, dim3 grid, cudaStream_t stream) {
@@ -580,6 +664,12 @@ template <int Rate> int LaunchGemm(const PrefillArgs &a, dim3 grid, cudaStream_t
 
 } // namespace
 
+#ifdef PADRA_PREFILL_TRACE
+extern "C" __attribute__((visibility("default"))) int padra_prefill_trace_read(void *host, size_t bytes) {
+  return cudaMemcpyFromSymbol(host, g_trace, bytes);
+}
+#endif
+
 int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, const float *input,
                               unsigned short *output, const unsigned short *gate, const unsigned short *up,
                               const unsigned short *table, void *transformed, int tokens, int *bad, cudaStream_t stream, int rate,
@@ -587,9 +677,9 @@ int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const
   if (tokens < 1 || tokens > kMaxTokensPrefill || !transformed)
     return PADRA_INVALID_ARGUMENT;
   const int rows = part == 2 ? hidden : inter, cols = part == 2 ? inter : hidden, pairs = tokens * kTopK;
-  const long long items = static_cast<long long>(pairs) * (cols / 128);
-  const long long wanted = (items + 7) / 8;
-  PrefillInputKernel<<<static_cast<unsigned>(wanted < 148 * 16 ? wanted : 148 * 16), 256, 0, stream>>>(matrices, layer, part, groups, counts, input, gate, up, table,
+  if (reinterpret_cast<uintptr_t>(output) % 16 || reinterpret_cast<uintptr_t>(transformed) % 16)
+    return PADRA_INVALID_ARGUMENT;
+  PrefillInputKernel<<<(pairs + 7) / 8, 256, 0, stream>>>(matrices, layer, part, groups, counts, input, gate, up, table,
                                                                                static_cast<__half *>(transformed), tokens, hidden, inter,
                                                                                bad);
   if (cudaGetLastError() != cudaSuccess)
