@@ -35,9 +35,9 @@ sys.path.insert(0, str(ROOT))
 
 HIDDEN, INTER, EXPERTS, TOPK, RATE, LAYERS, TOKENS = 2048, 1024, 64, 8, 4, 28, 1
 METRIC = "exl3_k4_moe_layer_decode_hbm_gbs"
-# dram__bytes_read.sum + dram__bytes_write.sum of one layer-kernel launch from the ncu capture summarised under
-# profiles/ (None until a capture of the current kernel exists)
-TRAFFIC_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate+up SplitProjectionKernel launch, from the ncu capture
+# summarised under profiles/ (16.88 MB read, nothing written back to DRAM inside the launch)
+TRAFFIC_PER_LAUNCH = 16.88e6
 WORKLOAD = "configs[1]: K4 MoE layer decode, 1 token, 64 experts top-8, hidden 2048, intermediate 1024"
 
 
@@ -160,6 +160,42 @@ def run_reference(args):
 
 
 # ---- GPU arm ------------------------------------------------------------------------------------------------
+def prefill_leg(k, dev, layers: int, tokens: int = 2048, passes: int = 3) -> dict:
+    """One prefill chunk per layer (grouping, three grouped projections with the decode fused in, SwiGLU, combine) over
+    `layers` layers of distinct weights, Zipf(1.1) routing; device time per chunk from CUDA events."""
+    import torch
+    from padra_b200.experts import bf16_values, zipf_routing
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(77)
+    chunks = []
+    for layer in range(layers):
+        ids, w = zipf_routing(tokens, seed=layer, device=dev)
+        chunks.append((layer, ids.reshape(-1), w.reshape(-1), bf16_values(torch.randn((tokens, HIDDEN), device=dev, generator=g)),
+                       bf16_values(torch.randn((tokens, HIDDEN), device=dev, generator=g))))
+    for c in chunks[:3]:
+        k.prefill_layer(*c, tokens)
+    torch.cuda.synchronize(dev)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(passes):
+        for c in chunks:
+            k.prefill_layer(*c, tokens)
+    b.record()
+    torch.cuda.synchronize(dev)
+    seconds = a.elapsed_time(b) / 1e3 / (passes * layers)
+    flops = tokens * TOPK * 3 * 2 * HIDDEN * INTER
+    measured = ROOT / "MEASURED_PEAKS.json"
+    data = json.loads(measured.read_text()) if measured.exists() else {}
+    tensor_peak = float(data.get("bf16_tflops_sustained", 1400.0))
+    return {"workload": f"prefill chunk: {tokens} tokens x top-8 of 64 experts, hidden {HIDDEN} / inter {INTER}, K{RATE}, Zipf(1.1) routing",
+            "tokens_per_s": tokens / seconds, "us_per_layer_chunk": seconds * 1e6, "tflops": flops / seconds / 1e12,
+            "roofline": {"bound": "tensor", "achieved": flops / seconds / 1e12, "peak": tensor_peak, "unit": "TFLOP/s",
+                         "frac": flops / seconds / 1e12 / tensor_peak,
+                         "peak_source": "measured (sustained cuBLAS bf16)" if data else "fallback"},
+            "kernels_per_chunk": 9, "layers_rotated": layers, "passes": passes}
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -345,6 +381,9 @@ def run_ours(args):
         "clocks": {"sm_mhz": clock_info["sm_mhz"], "sm_max_mhz": clock_info["sm_max_mhz"], "reasons": clock_info["reasons"],
                    "samples": clock_info["samples"]},
     }
+    if world == 1:
+        line["prefill_chunk"] = prefill_leg(k, dev, layers)
+        assert k.bad_flag() == 0, "the sticky error flag was raised during the prefill leg"
     if world == 1 and not args.no_cpu:
         threads = os.cpu_count() or 1
         sec, nbytes = cpu_layer_steps(steps=12, warmup=1, threads=threads)

@@ -178,19 +178,6 @@ __device__ __forceinline__ void TmemLoad4x8(unsigned taddr, float (&v)[4][8]) {
       v[q][j] = __uint_as_float(r[q][j]);
 }
 
-#ifdef PADRA_PREFILL_TRACE
-__device__ unsigned long long g_trace[8 * 8192];
-__device__ __forceinline__ unsigned long long Now() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define TRACE(index, slot) g_trace[(index) * 8 + (slot)] = Now()
-#define TRACE_VALUE(index, slot, value) g_trace[(index) * 8 + (slot)] = (value)
-#else
-#define TRACE(index, slot)
-#define TRACE_VALUE(index, slot, value)
-#endif
 
 // Item `sequence` of this CTA: tiles sorted by size are dealt out forwards and backwards in turn.
 __device__ __forceinline__ int ItemIndex(int sequence) {
@@ -273,7 +260,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
   }
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
-      BarrierInit(&sm.full[s], kWarpsPerSet);
+      BarrierInit(&sm.full[s], kWarpsPerSet * 32 + kWarpsPerSet); // every producer thread's copies + one arrival per warp
       BarrierInit(&sm.empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -334,7 +321,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
     for (int d = 0; d < kAhead; ++d)
       fetch(ahead[d]);
     bool alive = true;
-    int pending_slot = -1; // stage written but not yet published
     unsigned q = 0;        // stages this CTA has been through before the current item
     for (int sequence = 0; alive; ++sequence, q += stages) {
       const int index = ItemIndex(sequence);
@@ -373,30 +359,26 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
         const __half *b_stage_rows = b_rows + i * kStageK;
 #pragma unroll
         for (int j = 0; j < kMaxTileN / 32; ++j)
-          if ((ptid >> 3) + 32 * j < tile_n)
+          if ((ptid >> 3) + 32 * j < tile_n
+          )
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_target + j * 512), "l"(b_stage_rows + b_source[j]) : "memory");
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        // A: this lane's four 16-byte core-matrix rows (fragment f: K half f>>1, output group f&1)
+        // the stage's barrier counts this thread's copies as one arrival of their own, once they have landed
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(SmemAddress(&sm.full[s])) : "memory");
+        // weights: this lane's four 16-byte core-matrix rows (fragment f: K half f>>1, output group f&1)
         unsigned char *a_stage = sm.a[s];
 #pragma unroll
         for (int f = 0; f < 4; ++f) {
           const uint4 row = make_uint4(frag[0][f], frag[1][f], frag[2][f], frag[3][f]);
           *reinterpret_cast<uint4 *>(a_stage + (2 * kstep + (f >> 1)) * 2048 + (2 * column + (f & 1)) * 128 + g * 16) = row;
         }
-        // publish this set's PREVIOUS stage: its copy group has had a whole stage time to land
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // publish at once (release); the MMA thread orders these generic-proxy writes before its tensor-core reads
+        // with a proxy fence after its wait, so nobody waits here for the copies
         __syncwarp();
-        if (pending_slot >= 0 && lane == 0)
-          BarrierArrive(&sm.full[pending_slot]);
-        pending_slot = s;
+        if (lane == 0)
+          BarrierArrive(&sm.full[s]);
       }
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncwarp();
-    if (alive && pending_slot >= 0 && lane == 0)
-      BarrierArrive(&sm.full[pending_slot]);
+    asm volatile("cp.async.wait_all;" ::: "memory");
   } else if (warp == kMmaWarp) {
     // =============================== MMA issue ===============================
     if (lane == 0) {
@@ -414,19 +396,13 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
         // the accumulator must have been drained by the epilogue of the item two before
         alive = BarrierWait(&sm.accumulator_free[buffer], ((sequence >> 1) & 1) ^ 1, abort, 0);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        TRACE(index, 0);
-        TRACE_VALUE(index, 6, blockIdx.x);
-        TRACE_VALUE(index, 7, tile_n);
         for (int i = 0; i < stages && alive; ++i) {
           const int s = (q + i) % kStages;
           alive = BarrierWait(&sm.full[s], ((q + i) / kStages) & 1, abort, 0);
           if (!alive)
             break;
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // producers' stores and copies -> tensor-core reads
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          if (i == 0)
-            TRACE(index, 1);
-          if (i == stages - 1)
-            TRACE(index, 2);
           const unsigned w_base = SmemAddress(sm.a[s]), x_base = SmemAddress(sm.b[s]);
           // rows of the last token tile past tile_n hold whatever the ring held before: they only reach accumulator
           // rows that nobody reads
@@ -481,11 +457,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
                    : "memory");
       if (any_failed)
         break;
-#ifdef PADRA_PREFILL_TRACE
-      if (tid == 0)
-        TRACE(index, 3);
-      __syncwarp();
-#endif
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float *scale = sm.scale[buffer];
       for (int mt = 0; mt * 128 + warp * 32 < valid; ++mt) { // warp-uniform: token tiles that hold rows of this warp
@@ -544,11 +515,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
       __syncwarp();
       if (lane == 0)
         BarrierArrive(&sm.accumulator_free[buffer]);
-#ifdef PADRA_PREFILL_TRACE
-      if (tid == 0)
-        TRACE(index, 4);
-      __syncwarp();
-#endif
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
@@ -664,11 +630,6 @@ template <int Rate> int LaunchGemm(const PrefillArgs &a, dim3 grid, cudaStream_t
 
 } // namespace
 
-#ifdef PADRA_PREFILL_TRACE
-extern "C" __attribute__((visibility("default"))) int padra_prefill_trace_read(void *host, size_t bytes) {
-  return cudaMemcpyFromSymbol(host, g_trace, bytes);
-}
-#endif
 
 int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, const float *input,
                               unsigned short *output, const unsigned short *gate, const unsigned short *up,
