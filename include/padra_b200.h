@@ -2,8 +2,8 @@
  * padra_b200 -- C ABI of the B200 (sm_100a) EXL3 mixture-of-experts expert kernels.
  *
  * Every entry point takes plain device pointers and sizes, enqueues work on the given CUDA stream and
- * returns at once; none of them allocates, frees, synchronises or reads device memory on the host, so all
- * of them may be recorded into CUDA graphs.  Activations follow the reference's conventions: decode-side
+ * returns at once; none of them allocates, frees, synchronises or reads device memory on the host, so the
+ * entry points that stand in for a reference launcher may be recorded into CUDA graphs.  Activations follow the reference's conventions: decode-side
  * buffers are `float` arrays holding BF16-representable values, prefill-side buffers are BF16 bit patterns
  * in `unsigned short`.  Errors discovered on the device (a descriptor that does not fit the call, an expert
  * id outside 0..63, a non-finite or FP16-overflowing value) set the caller's sticky `*bad` flag with an
@@ -177,6 +177,27 @@ PADRA_API int padra_exl3_moe_decode_layer_persistent(const padra_matrix *matrice
  * trace off.  While set, every layer call makes each CTA record %globaltimer at fixed points (start, set-up
  * done, streaming done, counting done, end, and per chunk); a host-side setting, not stream-ordered. */
 PADRA_API int padra_exl3_moe_decode_set_trace(void *buffer, size_t bytes);
+
+/* ---- decode layer without any device allocation ------------------------------------------------------------
+ * This entry point has no counterpart in the reference.  It is padra_exl3_moe_decode_layer for callers that cannot
+ * allocate device memory: a server that gave every free byte of the device to its own arena at start-up, a plugin
+ * that is not allowed to touch the allocator, or a latency-critical path that must avoid the device-wide
+ * synchronisation of cudaMalloc/cudaFree.  Instead of a caller workspace it uses an array of
+ * PADRA_STATIC_SCRATCH_BYTES that is built into the library's device code, and it calls no cudaMalloc, cudaFree or
+ * other allocating routine.
+ *   - Shapes whose workspace (padra_exl3_moe_decode_workspace_bytes for the split pipeline) exceeds the array are
+ *     refused with PADRA_RESOURCE_EXHAUSTED; at hidden 2048 / intermediate 1024 that is more than 7 tokens, at
+ *     2304 / 896 more than 5.
+ *   - There is one array per device and every call shares it: calls that may overlap on the GPU race on it, so the
+ *     caller orders them (one stream, or events).  The array keeps the last call's contents; nothing in it needs to
+ *     start at zero.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current); make that first call outside any stream capture. */
+#define PADRA_STATIC_SCRATCH_BYTES (4u << 20)
+PADRA_API int padra_exl3_moe_decode_layer_static(const padra_matrix *matrices, int layer, const int *ids,
+                                                 const float *routing, const float *normalized, float *x, int tokens,
+                                                 int rate, int hidden, int inter, const unsigned short *table, int *bad,
+                                                 padra_stream stream);
 
 
 /* ---- utilities ------------------------------------------------------------------------------------------

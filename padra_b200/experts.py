@@ -295,6 +295,13 @@ class ExpertKernels:
                                                              B.stream_handle(stream))
         B.check(st, "padra_exl3_moe_decode_layer_persistent")
 
+    def moe_decode_layer_static(self, layer, ids, routing, normalized, x, tokens, stream=None):
+        """The decode layer on the library's built-in scratch array: no workspace, no allocation in the call."""
+        st = self.lib.padra_exl3_moe_decode_layer_static(self.t.descriptors.data_ptr(), layer, B.ptr(ids), B.ptr(routing),
+                                                         B.ptr(normalized), B.ptr(x), tokens, self.t.rate, *self.dims,
+                                                         B.ptr(self.table), B.ptr(self.bad), B.stream_handle(stream))
+        B.check(st, "padra_exl3_moe_decode_layer_static")
+
     def moe_decode_layer(self, layer, ids, routing, normalized, x, tokens, stream=None):
         ws = self.decode_workspace(tokens)
         st = self.lib.padra_exl3_moe_decode_layer(self.t.descriptors.data_ptr(), layer, B.ptr(ids), B.ptr(routing),
