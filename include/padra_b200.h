@@ -186,8 +186,8 @@ PADRA_API int padra_exl3_moe_decode_set_trace(void *buffer, size_t bytes);
  * PADRA_STATIC_SCRATCH_BYTES that is built into the library's device code, and it calls no cudaMalloc, cudaFree or
  * other allocating routine.
  *   - Shapes whose workspace (padra_exl3_moe_decode_workspace_bytes for the split pipeline) exceeds the array are
- *     refused with PADRA_RESOURCE_EXHAUSTED; at hidden 2048 / intermediate 1024 that is more than 7 tokens, at
- *     2304 / 896 more than 5.
+ *     refused with PADRA_RESOURCE_EXHAUSTED; at hidden 2048 / intermediate 1024 and at 2304 / 896 that is more than
+ *     7 tokens.
  *   - There is one array per device and every call shares it: calls that may overlap on the GPU race on it, so the
  *     caller orders them (one stream, or events).  The array keeps the last call's contents; nothing in it needs to
  *     start at zero.
