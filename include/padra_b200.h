@@ -131,6 +131,31 @@ PADRA_API int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer,
                                         padra_stream stream, unsigned *stats, int wide_input, int rate,
                                         int hidden, int inter);
 
+/* ---- expert-parallel prefill -----------------------------------------------------------------------------
+ * The reference runs on one GPU; these four entry points are what a host needs around an all-to-all exchange when the
+ * 64 experts of a layer are spread over several GPUs (the exchange itself is the host's: NCCL).  Arithmetic is that
+ * of the single-GPU prefill path; rows travel as BF16, which is what the projections read and write anyway.
+ *   padra_ep_pack_rows: packed[j] = BF16 bits of activations[order[j]/8], j < rows = tokens*8; order lists the
+ *     (token*8+slot) pairs in the order in which they are sent (sorted by destination rank).
+ *   padra_ep_group_rows: fast_expert::Group for received rows: ids[rows] are expert ids 0..63 (any number of rows
+ *     per expert, up to group_stride), groups[e*group_stride + n] = n-th row of expert e in ascending row order.
+ *   padra_exl3_prefill_rows_launch: padra_exl3_prefill_launch's tensor-memory GEMM with one BF16 input row per pair
+ *     (parts 0, 1: input_rows [rows][hidden]; part 2: gate/up [rows][inter]); output [rows][out] BF16 bits in row
+ *     order; transformed is workspace of rows*max(hidden, inter) halves.  rows <= 16384.
+ *   padra_ep_combine: padra_combine_packed with the down row of pair p at down_rows[position[p]]. */
+PADRA_API int padra_ep_pack_rows(const float *activations, const int *order, unsigned short *packed, int rows, int hidden,
+                                 int *bad, padra_stream stream);
+PADRA_API int padra_ep_group_rows(const int *ids, int *groups, int *counts, int rows, int group_stride, int *bad,
+                                  padra_stream stream);
+PADRA_API int padra_exl3_prefill_rows_launch(const padra_matrix *matrices, int layer, int part, const int *groups,
+                                             const int *counts, int group_stride, int rows,
+                                             const unsigned short *input_rows, unsigned short *output,
+                                             const unsigned short *gate, const unsigned short *up,
+                                             const unsigned short *table, void *transformed, int *bad,
+                                             padra_stream stream, int rate, int hidden, int inter);
+PADRA_API int padra_ep_combine(float *x, const unsigned short *down_rows, const int *position, const float *weights,
+                               int tokens, int *bad, int residual, int hidden, padra_stream stream);
+
 /* ---- small-batch projection (T < 4) -------------------------------------------------------------------
  * exl3_expert::Launch (src/cuda/expert_exl3.cuh:137-151): pairs = tokens*8, input row pair/8 (gate/up) or
  * pair (down), FP32-held BF16 in and out.  in_scratch / out_scratch are accepted and unused. */

@@ -121,6 +121,33 @@ int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer, int part,
                               bad, S(stream), rate, hidden, inter);
 }
 
+int padra_ep_pack_rows(const float *activations, const int *order, unsigned short *packed, int rows, int hidden, int *bad,
+                       padra_stream stream) {
+  return LaunchPackRows(activations, order, packed, rows, hidden, bad, S(stream));
+}
+
+int padra_ep_group_rows(const int *ids, int *groups, int *counts, int rows, int group_stride, int *bad, padra_stream stream) {
+  return LaunchGroupRows(ids, groups, counts, rows, group_stride, bad, S(stream));
+}
+
+int padra_exl3_prefill_rows_launch(const padra_matrix *matrices, int layer, int part, const int *groups, const int *counts,
+                                   int group_stride, int rows, const unsigned short *input_rows, unsigned short *output,
+                                   const unsigned short *gate, const unsigned short *up, const unsigned short *table,
+                                   void *transformed, int *bad, padra_stream stream, int rate, int hidden, int inter) {
+  if (!RateOk(rate))
+    return PADRA_UNSUPPORTED;
+  if (!matrices || !groups || !counts || !output || !transformed || !bad || part < 0 || part > 2 || layer < 0 || hidden < 128 ||
+      inter < 128 || (hidden % 128) || (inter % 128) || (part == 2 ? (!gate || !up || !table) : !input_rows))
+    return PADRA_INVALID_ARGUMENT;
+  return LaunchPrefillRows(matrices, layer, part, groups, counts, group_stride, rows, input_rows, output, gate, up, table,
+                           transformed, bad, S(stream), rate, hidden, inter);
+}
+
+int padra_ep_combine(float *x, const unsigned short *down_rows, const int *position, const float *weights, int tokens, int *bad,
+                     int residual, int hidden, padra_stream stream) {
+  return LaunchCombineIndexed(x, down_rows, position, weights, tokens, bad, residual, hidden, S(stream));
+}
+
 int padra_exl3_expert_launch(const padra_matrix *matrices, int layer, int part, const int *ids, const float *input,
                              float *output, float *in_scratch, float *out_scratch, int tokens, int *bad,
                              padra_stream stream, int rate, int hidden, int inter) {

@@ -37,6 +37,15 @@ int LaunchTileProjection(const Matrix *matrices, int layer, int part, const int 
                          const int *tile_count, const float *input, unsigned short *output,
                          const unsigned short *gate, const unsigned short *up, const unsigned short *table, int tokens,
                          int *bad, cudaStream_t stream, int rate, int hidden, int inter);
+int LaunchPrefillRows(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, int group_stride, int rows,
+                      const unsigned short *input_rows, unsigned short *output, const unsigned short *gate,
+                      const unsigned short *up, const unsigned short *table, void *transformed, int *bad, cudaStream_t stream,
+                      int rate, int hidden, int inter);
+int LaunchGroupRows(const int *ids, int *groups, int *counts, int rows, int group_stride, int *bad, cudaStream_t stream);
+int LaunchPackRows(const float *activations, const int *order, unsigned short *packed, int rows, int hidden, int *bad,
+                   cudaStream_t stream);
+int LaunchCombineIndexed(float *x, const unsigned short *down_rows, const int *position, const float *weights, int tokens,
+                         int *bad, int residual, int hidden, cudaStream_t stream);
 int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, const float *input,
                               unsigned short *output, const unsigned short *gate, const unsigned short *up,
                               const unsigned short *table, void *transformed, int tokens, int *bad, cudaStream_t stream, int rate,

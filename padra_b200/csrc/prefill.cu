@@ -72,7 +72,9 @@ struct PrefillArgs {
   const int *groups, *counts;
   const __half *transformed; // [pairs][cols] in expert-grouped order
   unsigned short *output;    // [pairs][rows] BF16 bits, pair order
-  int tokens, hidden, inter;
+  int group_stride; // rows of `groups` per expert = the most pairs one expert can hold
+  int pairs_total;  // pairs (rows of `output`) in the call
+  int hidden, inter;
   int *bad;
 };
 
@@ -192,7 +194,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
   PrefillSmem &sm = *reinterpret_cast<PrefillSmem *>(raw_smem); // no-swizzle operands need 16-byte alignment only
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rows = a.part == 2 ? a.hidden : a.inter, cols = a.part == 2 ? a.inter : a.hidden;
-  const int pairs_total = a.tokens * kTopK;
+  const int pairs_total = a.pairs_total;
   const int row_blocks = rows / kTileM, stages = cols / kStageK;
 
   // ---- the tile list: every CTA builds the same one ----
@@ -204,7 +206,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
   int my_count = 0, my_tiles = 0, tile_prefix = 0, pair_prefix = 0;
   if (tid < kExperts) {
     my_count = a.counts[tid];
-    if (my_count < 0 || my_count > a.tokens) {
+    if (my_count < 0 || my_count > a.group_stride) {
       Raise(a.bad);
       sm.abort = 1;
       my_count = 0;
@@ -437,7 +439,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
       sm.scale[buffer][o] = HalfBitsToFloat(m.svh[block * kTileM + o]);
       int *pairs = sm.pairs[buffer];
       for (int n = o; n < valid; n += kEpilogueWarps * 32) {
-        const int pair = a.groups[t.expert * a.tokens + t.begin + n];
+        const int pair = a.groups[static_cast<size_t>(t.expert) * a.group_stride + t.begin + n];
         pairs[n] = pair;
         if (pair < 0 || pair >= pairs_total) {
           Raise(a.bad);
@@ -530,14 +532,15 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
 // part 2: x = SwiGLU(gate[pair], up[pair]) first (expert_exl3_prefill_packed_activations.cuh:17-73).
 __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices, int layer, int part, const int *groups, const int *counts,
                                                           const float *input, const unsigned short *gate, const unsigned short *up,
-                                                          const unsigned short *table, __half *transformed, int tokens, int hidden,
+                                                          const unsigned short *pair_rows, const unsigned short *table,
+                                                          __half *transformed, int group_stride, int pairs, int hidden,
                                                           int inter, int *bad) {
   __shared__ int s_offset[kExperts + 1], s_half;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int cols = part == 2 ? inter : hidden, blocks = cols / 128, pairs = tokens * kTopK;
+  const int cols = part == 2 ? inter : hidden, blocks = cols / 128;
   if (threadIdx.x < kExperts) { // exclusive prefix sum of the 64 group sizes: two warp scans
     int n = counts[threadIdx.x];
-    n = (n < 0 || n > tokens) ? 0 : n;
+    n = (n < 0 || n > group_stride) ? 0 : n;
     int inclusive = n;
 #pragma unroll
     for (int d = 1; d < 32; d *= 2) {
@@ -562,7 +565,7 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
   for (int step = 32; step; step >>= 1)
     if (expert + step < kExperts && s_offset[expert + step] <= row)
       expert += step;
-  const int pair = groups[expert * tokens + (row - s_offset[expert])];
+  const int pair = groups[static_cast<size_t>(expert) * group_stride + (row - s_offset[expert])];
   if (pair < 0 || pair >= pairs) {
     if (!lane)
       Raise(bad);
@@ -593,6 +596,10 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
           Raise(bad);
       }
     }
+  } else if (pair_rows) { // one BF16 row per pair (rows received from other ranks)
+    const uint2 xb = *reinterpret_cast<const uint2 *>(pair_rows + static_cast<size_t>(pair) * cols + k);
+    src[0] = FromBF16Bits(xb.x & 0xffffu), src[1] = FromBF16Bits(xb.x >> 16);
+    src[2] = FromBF16Bits(xb.y & 0xffffu), src[3] = FromBF16Bits(xb.y >> 16);
   } else {
     const float4 x = *reinterpret_cast<const float4 *>(input + static_cast<size_t>(pair >> 3) * cols + k);
     src[0] = x.x, src[1] = x.y, src[2] = x.z, src[3] = x.w;
@@ -631,24 +638,24 @@ template <int Rate> int LaunchGemm(const PrefillArgs &a, dim3 grid, cudaStream_t
 } // namespace
 
 
-int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, const float *input,
-                              unsigned short *output, const unsigned short *gate, const unsigned short *up,
-                              const unsigned short *table, void *transformed, int tokens, int *bad, cudaStream_t stream, int rate,
-                              int hidden, int inter) {
-  if (tokens < 1 || tokens > kMaxTokensPrefill || !transformed)
+// `pair_rows` null: the reference's layout, pairs = tokens*8 and input row pair/8.  Otherwise one BF16 input row per
+// pair, any number of pairs per expert up to group_stride (rows that other ranks routed to this rank's experts).
+static int LaunchPrefillGemm(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, const float *input,
+                             const unsigned short *pair_rows, unsigned short *output, const unsigned short *gate,
+                             const unsigned short *up, const unsigned short *table, void *transformed, int group_stride, int pairs,
+                             int *bad, cudaStream_t stream, int rate, int hidden, int inter) {
+  if (pairs < 1 || pairs > kMaxTokensPrefill * kTopK || group_stride < 1 || group_stride > pairs || !transformed)
     return PADRA_INVALID_ARGUMENT;
-  const int rows = part == 2 ? hidden : inter, cols = part == 2 ? inter : hidden, pairs = tokens * kTopK;
   if (reinterpret_cast<uintptr_t>(output) % 16 || reinterpret_cast<uintptr_t>(transformed) % 16)
     return PADRA_INVALID_ARGUMENT;
-  PrefillInputKernel<<<(pairs + 7) / 8, 256, 0, stream>>>(matrices, layer, part, groups, counts, input, gate, up, table,
-                                                                               static_cast<__half *>(transformed), tokens, hidden, inter,
-                                                                               bad);
+  PrefillInputKernel<<<(pairs + 7) / 8, 256, 0, stream>>>(matrices, layer, part, groups, counts, input, gate, up, pair_rows, table,
+                                                          static_cast<__half *>(transformed), group_stride, pairs, hidden, inter, bad);
   if (cudaGetLastError() != cudaSuccess)
     return PADRA_INTERNAL;
   PrefillArgs a{};
   a.matrices = matrices, a.layer = layer, a.part = part, a.groups = groups, a.counts = counts;
-  a.transformed = static_cast<const __half *>(transformed), a.output = output, a.tokens = tokens, a.hidden = hidden, a.inter = inter;
-  a.bad = bad;
+  a.transformed = static_cast<const __half *>(transformed), a.output = output, a.group_stride = group_stride;
+  a.pairs_total = pairs, a.hidden = hidden, a.inter = inter, a.bad = bad;
   int device = 0, sms = 0;
   if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 1)
     return PADRA_INTERNAL;
@@ -663,6 +670,26 @@ int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const
   default:
     return PADRA_UNSUPPORTED;
   }
+}
+
+int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, const float *input,
+                              unsigned short *output, const unsigned short *gate, const unsigned short *up,
+                              const unsigned short *table, void *transformed, int tokens, int *bad, cudaStream_t stream, int rate,
+                              int hidden, int inter) {
+  if (tokens < 1 || tokens > kMaxTokensPrefill)
+    return PADRA_INVALID_ARGUMENT;
+  return LaunchPrefillGemm(matrices, layer, part, groups, counts, input, nullptr, output, gate, up, table, transformed, tokens,
+                           tokens * kTopK, bad, stream, rate, hidden, inter);
+}
+
+int LaunchPrefillRows(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, int group_stride, int rows,
+                      const unsigned short *input_rows, unsigned short *output, const unsigned short *gate,
+                      const unsigned short *up, const unsigned short *table, void *transformed, int *bad, cudaStream_t stream,
+                      int rate, int hidden, int inter) {
+  if (part != 2 && !input_rows)
+    return PADRA_INVALID_ARGUMENT;
+  return LaunchPrefillGemm(matrices, layer, part, groups, counts, nullptr, input_rows, output, gate, up, table, transformed,
+                           group_stride, rows, bad, stream, rate, hidden, inter);
 }
 
 } // namespace padra

@@ -1,0 +1,203 @@
+"""Expert-parallel prefill: the 64 experts of every layer spread over the ranks of a process group, token rows
+exchanged with all-to-all (NCCL over NVLink on GPUs; any torch.distributed backend for the host logic).
+
+One layer, seen from a rank that holds `tokens` tokens (at most 2048 per call):
+
+  plan      dest[pair] = owner of the pair's expert; the pairs sorted by destination (stable) give the send order
+  pack      one BF16 row per pair in send order                                   (padra_ep_pack_rows)
+  exchange  counts, then rows and their expert ids                                (all_to_all_single)
+  experts   received rows grouped by expert, gate/up projections, SwiGLU, down    (padra_ep_group_rows,
+                                                                                   padra_exl3_prefill_rows_launch)
+  exchange  down rows back, same splits reversed: they arrive in send order
+  combine   x[t] = B(x[t] + sum_s B(down * w)) reading pair p at row position[p]  (padra_ep_combine)
+
+The reference serves one GPU and has no counterpart of this file; the arithmetic per row is that of its prefill path
+(src/cuda/inference.cu:3896-3921).  The compute steps go through a backend object so that the exchange logic can be
+run on CPU ranks (gloo) against a host implementation of the same three steps.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+EXPERTS, TOPK = 64, 8
+MAX_ROWS = 2048 * TOPK  # rows one grouped-projection call takes
+
+
+def balanced_placement(popularity, world: int) -> np.ndarray:
+    """owner[expert] for `world` ranks holding 64/world experts each: experts in order of falling popularity go to the
+    rank with the least expected load that still has room (longest-processing-time-first).  Ties break towards the
+    lower rank, so every rank computes the same table from the same popularity."""
+    popularity = np.asarray(popularity, dtype=np.float64)
+    assert popularity.shape == (EXPERTS,) and EXPERTS % world == 0
+    room = np.full(world, EXPERTS // world)
+    load = np.zeros(world)
+    owner = np.empty(EXPERTS, dtype=np.int32)
+    for e in np.argsort(-popularity, kind="stable"):
+        candidates = np.where(room > 0)[0]
+        r = candidates[np.argmin(load[candidates])]
+        owner[e], load[r], room[r] = r, load[r] + popularity[e], room[r] - 1
+    return owner
+
+
+def contiguous_placement(world: int) -> np.ndarray:
+    return (np.arange(EXPERTS) // (EXPERTS // world)).astype(np.int32)
+
+
+@dataclass
+class Plan:
+    order: torch.Tensor       # [pairs] int32: pair sent as row j
+    position: torch.Tensor    # [pairs] int32: row at which pair p comes back
+    send_ids: torch.Tensor    # [pairs] int32: expert id of row j
+    send_counts: torch.Tensor  # [world] int64: rows per destination
+
+
+def make_plan(ids: torch.Tensor, owner: torch.Tensor, world: int) -> Plan:
+    """ids [pairs] int32 expert ids in (token, slot) order; owner [64] on the same device."""
+    flat = ids.reshape(-1).long()
+    dest = owner[flat]
+    order = torch.sort(dest, stable=True).indices
+    position = torch.empty_like(order)
+    position[order] = torch.arange(order.numel(), device=order.device)
+    return Plan(order.to(torch.int32), position.to(torch.int32), flat[order].to(torch.int32),
+                torch.bincount(dest, minlength=world))
+
+
+class GroupExchange:
+    """all-to-all over a torch.distributed process group.  The split sizes have to reach the host, which costs one
+    synchronisation per layer call: the price of exact-size messages."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+
+    def counts(self, send_counts: torch.Tensor):
+        recv = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv, send_counts, group=self.group)
+        both = torch.stack([send_counts, recv]).cpu()
+        return both[0].tolist(), both[1].tolist()
+
+    def rows(self, send: torch.Tensor, send_splits, recv_splits) -> torch.Tensor:
+        """Rows travel as bytes: every backend moves uint8, not every backend knows 16-bit integer types."""
+        width = send[0].numel() * send.element_size() if send.dim() > 1 else send.element_size()
+        recv = torch.empty((sum(recv_splits),) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+        dist.all_to_all_single(recv.view(torch.uint8).reshape(-1, width), send.contiguous().view(torch.uint8).reshape(-1, width),
+                               output_split_sizes=list(recv_splits), input_split_sizes=list(send_splits), group=self.group)
+        return recv
+
+
+class LoopbackHub:
+    """Meeting point of LoopbackExchange ranks."""
+
+    def __init__(self, world: int):
+        import threading
+
+        self.world = world
+        self.barrier = threading.Barrier(world)
+        self.slots = [None] * world
+
+
+class LoopbackExchange:
+    """The same interface with the ranks as threads of ONE process that share one device (and its default stream, so
+    kernels run in launch order): lets the whole expert-parallel path run where only one GPU is to be had."""
+
+    def __init__(self, hub: LoopbackHub, rank: int):
+        self.hub, self.rank, self.world = hub, rank, hub.world
+
+    def _swap(self, pieces):
+        self.hub.slots[self.rank] = pieces
+        self.hub.barrier.wait()
+        got = [self.hub.slots[source][self.rank] for source in range(self.world)]
+        self.hub.barrier.wait()
+        return got
+
+    def counts(self, send_counts: torch.Tensor):
+        mine = [int(v) for v in send_counts.tolist()]
+        return mine, self._swap(mine)
+
+    def rows(self, send: torch.Tensor, send_splits, recv_splits) -> torch.Tensor:
+        as_bytes = send.contiguous().view(torch.uint8).reshape(send.shape[0], -1)
+        got = self._swap(list(torch.split(as_bytes, list(send_splits))))
+        assert [g.shape[0] for g in got] == list(recv_splits)
+        return torch.cat(got).view(send.dtype).reshape((-1,) + tuple(send.shape[1:]))
+
+
+class KernelBackend:
+    """The three compute steps on the GPU through the C ABI."""
+
+    def __init__(self, kernels):
+        from . import binding as B
+
+        self.k, self.B, self.lib = kernels, B, kernels.lib
+        self.device = kernels.t.device
+        self.hidden, self.inter = kernels.dims
+        self._work = None
+
+    def _workspace(self):
+        if self._work is None:
+            dev, h, i = self.device, self.hidden, self.inter
+            self._work = dict(groups=torch.empty(EXPERTS * MAX_ROWS, dtype=torch.int32, device=dev),
+                              counts=torch.empty(EXPERTS, dtype=torch.int32, device=dev),
+                              gate=torch.empty((MAX_ROWS, i), dtype=torch.uint16, device=dev),
+                              up=torch.empty((MAX_ROWS, i), dtype=torch.uint16, device=dev),
+                              transformed=torch.empty((MAX_ROWS, max(h, i)), dtype=torch.float16, device=dev))
+        return self._work
+
+    def pack(self, plan: Plan, normalized: torch.Tensor) -> torch.Tensor:
+        B, rows = self.B, plan.order.numel()
+        packed = torch.empty((rows, self.hidden), dtype=torch.uint16, device=self.device)
+        B.check(self.lib.padra_ep_pack_rows(B.ptr(normalized), B.ptr(plan.order), B.ptr(packed), rows, self.hidden,
+                                            B.ptr(self.k.bad), B.stream_handle()), "padra_ep_pack_rows")
+        return packed
+
+    def experts(self, layer: int, rows: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        B, w, k = self.B, self._workspace(), self.k
+        total = rows.shape[0]
+        down = torch.empty((total, self.hidden), dtype=torch.uint16, device=self.device)
+        stream = B.stream_handle()
+        for begin in range(0, total, MAX_ROWS):
+            n = min(MAX_ROWS, total - begin)
+            B.check(self.lib.padra_ep_group_rows(B.ptr(ids[begin:begin + n]), B.ptr(w["groups"]), B.ptr(w["counts"]), n, n,
+                                                 B.ptr(k.bad), stream), "padra_ep_group_rows")
+            for part, target in ((0, w["gate"]), (1, w["up"]), (2, down[begin:begin + n])):
+                B.check(self.lib.padra_exl3_prefill_rows_launch(
+                    k.t.descriptors.data_ptr(), layer, part, B.ptr(w["groups"]), B.ptr(w["counts"]), n, n,
+                    B.ptr(rows[begin:begin + n]), B.ptr(target), B.ptr(w["gate"]), B.ptr(w["up"]), B.ptr(k.table),
+                    B.ptr(w["transformed"]), B.ptr(k.bad), stream, k.t.rate, self.hidden, self.inter),
+                    "padra_exl3_prefill_rows_launch")
+        return down
+
+    def combine(self, plan: Plan, returned: torch.Tensor, routing: torch.Tensor, x: torch.Tensor) -> None:
+        B, tokens = self.B, x.shape[0]
+        B.check(self.lib.padra_ep_combine(B.ptr(x), B.ptr(returned), B.ptr(plan.position), B.ptr(routing), tokens,
+                                          B.ptr(self.k.bad), 1, self.hidden, B.stream_handle()), "padra_ep_combine")
+
+
+class ExpertParallelPrefill:
+    """One MoE layer call for this rank's tokens; every rank of the group calls it together."""
+
+    def __init__(self, backend, exchange, owner: np.ndarray):
+        self.backend, self.exchange = backend, exchange
+        self.owner_host = np.asarray(owner, dtype=np.int32)
+        self._owner = {}
+
+    def owner_on(self, device) -> torch.Tensor:
+        if device not in self._owner:
+            self._owner[device] = torch.from_numpy(self.owner_host.astype(np.int64)).to(device)
+        return self._owner[device]
+
+    def layer(self, layer: int, ids: torch.Tensor, routing: torch.Tensor, normalized: torch.Tensor, x: torch.Tensor) -> None:
+        """ids/routing [tokens*8], normalized/x [tokens][hidden] (FP32 holding BF16 values); x updated in place."""
+        ex = self.exchange
+        plan = make_plan(ids, self.owner_on(ids.device), ex.world)
+        packed = self.backend.pack(plan, normalized)
+        send_splits, recv_splits = ex.counts(plan.send_counts)
+        rows = ex.rows(packed, send_splits, recv_splits)
+        row_ids = ex.rows(plan.send_ids, send_splits, recv_splits)
+        down = self.backend.experts(layer, rows, row_ids) if rows.shape[0] else rows
+        returned = ex.rows(down, recv_splits, send_splits)
+        self.backend.combine(plan, returned, routing, x)

@@ -1,0 +1,175 @@
+"""Expert-parallel prefill: placement, the exchange plan, and the whole layer over several ranks.
+
+CPU: two gloo ranks run the layer with a host backend built on the oracle; every rank's result must equal the
+oracle's single-process layer on that rank's tokens bit for bit (the exchange only moves rows).
+GPU: the ranks are threads sharing one device (LoopbackExchange); results must equal the single-GPU prefill path."""
+import threading
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import exl3_oracle as O
+from padra_b200 import expert_parallel as EP
+
+
+def test_balanced_placement_fills_every_rank_and_balances():
+    from padra_b200.experts import zipf_routing
+
+    # popularity as a server would measure it: how many pairs of a 2048-token chunk each expert received
+    ids, _ = zipf_routing(2048, seed=3, device="cpu")
+    popularity = np.bincount(ids.reshape(-1).numpy(), minlength=64).astype(np.float64)
+    for world in (1, 2, 4, 8):
+        owner = EP.balanced_placement(popularity, world)
+        assert np.bincount(owner, minlength=world).tolist() == [64 // world] * world
+        load = np.array([popularity[owner == r].sum() for r in range(world)])
+        contiguous = np.array([popularity[EP.contiguous_placement(world) == r].sum() for r in range(world)])
+        assert load.max() <= contiguous.max() + 1e-12
+        assert load.max() / load.mean() < 1.25
+    assert (EP.balanced_placement(popularity, 8) == EP.balanced_placement(popularity, 8)).all()
+
+
+def test_plan_is_a_stable_sort_by_destination():
+    g = torch.Generator().manual_seed(5)
+    ids = torch.stack([torch.randperm(64, generator=g)[:8] for _ in range(40)]).to(torch.int32)
+    owner = torch.from_numpy(EP.contiguous_placement(4).astype(np.int64))
+    plan = EP.make_plan(ids.reshape(-1), owner, 4)
+    dest = owner[ids.reshape(-1).long()]
+    sent = dest[plan.order.long()]
+    assert (sent[1:] >= sent[:-1]).all()
+    for r in range(4):
+        mine = plan.order[sent == r]
+        assert (mine[1:] > mine[:-1]).all()  # stable: ascending pair order inside a destination
+    assert plan.send_counts.tolist() == torch.bincount(dest, minlength=4).tolist()
+    assert (plan.order[plan.position.long()] == torch.arange(320, dtype=torch.int32)).all()
+    assert (plan.send_ids == ids.reshape(-1)[plan.order.long()]).all()
+
+
+class HostBackend:
+    """pack / experts / combine on the CPU through the oracle (test infrastructure)."""
+
+    def __init__(self, oracle, host, hidden, inter, rate):
+        self.o, self.host, self.hidden, self.inter, self.rate = oracle, host, hidden, inter, rate
+        self.silu = oracle.silu_table().astype(np.uint32)
+
+    @staticmethod
+    def bits(x):
+        return (np.ascontiguousarray(x, dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)
+
+    @staticmethod
+    def values(b):
+        return (np.asarray(b).astype(np.uint32) << 16).view(np.float32)
+
+    def pack(self, plan, normalized):
+        rows = normalized.numpy()[plan.order.numpy() >> 3]
+        return torch.from_numpy(self.bits(rows).view(np.int16))
+
+    def experts(self, layer, rows, ids):
+        x = self.values(rows.numpy().view(np.uint16))
+        out = np.empty((x.shape[0], self.hidden), np.float32)
+        for r, e in enumerate(ids.tolist()):
+            m = [self.o.matrix(*self.host.get(layer, e, part), *((self.hidden, self.inter) if part == 2 else (self.inter, self.hidden)),
+                               self.rate) for part in range(3)]
+            gate, _ = self.o.linear(m[0], x[r])
+            up, _ = self.o.linear(m[1], x[r])
+            act = O.bf16_round(self.values(self.silu[self.bits(gate)]) * up)
+            out[r], _ = self.o.linear(m[2], act)
+        return torch.from_numpy(self.bits(out).view(np.int16))
+
+    def combine(self, plan, returned, routing, x):
+        down = self.values(returned.numpy().view(np.uint16))[plan.position.numpy()].reshape(x.shape[0], 8, self.hidden)
+        w = routing.numpy().reshape(-1, 8)
+        total = np.zeros_like(x.numpy())
+        for s in range(8):
+            total = O.bf16_round(total + O.bf16_round(down[:, s] * w[:, s:s + 1]))
+        x.copy_(torch.from_numpy(O.bf16_round(x.numpy() + total)))
+
+
+def _inputs(oracle, rank, tokens, hidden):
+    rng = np.random.default_rng(100 + rank)
+    x = O.bf16_round(rng.standard_normal((tokens, hidden)).astype(np.float32))
+    ids, w, bad = oracle.route(O.bf16_round(rng.standard_normal((tokens, 64)).astype(np.float32)))
+    assert not bad
+    return x, ids, w
+
+
+def _gloo_rank(rank, world, port, results):
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        oracle = O.COracle()
+        hidden, inter, tokens = 256, 128, 6
+        host = O.HostMatrices(1, hidden, inter, 4, seed=21)
+        x, ids, w = _inputs(oracle, rank, tokens, hidden)
+        popularity = np.arange(1, 65, dtype=np.float64) ** -1.1
+        ep = EP.ExpertParallelPrefill(HostBackend(oracle, host, hidden, inter, 4), EP.GroupExchange(),
+                                      EP.balanced_placement(popularity, world))
+        got = torch.from_numpy(x.copy())
+        ep.layer(0, torch.from_numpy(ids.reshape(-1)), torch.from_numpy(w.reshape(-1)), torch.from_numpy(x), got)
+        want, bad = oracle.moe_layer(host.table, 0, ids, w, x, hidden, inter)
+        results.put((rank, bool(not bad and np.array_equal(got.numpy(), want)), float(np.abs(got.numpy() - want).max())))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_two_gloo_ranks_equal_the_single_process_layer():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    port = 29650 + (threading.get_native_id() % 200)
+    procs = [ctx.Process(target=_gloo_rank, args=(r, 2, port, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    got = sorted(results.get(timeout=5) for _ in range(2))
+    assert [g[:2] for g in got] == [(0, True), (1, True)], got
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4])
+def test_ranks_on_one_gpu_equal_the_single_gpu_prefill(oracle, gpu, world):
+    from padra_b200.experts import ExpertKernels, ExpertTable
+
+    hidden, inter, tokens, rate = 512, 256, 40, 4
+    host = O.HostMatrices(1, hidden, inter, rate, seed=33)
+    table = ExpertTable(1, hidden, inter, rate, gpu).fill_from_host(host)
+    hub = EP.LoopbackHub(world)
+    popularity = np.arange(1, 65, dtype=np.float64) ** -1.1
+    owner = EP.balanced_placement(popularity, world)
+    kernels = [ExpertKernels(table) for _ in range(world)]
+    inputs = [_inputs(oracle, r, tokens, hidden) for r in range(world)]
+    outputs, errors = [None] * world, []
+
+    def run(rank):
+        try:
+            torch.cuda.set_device(gpu)
+            x, ids, w = inputs[rank]
+            ep = EP.ExpertParallelPrefill(EP.KernelBackend(kernels[rank]), EP.LoopbackExchange(hub, rank), owner)
+            got = torch.from_numpy(x.copy()).to(gpu)
+            ep.layer(0, torch.from_numpy(ids.reshape(-1)).to(gpu), torch.from_numpy(w.reshape(-1)).to(gpu),
+                     torch.from_numpy(x).to(gpu), got)
+            outputs[rank] = got
+        except Exception as e:  # a failing rank must not leave the others at the barrier
+            errors.append(e)
+            hub.barrier.abort()
+
+    threads = [threading.Thread(target=run, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=120)
+    assert not errors, errors
+    torch.cuda.synchronize()
+    for rank in range(world):
+        x, ids, w = inputs[rank]
+        want = torch.from_numpy(x.copy()).to(gpu)
+        kernels[rank].prefill_layer(0, torch.from_numpy(ids.reshape(-1)).to(gpu), torch.from_numpy(w.reshape(-1)).to(gpu),
+                                    torch.from_numpy(x).to(gpu), want, tokens)
+        torch.cuda.synchronize()
+        assert kernels[rank].bad_flag() == 0
+        assert np.array_equal(outputs[rank].cpu().numpy(), want.cpu().numpy()), f"rank {rank} differs from the single-GPU path"
