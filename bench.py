@@ -196,6 +196,63 @@ def prefill_leg(k, dev, layers: int, tokens: int = 2048, passes: int = 3) -> dic
             "kernels_per_chunk": 9, "layers_rotated": layers, "passes": passes}
 
 
+def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, batch: int = 16384, chunk: int = 2048) -> dict:
+    """configs[4]: a batch of 16384 tokens through `layers` MoE layers, experts sharded 64/world per rank by measured
+    popularity, tokens split evenly over the ranks (strong scaling), all-to-all dispatch and combine per layer and
+    chunk.  Between layers the next input is the RMS-normalised residual stream, so layer l+1 depends on layer l.
+    Returns this rank's device time; the caller takes the maximum over ranks."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from padra_b200 import expert_parallel as EP
+    from padra_b200.experts import bf16_values, zipf_routing
+
+    local = batch // world
+    if world > 1 and local <= chunk:
+        chunk = local // 2  # at least two chunks per rank, so that exchange and expert work overlap
+    chunks = [(c, min(chunk, local - c)) for c in range(0, local, chunk)]
+    g = torch.Generator(device=dev)
+    g.manual_seed(500 + rank)
+    x0 = bf16_values(torch.randn((local, HIDDEN), device=dev, generator=g))
+    routing, owners = {}, []
+    for layer in range(layers):
+        sample, _ = zipf_routing(2048, seed=layer, device="cpu", popularity_seed=layer)
+        popularity = np.bincount(sample.reshape(-1).numpy(), minlength=EXPERTS)
+        owners.append(EP.balanced_placement(popularity, world))
+        for c, n in chunks:
+            ids, w = zipf_routing(n, seed=10007 * layer + (rank * local + c) // chunk + 1, device=dev, popularity_seed=layer)
+            routing[layer, c] = (ids.reshape(-1), w.reshape(-1))
+    engines = None
+    if world > 1:
+        backend, exchange = EP.KernelBackend(k), EP.GroupExchange()
+        engines = [EP.ExpertParallelPrefill(backend, exchange, owners[layer]) for layer in range(layers)]
+
+    def normalise(rows):
+        return bf16_values(rows * torch.rsqrt(rows.square().mean(dim=-1, keepdim=True) + 1e-6))
+
+    def stack(x):
+        for layer in range(layers):
+            if engines is None:
+                for c, n in chunks:
+                    rows = x[c:c + n]
+                    k.prefill_layer(layer, *routing[layer, c], normalise(rows), rows, n)
+            else:  # all of the layer's chunks in one pipelined call
+                engines[layer].layer_chunks(layer, [(*routing[layer, c], normalise(x[c:c + n]), x[c:c + n]) for c, n in chunks])
+
+    stack(x0.clone())  # warm-up: workspaces, NCCL channels
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
+    x = x0.clone()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    stack(x)
+    b.record()
+    torch.cuda.synchronize(dev)
+    assert k.bad_flag() == 0 and bool(torch.isfinite(x).all()), "expert-parallel prefill raised the error flag"
+    return {"seconds": a.elapsed_time(b) / 1e3, "batch": batch, "layers": layers, "chunk": chunk}
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -344,10 +401,13 @@ def run_ours(args):
     e2e_seconds = time.perf_counter() - t0
     barrier()
 
+    ep = expert_parallel_leg(k, dev, world, rank, layers) if EXPERTS % world == 0 and not args.no_ep else None
     if world > 1:
-        t = torch.tensor([seconds, e2e_seconds], device=dev, dtype=torch.float64)
+        t = torch.tensor([seconds, e2e_seconds, ep["seconds"] if ep else 0.0], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         seconds, e2e_seconds = float(t[0]), float(t[1])
+        if ep:
+            ep["seconds"] = float(t[2])
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -381,6 +441,14 @@ def run_ours(args):
         "clocks": {"sm_mhz": clock_info["sm_mhz"], "sm_max_mhz": clock_info["sm_max_mhz"], "reasons": clock_info["reasons"],
                    "samples": clock_info["samples"]},
     }
+    if ep:
+        flops = ep["batch"] * TOPK * 3 * 2 * HIDDEN * INTER * ep["layers"]
+        line["expert_parallel_prefill"] = {
+            "workload": f"configs[4]: {ep['batch']}-token batch through {ep['layers']} K{RATE} MoE layers, experts sharded 64/{world} per GPU "
+                        "by measured popularity, Zipf(1.1) routing, NCCL all-to-all dispatch and combine" if world > 1 else
+                        f"configs[4] at one GPU: {ep['batch']}-token batch through {ep['layers']} K{RATE} MoE layers in chunks of {ep['chunk']}",
+            "n_gpus": world, "scaling": "strong", "tokens_per_s": ep["batch"] / ep["seconds"], "ms_per_batch": ep["seconds"] * 1e3,
+            "tflops_all_gpus": flops / ep["seconds"] / 1e12, "timing": "CUDA events on each rank, maximum over ranks"}
     if world == 1:
         line["prefill_chunk"] = prefill_leg(k, dev, layers)
         assert k.bad_flag() == 0, "the sticky error flag was raised during the prefill leg"
@@ -402,6 +470,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=56)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-ep", action="store_true", help="skip the expert-parallel prefill leg")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers of distinct weights to rotate over (profiling: fewer)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -135,14 +135,19 @@ PADRA_API int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer,
  * The reference runs on one GPU; these four entry points are what a host needs around an all-to-all exchange when the
  * 64 experts of a layer are spread over several GPUs (the exchange itself is the host's: NCCL).  Arithmetic is that
  * of the single-GPU prefill path; rows travel as BF16, which is what the projections read and write anyway.
+ *   padra_ep_plan: the send plan of a rank, a stable sort of its pairs by destination owner[ids[pair]] (owner[64] on
+ *     the device, ranks 0..world-1, world <= 8): order[j] = pair sent as row j, position[pair] = row at which the pair's
+ *     result returns, send_ids[j] = expert id of row j, send_counts[r] = rows for rank r.
  *   padra_ep_pack_rows: packed[j] = BF16 bits of activations[order[j]/8], j < rows = tokens*8; order lists the
  *     (token*8+slot) pairs in the order in which they are sent (sorted by destination rank).
  *   padra_ep_group_rows: fast_expert::Group for received rows: ids[rows] are expert ids 0..63 (any number of rows
  *     per expert, up to group_stride), groups[e*group_stride + n] = n-th row of expert e in ascending row order.
  *   padra_exl3_prefill_rows_launch: padra_exl3_prefill_launch's tensor-memory GEMM with one BF16 input row per pair
  *     (parts 0, 1: input_rows [rows][hidden]; part 2: gate/up [rows][inter]); output [rows][out] BF16 bits in row
- *     order; transformed is workspace of rows*max(hidden, inter) halves.  rows <= 16384.
+ *     order; transformed is workspace of rows*max(hidden, inter) halves.  rows <= 32768.
  *   padra_ep_combine: padra_combine_packed with the down row of pair p at down_rows[position[p]]. */
+PADRA_API int padra_ep_plan(const int *ids, const int *owner, int *order, int *position, int *send_ids,
+                            long long *send_counts, int pairs, int world, int *bad, padra_stream stream);
 PADRA_API int padra_ep_pack_rows(const float *activations, const int *order, unsigned short *packed, int rows, int hidden,
                                  int *bad, padra_stream stream);
 PADRA_API int padra_ep_group_rows(const int *ids, int *groups, int *counts, int rows, int group_stride, int *bad,

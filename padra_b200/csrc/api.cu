@@ -121,6 +121,11 @@ int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer, int part,
                               bad, S(stream), rate, hidden, inter);
 }
 
+int padra_ep_plan(const int *ids, const int *owner, int *order, int *position, int *send_ids, long long *send_counts, int pairs,
+                  int world, int *bad, padra_stream stream) {
+  return LaunchPlan(ids, owner, order, position, send_ids, send_counts, pairs, world, bad, S(stream));
+}
+
 int padra_ep_pack_rows(const float *activations, const int *order, unsigned short *packed, int rows, int hidden, int *bad,
                        padra_stream stream) {
   return LaunchPackRows(activations, order, packed, rows, hidden, bad, S(stream));

@@ -12,7 +12,8 @@
 namespace padra {
 namespace {
 
-constexpr int kMaxRows = 2048 * kTopK;
+constexpr int kMaxRows = 4096 * kTopK; // rows one grouped-projection call takes (received rows may exceed a rank's own)
+constexpr int kMaxRanks = 8;
 
 // One CTA per expert walks the rows in order and appends those routed to it (stable, like GroupKernel).  `ids` are
 // expert ids 0..63 per row; experts this rank does not own simply get no rows.
@@ -55,6 +56,70 @@ __global__ void __launch_bounds__(256) GroupRowsKernel(const int *ids, int *grou
   }
 }
 
+// The send plan of one rank, one CTA: a stable counting sort of the pairs by destination rank owner[ids[pair]].
+//   order[j]      pair that travels as row j          position[pair]  row at which the pair's result comes back
+//   send_ids[j]   expert id of row j                  send_counts[r]  rows for rank r (64-bit, as the host API wants)
+// Thread t owns the 16 consecutive pairs from 16*t on; a scan over (destination, thread) keeps the order stable.
+__global__ void __launch_bounds__(1024) PlanKernel(const int *ids, const int *owner, int *order, int *position, int *send_ids,
+                                                   long long *send_counts, int pairs, int world, int *bad) {
+  __shared__ int s_owner[kExperts], s_scan[kMaxRanks][1024 + 1], s_base[kMaxRanks + 1];
+  const int t = threadIdx.x, per = (pairs + 1023) / 1024, first = t * per;
+  if (t < kExperts)
+    s_owner[t] = owner[t];
+  __syncthreads();
+  int mine[kMaxRanks] = {};
+  for (int i = 0; i < per; ++i) {
+    const int pair = first + i;
+    if (pair < pairs) {
+      const int e = ids[pair];
+      const int r = (e >= 0 && e < kExperts) ? s_owner[e] : -1;
+      if (r < 0 || r >= world)
+        Raise(bad);
+      else
+        ++mine[r];
+    }
+  }
+  for (int r = 0; r < world; ++r)
+    s_scan[r][t] = mine[r];
+  __syncthreads();
+  if (t < world) { // one thread per destination: exclusive scan over the 1024 threads' counts
+    int sum = 0;
+    for (int i = 0; i < 1024; ++i) {
+      const int v = s_scan[t][i];
+      s_scan[t][i] = sum;
+      sum += v;
+    }
+    s_scan[t][1024] = sum;
+  }
+  __syncthreads();
+  if (t == 0) {
+    int sum = 0;
+    for (int r = 0; r < world; ++r) {
+      s_base[r] = sum;
+      sum += s_scan[r][1024];
+      send_counts[r] = s_scan[r][1024];
+    }
+    s_base[world] = sum;
+  }
+  __syncthreads();
+  int cursor[kMaxRanks];
+  for (int r = 0; r < world; ++r)
+    cursor[r] = s_base[r] + s_scan[r][t];
+  for (int i = 0; i < per; ++i) {
+    const int pair = first + i;
+    if (pair < pairs) {
+      const int e = ids[pair];
+      const int r = (e >= 0 && e < kExperts) ? s_owner[e] : -1;
+      if (r >= 0 && r < world) {
+        const int at = cursor[r]++;
+        order[at] = pair, send_ids[at] = e, position[pair] = at;
+      } else {
+        position[pair] = 0;
+      }
+    }
+  }
+}
+
 // packed[j] = BF16 bits of activations[order[j] / 8]: order[j] is the (token*8+slot) pair that travels as row j.
 __global__ void __launch_bounds__(256) PackRowsKernel(const float *activations, const int *order, unsigned short *packed, int rows,
                                                       int hidden, int *bad) {
@@ -80,12 +145,12 @@ __global__ void __launch_bounds__(256) PackRowsKernel(const float *activations, 
 
 // The combine of src/cuda/expert_exl3_prefill_packed_activations.cuh:86-103 with the down row of pair p found at
 // down_rows[position[p]]: x[t] = B(x[t] + sum), sum = B(sum + B(down * w)) over the eight slots in order.
-__global__ void CombineIndexedKernel(float *x, const unsigned short *down_rows, const int *position, const float *weights, int tokens,
-                                     int hidden, int *bad, bool residual) {
-  const int token = blockIdx.y, col = blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void __launch_bounds__(128) CombineIndexedKernel(float *x, const unsigned short *down_rows, const int *position,
+                                                            const float *weights, int tokens, int hidden, int *bad, bool residual) {
+  const int token = blockIdx.y, col = (blockIdx.x * blockDim.x + threadIdx.x) * 4; // four columns per thread
   if (token >= tokens || col >= hidden)
     return;
-  float sum = 0.f;
+  float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int s = 0; s < kTopK; ++s) {
     const int at = position[token * kTopK + s];
@@ -93,14 +158,24 @@ __global__ void CombineIndexedKernel(float *x, const unsigned short *down_rows, 
       Raise(bad);
       return;
     }
-    const float d = FromBF16Bits(down_rows[static_cast<size_t>(at) * hidden + col]);
-    sum = RoundBF16(__fadd_rn(sum, RoundBF16(__fmul_rn(d, weights[token * kTopK + s]))));
+    const uint2 bits = *reinterpret_cast<const uint2 *>(down_rows + static_cast<size_t>(at) * hidden + col);
+    const float w = weights[token * kTopK + s];
+    const float d[4] = {FromBF16Bits(bits.x & 0xffffu), FromBF16Bits(bits.x >> 16), FromBF16Bits(bits.y & 0xffffu),
+                        FromBF16Bits(bits.y >> 16)};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      sum[j] = RoundBF16(__fadd_rn(sum[j], RoundBF16(__fmul_rn(d[j], w))));
   }
-  const size_t i = static_cast<size_t>(token) * hidden + col;
-  const float v = residual ? RoundBF16(__fadd_rn(x[i], sum)) : sum;
-  if (!isfinite(v))
+  float4 *target = reinterpret_cast<float4 *>(x + static_cast<size_t>(token) * hidden + col);
+  const float4 old = *target;
+  float4 v;
+  v.x = residual ? RoundBF16(__fadd_rn(old.x, sum[0])) : sum[0];
+  v.y = residual ? RoundBF16(__fadd_rn(old.y, sum[1])) : sum[1];
+  v.z = residual ? RoundBF16(__fadd_rn(old.z, sum[2])) : sum[2];
+  v.w = residual ? RoundBF16(__fadd_rn(old.w, sum[3])) : sum[3];
+  if (!isfinite(v.x) || !isfinite(v.y) || !isfinite(v.z) || !isfinite(v.w))
     Raise(bad);
-  x[i] = v;
+  *target = v;
 }
 
 } // namespace
@@ -109,6 +184,15 @@ int LaunchGroupRows(const int *ids, int *groups, int *counts, int rows, int grou
   if (!ids || !groups || !counts || !bad || rows < 1 || rows > kMaxRows || group_stride < 1 || group_stride > rows)
     return PADRA_INVALID_ARGUMENT;
   GroupRowsKernel<<<kExperts, 256, 0, stream>>>(ids, groups, counts, rows, group_stride, bad);
+  return CudaStatus(cudaGetLastError());
+}
+
+int LaunchPlan(const int *ids, const int *owner, int *order, int *position, int *send_ids, long long *send_counts, int pairs,
+               int world, int *bad, cudaStream_t stream) {
+  if (!ids || !owner || !order || !position || !send_ids || !send_counts || !bad || pairs < 1 || pairs > 2048 * kTopK ||
+      world < 1 || world > kMaxRanks)
+    return PADRA_INVALID_ARGUMENT;
+  PlanKernel<<<1, 1024, 0, stream>>>(ids, owner, order, position, send_ids, send_counts, pairs, world, bad);
   return CudaStatus(cudaGetLastError());
 }
 
@@ -124,9 +208,10 @@ int LaunchPackRows(const float *activations, const int *order, unsigned short *p
 
 int LaunchCombineIndexed(float *x, const unsigned short *down_rows, const int *position, const float *weights, int tokens,
                          int *bad, int residual, int hidden, cudaStream_t stream) {
-  if (!x || !down_rows || !position || !weights || !bad || tokens < 1 || hidden < 1)
+  if (!x || !down_rows || !position || !weights || !bad || tokens < 1 || hidden < 4 || (hidden % 4) ||
+      reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(down_rows) % 8)
     return PADRA_INVALID_ARGUMENT;
-  CombineIndexedKernel<<<dim3((hidden + 127) / 128, tokens), 128, 0, stream>>>(x, down_rows, position, weights, tokens, hidden, bad,
+  CombineIndexedKernel<<<dim3((hidden / 4 + 127) / 128, tokens), 128, 0, stream>>>(x, down_rows, position, weights, tokens, hidden, bad,
                                                                                 residual != 0);
   return CudaStatus(cudaGetLastError());
 }

@@ -41,6 +41,8 @@ int LaunchPrefillRows(const Matrix *matrices, int layer, int part, const int *gr
                       const unsigned short *input_rows, unsigned short *output, const unsigned short *gate,
                       const unsigned short *up, const unsigned short *table, void *transformed, int *bad, cudaStream_t stream,
                       int rate, int hidden, int inter);
+int LaunchPlan(const int *ids, const int *owner, int *order, int *position, int *send_ids, long long *send_counts, int pairs,
+               int world, int *bad, cudaStream_t stream);
 int LaunchGroupRows(const int *ids, int *groups, int *counts, int rows, int group_stride, int *bad, cudaStream_t stream);
 int LaunchPackRows(const float *activations, const int *order, unsigned short *packed, int rows, int hidden, int *bad,
                    cudaStream_t stream);

@@ -45,7 +45,8 @@ constexpr int kMmaWarp = kEpilogueWarps;
 constexpr int kFirstProducerWarp = kMmaWarp + 1;
 constexpr int kPrefillThreads = (kEpilogueWarps + 1 + kProducerSets * kWarpsPerSet) * 32; // 672
 constexpr int kTmemColumns = 512;                   // two accumulators of 256 columns
-constexpr int kMaxTiles = kExperts + 64;            // sum over experts of ceil(n_e / 256) for up to 2048 tokens
+constexpr int kMaxPairs = 4096 * kTopK;              // pairs (rows) one call takes
+constexpr int kMaxTiles = kExperts + kMaxPairs / kMaxTileN; // sum over experts of ceil(n_e / 256)
 constexpr int kAhead = 3;                           // own stages of packed words in flight per producer lane
 constexpr unsigned long long kWaitLimitNs = 1000000000ull; // a wait that lasts a second has failed
 constexpr int kMaxTokensPrefill = 2048;
@@ -644,7 +645,7 @@ static int LaunchPrefillGemm(const Matrix *matrices, int layer, int part, const 
                              const unsigned short *pair_rows, unsigned short *output, const unsigned short *gate,
                              const unsigned short *up, const unsigned short *table, void *transformed, int group_stride, int pairs,
                              int *bad, cudaStream_t stream, int rate, int hidden, int inter) {
-  if (pairs < 1 || pairs > kMaxTokensPrefill * kTopK || group_stride < 1 || group_stride > pairs || !transformed)
+  if (pairs < 1 || pairs > kMaxPairs || group_stride < 1 || group_stride > pairs || !transformed)
     return PADRA_INVALID_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(output) % 16 || reinterpret_cast<uintptr_t>(transformed) % 16)
     return PADRA_INVALID_ARGUMENT;

@@ -24,7 +24,7 @@ import torch
 import torch.distributed as dist
 
 EXPERTS, TOPK = 64, 8
-MAX_ROWS = 2048 * TOPK  # rows one grouped-projection call takes
+MAX_ROWS = 4096 * TOPK  # rows one grouped-projection call takes (a rank may receive more rows than it sends)
 
 
 def balanced_placement(popularity, world: int) -> np.ndarray:
@@ -81,6 +81,14 @@ class GroupExchange:
         both = torch.stack([send_counts, recv]).cpu()
         return both[0].tolist(), both[1].tolist()
 
+    def counts_many(self, send_counts: torch.Tensor):
+        """send_counts [chunks][world] -> (send split lists, receive split lists), one host synchronisation."""
+        recv = torch.empty_like(send_counts)
+        for i in range(send_counts.shape[0]):
+            dist.all_to_all_single(recv[i], send_counts[i], group=self.group)
+        both = torch.stack([send_counts, recv]).cpu()
+        return both[0].tolist(), both[1].tolist()
+
     def rows(self, send: torch.Tensor, send_splits, recv_splits) -> torch.Tensor:
         """Rows travel as bytes: every backend moves uint8, not every backend knows 16-bit integer types."""
         width = send[0].numel() * send.element_size() if send.dim() > 1 else send.element_size()
@@ -109,15 +117,31 @@ class LoopbackExchange:
         self.hub, self.rank, self.world = hub, rank, hub.world
 
     def _swap(self, pieces):
-        self.hub.slots[self.rank] = pieces
+        """pieces[destination] -> [piece from every source].  On a GPU the pieces come with an event of the sending
+        thread's stream, which the receiving thread's stream waits for."""
+        event = None
+        if torch.cuda.is_available() and any(torch.is_tensor(p) and p.is_cuda for p in pieces):
+            event = torch.cuda.Event()
+            event.record(torch.cuda.current_stream())
+        self.hub.slots[self.rank] = (pieces, event)
         self.hub.barrier.wait()
-        got = [self.hub.slots[source][self.rank] for source in range(self.world)]
+        got = []
+        for source in range(self.world):
+            theirs, their_event = self.hub.slots[source]
+            if their_event is not None:
+                torch.cuda.current_stream().wait_event(their_event)
+            got.append(theirs[self.rank])
         self.hub.barrier.wait()
         return got
 
     def counts(self, send_counts: torch.Tensor):
         mine = [int(v) for v in send_counts.tolist()]
         return mine, self._swap(mine)
+
+    def counts_many(self, send_counts: torch.Tensor):
+        mine = [[int(v) for v in row] for row in send_counts.tolist()]
+        theirs = self._swap([[row[d] for row in mine] for d in range(self.world)])  # theirs[source][chunk]
+        return mine, [[theirs[source][c] for source in range(self.world)] for c in range(len(mine))]
 
     def rows(self, send: torch.Tensor, send_splits, recv_splits) -> torch.Tensor:
         as_bytes = send.contiguous().view(torch.uint8).reshape(send.shape[0], -1)
@@ -146,6 +170,15 @@ class KernelBackend:
                               up=torch.empty((MAX_ROWS, i), dtype=torch.uint16, device=dev),
                               transformed=torch.empty((MAX_ROWS, max(h, i)), dtype=torch.float16, device=dev))
         return self._work
+
+    def plan(self, ids: torch.Tensor, owner: torch.Tensor, world: int) -> Plan:
+        """make_plan in one kernel (padra_ep_plan); owner is int32 [64] on the device."""
+        B, pairs, dev = self.B, ids.numel(), self.device
+        order, position, send_ids = (torch.empty(pairs, dtype=torch.int32, device=dev) for _ in range(3))
+        counts = torch.empty(world, dtype=torch.int64, device=dev)
+        B.check(self.lib.padra_ep_plan(B.ptr(ids), B.ptr(owner), B.ptr(order), B.ptr(position), B.ptr(send_ids), B.ptr(counts),
+                                       pairs, world, B.ptr(self.k.bad), B.stream_handle()), "padra_ep_plan")
+        return Plan(order, position, send_ids, counts)
 
     def pack(self, plan: Plan, normalized: torch.Tensor) -> torch.Tensor:
         B, rows = self.B, plan.order.numel()
@@ -184,16 +217,22 @@ class ExpertParallelPrefill:
         self.backend, self.exchange = backend, exchange
         self.owner_host = np.asarray(owner, dtype=np.int32)
         self._owner = {}
+        self._comm_stream = None
 
-    def owner_on(self, device) -> torch.Tensor:
-        if device not in self._owner:
-            self._owner[device] = torch.from_numpy(self.owner_host.astype(np.int64)).to(device)
-        return self._owner[device]
+    def owner_on(self, device, dtype=torch.int64) -> torch.Tensor:
+        if (device, dtype) not in self._owner:
+            self._owner[device, dtype] = torch.from_numpy(self.owner_host.astype(np.int64)).to(device=device, dtype=dtype)
+        return self._owner[device, dtype]
+
+    def _plan(self, ids: torch.Tensor) -> Plan:
+        if hasattr(self.backend, "plan"):
+            return self.backend.plan(ids, self.owner_on(ids.device, torch.int32), self.exchange.world)
+        return make_plan(ids, self.owner_on(ids.device), self.exchange.world)
 
     def layer(self, layer: int, ids: torch.Tensor, routing: torch.Tensor, normalized: torch.Tensor, x: torch.Tensor) -> None:
         """ids/routing [tokens*8], normalized/x [tokens][hidden] (FP32 holding BF16 values); x updated in place."""
         ex = self.exchange
-        plan = make_plan(ids, self.owner_on(ids.device), ex.world)
+        plan = self._plan(ids)
         packed = self.backend.pack(plan, normalized)
         send_splits, recv_splits = ex.counts(plan.send_counts)
         rows = ex.rows(packed, send_splits, recv_splits)
@@ -201,3 +240,63 @@ class ExpertParallelPrefill:
         down = self.backend.experts(layer, rows, row_ids) if rows.shape[0] else rows
         returned = ex.rows(down, recv_splits, send_splits)
         self.backend.combine(plan, returned, routing, x)
+
+    def layer_chunks(self, layer: int, chunks) -> None:
+        """The same for several chunks [(ids, routing, normalized, x), ...] of this rank's tokens (every rank passes the
+        same number of chunks), software-pipelined over two CUDA streams: while the experts of chunk i run, the rows of
+        chunk i+1 arrive and the results of chunk i-1 leave.  One host synchronisation per call (the split sizes of
+        all chunks travel together)."""
+        ex, be = self.exchange, self.backend
+        compute = torch.cuda.current_stream()
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=compute.device)
+        comm = self._comm_stream
+        n = len(chunks)
+        plans, packed = [], []
+        for ids, _, normalized, _ in chunks:
+            plan = self._plan(ids)
+            plans.append(plan)
+            packed.append(be.pack(plan, normalized))
+        ready = torch.cuda.Event()
+        ready.record(compute)
+        with torch.cuda.stream(comm):
+            comm.wait_event(ready)
+            send_splits, recv_splits = ex.counts_many(torch.stack([p.send_counts for p in plans]))  # the one host sync
+        rows, row_ids, down, returned = [None] * n, [None] * n, [None] * n, [None] * n
+        arrived = [torch.cuda.Event() for _ in range(n)]
+        computed = [torch.cuda.Event() for _ in range(n)]
+        back = [torch.cuda.Event() for _ in range(n)]
+
+        def receive(i):
+            with torch.cuda.stream(comm):
+                rows[i] = ex.rows(packed[i], send_splits[i], recv_splits[i])
+                row_ids[i] = ex.rows(plans[i].send_ids, send_splits[i], recv_splits[i])
+                arrived[i].record(comm)
+            for t in (rows[i], row_ids[i]):
+                t.record_stream(compute)
+            packed[i].record_stream(comm)
+            plans[i].send_ids.record_stream(comm)
+
+        def give_back(i):
+            with torch.cuda.stream(comm):
+                comm.wait_event(computed[i])
+                returned[i] = ex.rows(down[i], recv_splits[i], send_splits[i])
+                back[i].record(comm)
+            returned[i].record_stream(compute)
+            down[i].record_stream(comm)
+
+        def combine(i):
+            compute.wait_event(back[i])
+            be.combine(plans[i], returned[i], chunks[i][1], chunks[i][3])
+
+        receive(0)
+        for i in range(n):
+            if i + 1 < n:
+                receive(i + 1)
+            compute.wait_event(arrived[i])
+            down[i] = be.experts(layer, rows[i], row_ids[i]) if rows[i].shape[0] else rows[i]
+            computed[i].record(compute)
+            give_back(i)
+            if i > 0:
+                combine(i - 1)
+        combine(n - 1)

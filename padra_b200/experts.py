@@ -337,12 +337,15 @@ def route_topk(logits: torch.Tensor):
     return ids.to(torch.int32).contiguous(), bf16_values(w).contiguous()
 
 
-def zipf_routing(tokens: int, seed: int, s: float = 1.1, device="cuda"):
+def zipf_routing(tokens: int, seed: int, s: float = 1.1, device="cuda", popularity_seed=None):
     """Routing with Zipf(s)-skewed expert popularity: per token, eight distinct experts sampled without
-    replacement with probability proportional to rank^-s, the expert<->rank map a seeded permutation."""
+    replacement with probability proportional to rank^-s, the expert<->rank map a seeded permutation (seeded by
+    `popularity_seed` when given, so that several chunks can share one popularity order)."""
     g = torch.Generator(device="cpu")
-    g.manual_seed(seed)
+    g.manual_seed(seed if popularity_seed is None else popularity_seed)
     rank = torch.randperm(EXPERTS, generator=g)
+    if popularity_seed is not None:
+        g.manual_seed(seed)
     popularity = torch.empty(EXPERTS)
     popularity[rank] = torch.arange(1, EXPERTS + 1, dtype=torch.float32) ** (-s)
     ids = torch.multinomial(popularity.expand(tokens, EXPERTS), TOPK, replacement=False, generator=g)

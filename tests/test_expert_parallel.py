@@ -131,8 +131,8 @@ def test_two_gloo_ranks_equal_the_single_process_layer():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("world", [2, 4])
-def test_ranks_on_one_gpu_equal_the_single_gpu_prefill(oracle, gpu, world):
+@pytest.mark.parametrize("world,chunks", [(2, 1), (4, 1), (2, 3), (8, 2)])
+def test_ranks_on_one_gpu_equal_the_single_gpu_prefill(oracle, gpu, world, chunks):
     from padra_b200.experts import ExpertKernels, ExpertTable
 
     hidden, inter, tokens, rate = 512, 256, 40, 4
@@ -142,6 +142,7 @@ def test_ranks_on_one_gpu_equal_the_single_gpu_prefill(oracle, gpu, world):
     popularity = np.arange(1, 65, dtype=np.float64) ** -1.1
     owner = EP.balanced_placement(popularity, world)
     kernels = [ExpertKernels(table) for _ in range(world)]
+    tokens *= chunks
     inputs = [_inputs(oracle, r, tokens, hidden) for r in range(world)]
     outputs, errors = [None] * world, []
 
@@ -151,8 +152,13 @@ def test_ranks_on_one_gpu_equal_the_single_gpu_prefill(oracle, gpu, world):
             x, ids, w = inputs[rank]
             ep = EP.ExpertParallelPrefill(EP.KernelBackend(kernels[rank]), EP.LoopbackExchange(hub, rank), owner)
             got = torch.from_numpy(x.copy()).to(gpu)
-            ep.layer(0, torch.from_numpy(ids.reshape(-1)).to(gpu), torch.from_numpy(w.reshape(-1)).to(gpu),
-                     torch.from_numpy(x).to(gpu), got)
+            dids, dw, dx = torch.from_numpy(ids.reshape(-1)).to(gpu), torch.from_numpy(w.reshape(-1)).to(gpu), torch.from_numpy(x).to(gpu)
+            if chunks == 1:
+                ep.layer(0, dids, dw, dx, got)
+            else:  # the pipelined form: several chunks, two streams
+                n = tokens // chunks
+                ep.layer_chunks(0, [(dids[8 * n * c:8 * n * (c + 1)], dw[8 * n * c:8 * n * (c + 1)], dx[n * c:n * (c + 1)],
+                                     got[n * c:n * (c + 1)]) for c in range(chunks)])
             outputs[rank] = got
         except Exception as e:  # a failing rank must not leave the others at the barrier
             errors.append(e)
