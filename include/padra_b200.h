@@ -144,8 +144,34 @@ PADRA_API int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer,
  *     per expert, up to group_stride), groups[e*group_stride + n] = n-th row of expert e in ascending row order.
  *   padra_exl3_prefill_rows_launch: padra_exl3_prefill_launch's tensor-memory GEMM with one BF16 input row per pair
  *     (parts 0, 1: input_rows [rows][hidden]; part 2: gate/up [rows][inter]); output [rows][out] BF16 bits in row
- *     order; transformed is workspace of rows*max(hidden, inter) halves.  rows <= 32768.
+ *     order (row indices may be sparse, up to 2^20; at most 32768 rows may be grouped); transformed is workspace of
+ *     32768*max(hidden, inter) halves at most.
  *   padra_ep_combine: padra_combine_packed with the down row of pair p at down_rows[position[p]]. */
+/* The exchange done by the GPUs themselves over NVLink peer memory (no host in the loop, no NCCL on the data path).
+ * Every rank owns one exchange block of padra_ep_exchange_bytes(world, cap, hidden, offsets) bytes, zero-filled once,
+ * that every rank has mapped (peer_blocks[r] = address of rank r's block in THIS process, 256-byte aligned); cap is the
+ * most pairs a rank sends per call.  offsets[0..5] = byte offsets of: received rows [world][cap][hidden] BF16, their
+ * expert ids [world][cap], meta, returned rows [cap][hidden] BF16, and the two flag arrays.
+ *   padra_ep_dispatch: padra_ep_pack_rows fused with the transfer: row j of the send order is stored into its owner's
+ *     block, region `rank`; when all rows are out, the row counts and a flag carrying `epoch` follow.
+ *   padra_ep_wait: which = 0 waits until every rank's rows for this call have arrived in `block` (this rank's own),
+ *     which = 1 until every rank has returned this rank's rows; bounded (two seconds), then *bad is set.
+ *   padra_ep_group_received: padra_ep_group_rows over the regions of `block`; row index = source*cap + k.  Pass that
+ *     index space to padra_exl3_prefill_rows_launch: rows = world*cap, input_rows = block + offsets[0].
+ *   padra_ep_return: down rows (same index space) go back into their source's block at the send rows they came
+ *     from, then a flag with `epoch`; after padra_ep_wait(which = 1), padra_ep_combine reads block + offsets[3].
+ * epoch must differ from call to call (count up from 1).  A rank may start call n+1 only after its own combine of call
+ * n has been enqueued on the same stream: that order is what makes reuse of the blocks safe. */
+PADRA_API size_t padra_ep_exchange_bytes(int world, int cap, int hidden, size_t *offsets);
+PADRA_API int padra_ep_dispatch(const float *activations, const int *order, const int *send_ids,
+                                const long long *send_counts, const unsigned long long *peer_blocks, int rank, int world,
+                                int cap, int pairs, int hidden, unsigned epoch, int *bad, padra_stream stream);
+PADRA_API int padra_ep_wait(const void *block, int which, int world, int cap, int hidden, unsigned epoch, int *bad,
+                            padra_stream stream);
+PADRA_API int padra_ep_group_received(const void *block, int world, int cap, int hidden, int *groups, int *counts,
+                                      int group_stride, int *bad, padra_stream stream);
+PADRA_API int padra_ep_return(const unsigned short *down_rows, const unsigned long long *peer_blocks, int rank, int world,
+                              int cap, int hidden, unsigned epoch, int *bad, padra_stream stream);
 PADRA_API int padra_ep_plan(const int *ids, const int *owner, int *order, int *position, int *send_ids,
                             long long *send_counts, int pairs, int world, int *bad, padra_stream stream);
 PADRA_API int padra_ep_pack_rows(const float *activations, const int *order, unsigned short *packed, int rows, int hidden,

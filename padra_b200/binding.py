@@ -37,6 +37,11 @@ SIGNATURES = {
     "padra_exl3_moe_decode_workspace_bytes": ([_i, _i, _i], C.c_size_t),
     "padra_exl3_moe_decode_workspace_init": ([_p, C.c_size_t, _p], _i),
     "padra_exl3_moe_decode_set_trace": ([_p, C.c_size_t], _i),
+    "padra_ep_exchange_bytes": ([_i, _i, _i, _p], C.c_size_t),
+    "padra_ep_dispatch": ([_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, C.c_uint, _p, _p], _i),
+    "padra_ep_wait": ([_p, _i, _i, _i, _i, C.c_uint, _p, _p], _i),
+    "padra_ep_group_received": ([_p, _i, _i, _i, _p, _p, _i, _p, _p], _i),
+    "padra_ep_return": ([_p, _p, _i, _i, _i, _i, C.c_uint, _p, _p], _i),
     "padra_ep_plan": ([_p, _p, _p, _p, _p, _p, _i, _i, _p, _p], _i),
     "padra_ep_pack_rows": ([_p, _p, _p, _i, _i, _p, _p], _i),
     "padra_ep_group_rows": ([_p, _p, _p, _i, _i, _p, _p], _i),

@@ -121,6 +121,30 @@ int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer, int part,
                               bad, S(stream), rate, hidden, inter);
 }
 
+size_t padra_ep_exchange_bytes(int world, int cap, int hidden, size_t *offsets) {
+  return ExchangeBytes(world, cap, hidden, offsets);
+}
+
+int padra_ep_dispatch(const float *activations, const int *order, const int *send_ids, const long long *send_counts,
+                      const unsigned long long *peer_blocks, int rank, int world, int cap, int pairs, int hidden, unsigned epoch,
+                      int *bad, padra_stream stream) {
+  return LaunchDispatch(activations, order, send_ids, send_counts, peer_blocks, rank, world, cap, pairs, hidden, epoch, bad, S(stream));
+}
+
+int padra_ep_wait(const void *block, int which, int world, int cap, int hidden, unsigned epoch, int *bad, padra_stream stream) {
+  return LaunchWaitFlags(block, which, world, cap, hidden, epoch, bad, S(stream));
+}
+
+int padra_ep_group_received(const void *block, int world, int cap, int hidden, int *groups, int *counts, int group_stride, int *bad,
+                            padra_stream stream) {
+  return LaunchGroupRegions(block, world, cap, hidden, groups, counts, group_stride, bad, S(stream));
+}
+
+int padra_ep_return(const unsigned short *down_rows, const unsigned long long *peer_blocks, int rank, int world, int cap, int hidden,
+                    unsigned epoch, int *bad, padra_stream stream) {
+  return LaunchReturn(down_rows, peer_blocks, rank, world, cap, hidden, epoch, bad, S(stream));
+}
+
 int padra_ep_plan(const int *ids, const int *owner, int *order, int *position, int *send_ids, long long *send_counts, int pairs,
                   int world, int *bad, padra_stream stream) {
   return LaunchPlan(ids, owner, order, position, send_ids, send_counts, pairs, world, bad, S(stream));

@@ -6,6 +6,15 @@
 // down rows back, and (5) combines them with the routing weights, reading each pair's row through an index map so
 // that no un-permute pass over the rows is needed.  Arithmetic is that of the single-GPU path: rows cross the wire as
 // BF16, which is exactly what the projections' inputs and outputs hold.
+//
+// Two forms of the exchange exist.  The host can run it (all_to_all_single of packed rows), or the GPUs do it
+// themselves over NVLink peer memory: every rank owns an exchange block that all ranks have mapped, the dispatch
+// kernel converts a pair's activation row to BF16 and stores it straight into the owner rank's block (into the region
+// reserved for this source rank, so no offsets have to be agreed first), and the return kernel stores the down rows
+// straight back into the source's block at the rows it sent them from.  Arrival is announced with one flag per
+// (source, destination) that carries the call's epoch, written after a system-scope fence by the last CTA of the
+// sending kernel; a one-CTA wait kernel on the receiving side polls its own flags, bounded in time.  Nothing in this
+// form touches the host: row counts stay on the device, next to the flags.
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -178,7 +187,288 @@ __global__ void __launch_bounds__(128) CombineIndexedKernel(float *x, const unsi
   *target = v;
 }
 
+// ---- the exchange over peer memory ------------------------------------------------------------------------------
+struct ExchangeLayout {
+  size_t rows, ids, meta, returned, arrived, came_back, tickets, total;
+};
+// One block per rank: rows/ids = what others sent me, region s (cap rows) for source rank s; meta[s] = {rows source s
+// sent me, the send row its first row came from}; returned = the down rows of MY pairs, in my send order;
+// arrived[s] / came_back[d] = epoch flags written by peers; tickets = two CTA counters of my own kernels.
+__host__ __device__ inline ExchangeLayout MakeExchangeLayout(int world, int cap, int hidden) {
+  ExchangeLayout l{};
+  size_t at = 0;
+#define PADRA_ALIGN_256(n) (((n) + 255) & ~static_cast<size_t>(255))
+  l.rows = at, at += PADRA_ALIGN_256(static_cast<size_t>(world) * cap * hidden * 2);
+  l.ids = at, at += PADRA_ALIGN_256(static_cast<size_t>(world) * cap * 4);
+  l.meta = at, at += PADRA_ALIGN_256(static_cast<size_t>(world) * 16);
+  l.returned = at, at += PADRA_ALIGN_256(static_cast<size_t>(cap) * hidden * 2);
+  l.arrived = at, at += PADRA_ALIGN_256(static_cast<size_t>(world) * 4);
+  l.came_back = at, at += PADRA_ALIGN_256(static_cast<size_t>(world) * 4);
+#undef PADRA_ALIGN_256
+  l.tickets = at, at += 256;
+  l.total = at;
+  return l;
+}
+
+struct PeerBlocks {
+  unsigned char *base[kMaxRanks];
+};
+
+constexpr unsigned long long kFlagWaitNs = 2000000000ull;
+
+__device__ __forceinline__ void StoreFlagSystem(unsigned *flag, unsigned value) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
+}
+__device__ __forceinline__ unsigned LoadFlagSystem(const unsigned *flag) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+  return v;
+}
+
+// Fused pack + dispatch: send row j (pair order[j]) goes to rank d = the destination whose range of the send order
+// holds j, as row rank*cap + (j - first row for d) of d's block.
+__global__ void __launch_bounds__(256) DispatchKernel(const float *activations, const int *order, const int *send_ids,
+                                                      const long long *send_counts, PeerBlocks peers, ExchangeLayout layout, int rank,
+                                                      int world, int cap, int pairs, int hidden, unsigned epoch, int *bad) {
+  __shared__ int s_first[kMaxRanks + 1], s_ok, s_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (!threadIdx.x) {
+    int sum = 0, ok = 1;
+    for (int d = 0; d < world; ++d) {
+      const long long c = send_counts[d];
+      s_first[d] = sum;
+      if (c < 0 || c > cap)
+        ok = 0;
+      else
+        sum += static_cast<int>(c);
+    }
+    s_first[world] = sum;
+    s_ok = ok && sum == pairs;
+    if (!s_ok)
+      Raise(bad);
+  }
+  __syncthreads();
+  if (s_ok) {
+    for (int row = blockIdx.x * 8 + warp; row < pairs; row += gridDim.x * 8) {
+      int d = 0;
+      while (d + 1 < world && s_first[d + 1] <= row)
+        ++d;
+      const int pair = order[row];
+      if (pair < 0 || pair >= pairs) {
+        if (!lane)
+          Raise(bad);
+        continue;
+      }
+      const size_t slot = static_cast<size_t>(rank) * cap + (row - s_first[d]);
+      const float *from = activations + static_cast<size_t>(pair >> 3) * hidden;
+      unsigned short *to = reinterpret_cast<unsigned short *>(peers.base[d] + layout.rows) + slot * hidden;
+      for (int k = lane * 8; k < hidden; k += 256) {
+        const float4 a = *reinterpret_cast<const float4 *>(from + k), b = *reinterpret_cast<const float4 *>(from + k + 4);
+        uint4 bits;
+        bits.x = static_cast<unsigned>(BF16Bits(a.x)) | (static_cast<unsigned>(BF16Bits(a.y)) << 16);
+        bits.y = static_cast<unsigned>(BF16Bits(a.z)) | (static_cast<unsigned>(BF16Bits(a.w)) << 16);
+        bits.z = static_cast<unsigned>(BF16Bits(b.x)) | (static_cast<unsigned>(BF16Bits(b.y)) << 16);
+        bits.w = static_cast<unsigned>(BF16Bits(b.z)) | (static_cast<unsigned>(BF16Bits(b.w)) << 16);
+        *reinterpret_cast<uint4 *>(to + k) = bits;
+      }
+      if (!lane)
+        reinterpret_cast<int *>(peers.base[d] + layout.ids)[slot] = send_ids[row];
+    }
+  }
+  // every CTA's stores are fenced before its ticket; the CTA that draws the last ticket announces the rows
+  __threadfence_system();
+  __syncthreads();
+  unsigned *ticket = reinterpret_cast<unsigned *>(peers.base[rank] + layout.tickets);
+  if (!threadIdx.x)
+    s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (s_last && threadIdx.x < world) {
+    const int d = threadIdx.x;
+    int4 meta;
+    meta.x = s_ok ? s_first[d + 1] - s_first[d] : 0, meta.y = s_first[d], meta.z = 0, meta.w = 0;
+    *reinterpret_cast<int4 *>(peers.base[d] + layout.meta + static_cast<size_t>(rank) * 16) = meta;
+    __threadfence_system();
+    StoreFlagSystem(reinterpret_cast<unsigned *>(peers.base[d] + layout.arrived) + rank, epoch);
+    if (!d)
+      *ticket = 0;
+  }
+}
+
+// Poll `world` flags of this rank's own block until each carries `epoch`; give up after kFlagWaitNs.
+__global__ void WaitFlagsKernel(const unsigned *flags, int world, unsigned epoch, int *bad) {
+  if (threadIdx.x >= world)
+    return;
+  unsigned long long started;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(started));
+  while (LoadFlagSystem(flags + threadIdx.x) != epoch) {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (now - started > kFlagWaitNs) {
+      Raise(bad);
+      break;
+    }
+    __nanosleep(200);
+  }
+}
+
+// GroupRowsKernel over the regions of the exchange block: region s holds meta[s].x rows.
+__global__ void __launch_bounds__(256) GroupRegionsKernel(const int *ids, const int4 *meta, int world, int cap, int *groups, int *counts,
+                                                          int stride, int *bad) {
+  const int expert = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __shared__ int warp_counts[8], warp_offsets[8], total;
+  if (!threadIdx.x)
+    total = 0;
+  __syncthreads();
+  for (int s = 0; s < world; ++s) {
+    int n = meta[s].x;
+    if (n < 0 || n > cap) {
+      if (!threadIdx.x && !expert)
+        Raise(bad);
+      n = 0;
+    }
+    for (int base = 0; base < n; base += 256) {
+      const int k = base + threadIdx.x;
+      const int row = s * cap + k;
+      const int id = k < n ? ids[row] : -1;
+      if (k < n && (id < 0 || id >= kExperts) && expert == 0)
+        Raise(bad);
+      const bool mine = id == expert;
+      const unsigned votes = __ballot_sync(0xffffffffu, mine);
+      if (!lane)
+        warp_counts[warp] = __popc(votes);
+      __syncthreads();
+      if (!threadIdx.x) {
+        int at = total;
+        for (int w = 0; w < 8; ++w) {
+          warp_offsets[w] = at;
+          at += warp_counts[w];
+        }
+        total = at;
+      }
+      __syncthreads();
+      if (mine) {
+        const int at = warp_offsets[warp] + __popc(votes & ((1u << lane) - 1u));
+        if (at < stride)
+          groups[static_cast<size_t>(expert) * stride + at] = row;
+      }
+      __syncthreads();
+    }
+  }
+  if (!threadIdx.x) {
+    if (total > stride)
+      Raise(bad);
+    counts[expert] = total < stride ? total : stride;
+  }
+}
+
+// The down rows of region s go back to rank s, to the send rows they came from.
+__global__ void __launch_bounds__(256) ReturnKernel(const unsigned short *down, PeerBlocks peers, ExchangeLayout layout, int rank, int world,
+                                                    int cap, int hidden, unsigned epoch, int *bad) {
+  __shared__ int s_first[kMaxRanks + 1], s_from[kMaxRanks], s_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (!threadIdx.x) {
+    const int4 *meta = reinterpret_cast<const int4 *>(peers.base[rank] + layout.meta);
+    int sum = 0;
+    for (int s = 0; s < world; ++s) {
+      int n = meta[s].x;
+      if (n < 0 || n > cap || meta[s].y < 0 || meta[s].y + n > cap) {
+        Raise(bad);
+        n = 0;
+      }
+      s_first[s] = sum, s_from[s] = meta[s].y;
+      sum += n;
+    }
+    s_first[world] = sum;
+  }
+  __syncthreads();
+  for (int item = blockIdx.x * 8 + warp; item < s_first[world]; item += gridDim.x * 8) {
+    int s = 0;
+    while (s + 1 < world && s_first[s + 1] <= item)
+      ++s;
+    const int k = item - s_first[s];
+    const uint4 *from = reinterpret_cast<const uint4 *>(down + (static_cast<size_t>(s) * cap + k) * hidden);
+    uint4 *to = reinterpret_cast<uint4 *>(reinterpret_cast<unsigned short *>(peers.base[s] + layout.returned) +
+                                          static_cast<size_t>(s_from[s] + k) * hidden);
+    for (int c = lane; c < hidden / 8; c += 32)
+      to[c] = from[c];
+  }
+  __threadfence_system();
+  __syncthreads();
+  unsigned *ticket = reinterpret_cast<unsigned *>(peers.base[rank] + layout.tickets) + 1;
+  if (!threadIdx.x)
+    s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (s_last && threadIdx.x < world) {
+    StoreFlagSystem(reinterpret_cast<unsigned *>(peers.base[threadIdx.x] + layout.came_back) + rank, epoch);
+    if (!threadIdx.x)
+      *ticket = 0;
+  }
+}
+
+bool FillPeers(PeerBlocks &peers, const unsigned long long *bases, int world) {
+  for (int r = 0; r < kMaxRanks; ++r) {
+    peers.base[r] = r < world ? reinterpret_cast<unsigned char *>(static_cast<uintptr_t>(bases[r])) : nullptr;
+    if (r < world && (!peers.base[r] || bases[r] % 256))
+      return false;
+  }
+  return true;
+}
+
 } // namespace
+
+size_t ExchangeBytes(int world, int cap, int hidden, size_t *offsets) {
+  if (world < 1 || world > kMaxRanks || cap < 8 || cap > 2048 * kTopK || hidden < 128 || (hidden % 128))
+    return 0;
+  const ExchangeLayout l = MakeExchangeLayout(world, cap, hidden);
+  if (offsets)
+    offsets[0] = l.rows, offsets[1] = l.ids, offsets[2] = l.meta, offsets[3] = l.returned, offsets[4] = l.arrived, offsets[5] = l.came_back;
+  return l.total;
+}
+
+int LaunchDispatch(const float *activations, const int *order, const int *send_ids, const long long *send_counts,
+                   const unsigned long long *bases, int rank, int world, int cap, int pairs, int hidden, unsigned epoch, int *bad,
+                   cudaStream_t stream) {
+  PeerBlocks peers;
+  if (!activations || !order || !send_ids || !send_counts || !bases || !bad || rank < 0 || rank >= world || pairs < 8 ||
+      pairs > cap || !ExchangeBytes(world, cap, hidden, nullptr) || !FillPeers(peers, bases, world) ||
+      reinterpret_cast<uintptr_t>(activations) % 16)
+    return PADRA_INVALID_ARGUMENT;
+  const int blocks = (pairs + 7) / 8;
+  DispatchKernel<<<blocks < 148 * 4 ? blocks : 148 * 4, 256, 0, stream>>>(activations, order, send_ids, send_counts, peers,
+                                                                          MakeExchangeLayout(world, cap, hidden), rank, world, cap, pairs,
+                                                                          hidden, epoch, bad);
+  return CudaStatus(cudaGetLastError());
+}
+
+int LaunchWaitFlags(const void *block, int which, int world, int cap, int hidden, unsigned epoch, int *bad, cudaStream_t stream) {
+  if (!block || !bad || (which != 0 && which != 1) || !ExchangeBytes(world, cap, hidden, nullptr))
+    return PADRA_INVALID_ARGUMENT;
+  const ExchangeLayout l = MakeExchangeLayout(world, cap, hidden);
+  WaitFlagsKernel<<<1, 32, 0, stream>>>(
+      reinterpret_cast<const unsigned *>(static_cast<const unsigned char *>(block) + (which ? l.came_back : l.arrived)), world, epoch, bad);
+  return CudaStatus(cudaGetLastError());
+}
+
+int LaunchGroupRegions(const void *block, int world, int cap, int hidden, int *groups, int *counts, int group_stride, int *bad,
+                       cudaStream_t stream) {
+  if (!block || !groups || !counts || !bad || group_stride < 1 || !ExchangeBytes(world, cap, hidden, nullptr))
+    return PADRA_INVALID_ARGUMENT;
+  const ExchangeLayout l = MakeExchangeLayout(world, cap, hidden);
+  const unsigned char *base = static_cast<const unsigned char *>(block);
+  GroupRegionsKernel<<<kExperts, 256, 0, stream>>>(reinterpret_cast<const int *>(base + l.ids), reinterpret_cast<const int4 *>(base + l.meta),
+                                                   world, cap, groups, counts, group_stride, bad);
+  return CudaStatus(cudaGetLastError());
+}
+
+int LaunchReturn(const unsigned short *down, const unsigned long long *bases, int rank, int world, int cap, int hidden, unsigned epoch,
+                 int *bad, cudaStream_t stream) {
+  PeerBlocks peers;
+  if (!down || !bases || !bad || rank < 0 || rank >= world || !ExchangeBytes(world, cap, hidden, nullptr) ||
+      !FillPeers(peers, bases, world) || reinterpret_cast<uintptr_t>(down) % 16)
+    return PADRA_INVALID_ARGUMENT;
+  ReturnKernel<<<148 * 4, 256, 0, stream>>>(down, peers, MakeExchangeLayout(world, cap, hidden), rank, world, cap, hidden, epoch, bad);
+  return CudaStatus(cudaGetLastError());
+}
 
 int LaunchGroupRows(const int *ids, int *groups, int *counts, int rows, int group_stride, int *bad, cudaStream_t stream) {
   if (!ids || !groups || !counts || !bad || rows < 1 || rows > kMaxRows || group_stride < 1 || group_stride > rows)

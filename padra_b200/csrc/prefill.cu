@@ -45,7 +45,8 @@ constexpr int kMmaWarp = kEpilogueWarps;
 constexpr int kFirstProducerWarp = kMmaWarp + 1;
 constexpr int kPrefillThreads = (kEpilogueWarps + 1 + kProducerSets * kWarpsPerSet) * 32; // 672
 constexpr int kTmemColumns = 512;                   // two accumulators of 256 columns
-constexpr int kMaxPairs = 4096 * kTopK;              // pairs (rows) one call takes
+constexpr int kMaxPairs = 4096 * kTopK;              // grouped pairs (rows) one call works on
+constexpr int kMaxPairIndex = 1 << 20;              // pair indices may be sparse (received rows in per-source regions)
 constexpr int kMaxTiles = kExperts + kMaxPairs / kMaxTileN; // sum over experts of ceil(n_e / 256)
 constexpr int kAhead = 3;                           // own stages of packed words in flight per producer lane
 constexpr unsigned long long kWaitLimitNs = 1000000000ull; // a wait that lasts a second has failed
@@ -236,7 +237,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
       tile_prefix += sm.scan[0], pair_prefix += sm.scan[1];
     if (tid == kExperts - 1) {
       sm.tiles = tile_prefix < kMaxTiles ? tile_prefix : kMaxTiles;
-      if (pair_prefix > pairs_total) {
+      if (pair_prefix > pairs_total || pair_prefix > kMaxPairs || tile_prefix > kMaxTiles) {
         Raise(a.bad);
         sm.abort = 1;
       }
@@ -561,7 +562,8 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
   if (*bad)
     return;
   // one warp per grouped row: the row's expert, pair and sidecar address are looked up once for all its blocks
-  for (int row = blockIdx.x * 8 + warp; row < s_offset[kExperts]; row += gridDim.x * 8) {
+  const int grouped_rows = s_offset[kExperts] < kMaxPairs ? s_offset[kExperts] : kMaxPairs; // the workspace holds no more
+  for (int row = blockIdx.x * 8 + warp; row < grouped_rows; row += gridDim.x * 8) {
   int expert = 0; // the expert whose group holds grouped row `row`
   for (int step = 32; step; step >>= 1)
     if (expert + step < kExperts && s_offset[expert + step] <= row)
@@ -645,11 +647,11 @@ static int LaunchPrefillGemm(const Matrix *matrices, int layer, int part, const 
                              const unsigned short *pair_rows, unsigned short *output, const unsigned short *gate,
                              const unsigned short *up, const unsigned short *table, void *transformed, int group_stride, int pairs,
                              int *bad, cudaStream_t stream, int rate, int hidden, int inter) {
-  if (pairs < 1 || pairs > kMaxPairs || group_stride < 1 || group_stride > pairs || !transformed)
+  if (pairs < 1 || pairs > kMaxPairIndex || group_stride < 1 || group_stride > kMaxPairs || !transformed)
     return PADRA_INVALID_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(output) % 16 || reinterpret_cast<uintptr_t>(transformed) % 16)
     return PADRA_INVALID_ARGUMENT;
-  PrefillInputKernel<<<(pairs + 7) / 8, 256, 0, stream>>>(matrices, layer, part, groups, counts, input, gate, up, pair_rows, table,
+  PrefillInputKernel<<<((pairs < kMaxPairs ? pairs : kMaxPairs) + 7) / 8, 256, 0, stream>>>(matrices, layer, part, groups, counts, input, gate, up, pair_rows, table,
                                                           static_cast<__half *>(transformed), group_stride, pairs, hidden, inter, bad);
   if (cudaGetLastError() != cudaSuccess)
     return PADRA_INTERNAL;

@@ -210,6 +210,99 @@ class KernelBackend:
                                           B.ptr(self.k.bad), 1, self.hidden, B.stream_handle()), "padra_ep_combine")
 
 
+class PeerExchangePrefill:
+    """The layer with the exchange done by the GPUs themselves: rows are stored straight into the owner rank's exchange
+    block over NVLink, arrival is announced with epoch flags, and nothing returns to the host between the router and
+    the combine (csrc/expert_parallel.cu).  `blocks` are this process's addresses of every rank's exchange block:
+    symmetric memory of a process group (see `over_group`), or plain allocations when the ranks are threads that share
+    one GPU (tests).  `between_phases` is called after the launches that announce rows and before the launch that waits
+    for them; ranks that share ONE GPU pass a thread barrier there, so that in stream order every announcing kernel
+    precedes every waiting kernel (kernels of one GPU must never wait for kernels launched later)."""
+
+    MAX_GROUPED = 4096 * TOPK
+
+    def __init__(self, kernels, owner, rank: int, world: int, cap: int, block: torch.Tensor, blocks, between_phases=None):
+        import ctypes as C
+
+        from . import binding as B
+
+        self.k, self.B, self.lib = kernels, B, kernels.lib
+        self.rank, self.world, self.cap = rank, world, cap
+        self.device = kernels.t.device
+        self.hidden, self.inter = kernels.dims
+        self.block, self.between_phases = block, between_phases
+        offsets = (C.c_size_t * 6)()
+        total = self.lib.padra_ep_exchange_bytes(world, cap, self.hidden, offsets)
+        assert total and block.numel() >= total and block.dtype == torch.uint8
+        self.offsets = list(offsets)
+        self.bases = (C.c_ulonglong * 8)(*[int(b) for b in blocks], *([0] * (8 - world)))
+        self.owner = torch.from_numpy(np.asarray(owner, dtype=np.int32)).to(self.device)
+        dev, rows = self.device, world * cap
+        self.groups = torch.empty(EXPERTS * self.MAX_GROUPED, dtype=torch.int32, device=dev)
+        self.counts = torch.empty(EXPERTS, dtype=torch.int32, device=dev)
+        self.gate = torch.empty((rows, self.inter), dtype=torch.uint16, device=dev)
+        self.up = torch.empty((rows, self.inter), dtype=torch.uint16, device=dev)
+        self.down = torch.empty((rows, self.hidden), dtype=torch.uint16, device=dev)
+        self.transformed = torch.empty((self.MAX_GROUPED, max(self.hidden, self.inter)), dtype=torch.float16, device=dev)
+        self.backend = KernelBackend(kernels)
+        self.epoch = 0
+
+    @staticmethod
+    def exchange_bytes(lib, world: int, cap: int, hidden: int) -> int:
+        return lib.padra_ep_exchange_bytes(world, cap, hidden, None)
+
+    @classmethod
+    def over_group(cls, kernels, owner, cap: int, group=None):
+        """Exchange blocks in symmetric memory of a process group (one GPU per rank)."""
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings are all this needs
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group or dist.group.WORLD
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        total = cls.exchange_bytes(kernels.lib, world, cap, kernels.dims[0])
+        block = symm_mem.empty(total, dtype=torch.uint8, device=kernels.t.device)
+        block.zero_()
+        handle = symm_mem.rendezvous(block, group)
+        torch.cuda.synchronize(kernels.t.device)
+        dist.barrier(group)
+        engine = cls(kernels, owner, rank, world, cap, block, [int(p) for p in handle.buffer_ptrs])
+        engine._handle = handle
+        return engine
+
+    def set_owner(self, owner) -> None:
+        self.owner.copy_(torch.from_numpy(np.asarray(owner, dtype=np.int32)))
+
+    def layer(self, layer: int, ids: torch.Tensor, routing: torch.Tensor, normalized: torch.Tensor, x: torch.Tensor) -> None:
+        B, lib, k = self.B, self.lib, self.k
+        self.epoch += 1
+        stream, bad = B.stream_handle(), B.ptr(k.bad)
+        tokens, pairs = x.shape[0], ids.numel()
+        geometry = (self.world, self.cap, self.hidden)
+        base = self.block.data_ptr()
+        plan = self.backend.plan(ids, self.owner, self.world)
+        B.check(lib.padra_ep_dispatch(B.ptr(normalized), B.ptr(plan.order), B.ptr(plan.send_ids), B.ptr(plan.send_counts), self.bases,
+                                      self.rank, self.world, self.cap, pairs, self.hidden, self.epoch, bad, stream), "padra_ep_dispatch")
+        if self.between_phases:
+            self.between_phases()
+        B.check(lib.padra_ep_wait(base, 0, *geometry, self.epoch, bad, stream), "padra_ep_wait")
+        B.check(lib.padra_ep_group_received(base, *geometry, B.ptr(self.groups), B.ptr(self.counts), self.MAX_GROUPED, bad, stream),
+                "padra_ep_group_received")
+        for part, target in ((0, self.gate), (1, self.up), (2, self.down)):
+            B.check(lib.padra_exl3_prefill_rows_launch(
+                k.t.descriptors.data_ptr(), layer, part, B.ptr(self.groups), B.ptr(self.counts), self.MAX_GROUPED, self.world * self.cap,
+                base + self.offsets[0], B.ptr(target), B.ptr(self.gate), B.ptr(self.up), B.ptr(k.table), B.ptr(self.transformed), bad,
+                stream, k.t.rate, self.hidden, self.inter), "padra_exl3_prefill_rows_launch")
+        B.check(lib.padra_ep_return(B.ptr(self.down), self.bases, self.rank, self.world, self.cap, self.hidden, self.epoch, bad, stream),
+                "padra_ep_return")
+        if self.between_phases:
+            self.between_phases()
+        B.check(lib.padra_ep_wait(base, 1, *geometry, self.epoch, bad, stream), "padra_ep_wait")
+        B.check(lib.padra_ep_combine(B.ptr(x), base + self.offsets[3], B.ptr(plan.position), B.ptr(routing), tokens, bad, 1, self.hidden,
+                                     stream), "padra_ep_combine")
+
+
 class ExpertParallelPrefill:
     """One MoE layer call for this rank's tokens; every rank of the group calls it together."""
 

@@ -179,3 +179,60 @@ def test_ranks_on_one_gpu_equal_the_single_gpu_prefill(oracle, gpu, world, chunk
         torch.cuda.synchronize()
         assert kernels[rank].bad_flag() == 0
         assert np.array_equal(outputs[rank].cpu().numpy(), want.cpu().numpy()), f"rank {rank} differs from the single-GPU path"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4])
+def test_peer_memory_exchange_on_one_gpu_equals_the_single_gpu_prefill(oracle, gpu, world):
+    """The exchange over peer memory with the ranks as threads of one process: every rank's block is a plain allocation
+    of the shared GPU, and a thread barrier between the announcing and the waiting launches keeps the stream order that
+    a single GPU needs.  Three layer calls in a row reuse the blocks."""
+    from padra_b200 import binding as B
+    from padra_b200.experts import ExpertKernels, ExpertTable
+
+    hidden, inter, tokens, rate, layers = 512, 256, 48, 4, 3
+    host = O.HostMatrices(layers, hidden, inter, rate, seed=35)
+    table = ExpertTable(layers, hidden, inter, rate, gpu).fill_from_host(host)
+    lib = B.load()
+    cap = tokens * 8
+    total = EP.PeerExchangePrefill.exchange_bytes(lib, world, cap, hidden)
+    blocks = [torch.zeros(total, dtype=torch.uint8, device=gpu) for _ in range(world)]
+    popularity = np.arange(1, 65, dtype=np.float64) ** -1.1
+    owner = EP.balanced_placement(popularity, world)
+    kernels = [ExpertKernels(table) for _ in range(world)]
+    inputs = [_inputs(oracle, r, tokens, hidden) for r in range(world)]
+    barrier = threading.Barrier(world)
+    outputs, errors = [None] * world, []
+    torch.cuda.synchronize()
+
+    def run(rank):
+        try:
+            torch.cuda.set_device(gpu)
+            x, ids, w = inputs[rank]
+            engine = EP.PeerExchangePrefill(kernels[rank], owner, rank, world, cap, blocks[rank], [b.data_ptr() for b in blocks],
+                                            between_phases=barrier.wait)
+            got = torch.from_numpy(x.copy()).to(gpu)
+            dids, dw, dx = torch.from_numpy(ids.reshape(-1)).to(gpu), torch.from_numpy(w.reshape(-1)).to(gpu), torch.from_numpy(x).to(gpu)
+            for layer in range(layers):
+                engine.layer(layer, dids, dw, dx, got)
+            outputs[rank] = got
+        except Exception as e:
+            errors.append(e)
+            barrier.abort()
+
+    threads = [threading.Thread(target=run, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=120)
+    assert not errors, errors
+    torch.cuda.synchronize()
+    for rank in range(world):
+        x, ids, w = inputs[rank]
+        want = torch.from_numpy(x.copy()).to(gpu)
+        dids, dw, dx = torch.from_numpy(ids.reshape(-1)).to(gpu), torch.from_numpy(w.reshape(-1)).to(gpu), torch.from_numpy(x).to(gpu)
+        for layer in range(layers):
+            kernels[rank].prefill_layer(layer, dids, dw, dx, want, tokens)
+        torch.cuda.synchronize()
+        assert kernels[rank].bad_flag() == 0
+        assert np.array_equal(outputs[rank].cpu().numpy(), want.cpu().numpy()), f"rank {rank} differs from the single-GPU path"
