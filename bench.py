@@ -196,7 +196,7 @@ def prefill_leg(k, dev, layers: int, tokens: int = 2048, passes: int = 3) -> dic
             "kernels_per_chunk": 9, "layers_rotated": layers, "passes": passes}
 
 
-def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, batch: int = 16384, chunk: int = 2048) -> dict:
+def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: str, batch: int = 16384, chunk: int = 2048) -> dict:
     """configs[4]: a batch of 16384 tokens through `layers` MoE layers, experts sharded 64/world per rank by measured
     popularity, tokens split evenly over the ranks (strong scaling), all-to-all dispatch and combine per layer and
     chunk.  Between layers the next input is the RMS-normalised residual stream, so layer l+1 depends on layer l.
@@ -208,7 +208,7 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, batch: int =
     from padra_b200.experts import bf16_values, zipf_routing
 
     local = batch // world
-    if world > 1 and local <= chunk:
+    if world > 1 and exchange == "nccl" and local <= chunk:
         chunk = local // 2  # at least two chunks per rank, so that exchange and expert work overlap
     chunks = [(c, min(chunk, local - c)) for c in range(0, local, chunk)]
     g = torch.Generator(device=dev)
@@ -222,21 +222,28 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, batch: int =
         for c, n in chunks:
             ids, w = zipf_routing(n, seed=10007 * layer + (rank * local + c) // chunk + 1, device=dev, popularity_seed=layer)
             routing[layer, c] = (ids.reshape(-1), w.reshape(-1))
-    engines = None
-    if world > 1:
-        backend, exchange = EP.KernelBackend(k), EP.GroupExchange()
-        engines = [EP.ExpertParallelPrefill(backend, exchange, owners[layer]) for layer in range(layers)]
+    engines = peer = None
+    if world > 1 and exchange == "nccl":
+        backend, group_exchange = EP.KernelBackend(k), EP.GroupExchange()
+        engines = [EP.ExpertParallelPrefill(backend, group_exchange, owners[layer]) for layer in range(layers)]
+    elif world > 1:
+        peer = EP.PeerExchangePrefill.over_group(k, owners[0], cap=chunk * TOPK)
+        device_owners = [torch.from_numpy(o.astype(np.int32)).to(dev) for o in owners]
 
     def normalise(rows):
         return bf16_values(rows * torch.rsqrt(rows.square().mean(dim=-1, keepdim=True) + 1e-6))
 
     def stack(x):
         for layer in range(layers):
-            if engines is None:
+            if peer is not None:  # rows stored straight into the owners' memory over NVLink, nothing returns to the host
+                for c, n in chunks:
+                    rows = x[c:c + n]
+                    peer.layer(layer, *routing[layer, c], normalise(rows), rows, owner=device_owners[layer])
+            elif engines is None:
                 for c, n in chunks:
                     rows = x[c:c + n]
                     k.prefill_layer(layer, *routing[layer, c], normalise(rows), rows, n)
-            else:  # all of the layer's chunks in one pipelined call
+            else:  # NCCL all-to-all, all of the layer's chunks in one pipelined call
                 engines[layer].layer_chunks(layer, [(*routing[layer, c], normalise(x[c:c + n]), x[c:c + n]) for c, n in chunks])
 
     stack(x0.clone())  # warm-up: workspaces, NCCL channels
@@ -250,7 +257,7 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, batch: int =
     b.record()
     torch.cuda.synchronize(dev)
     assert k.bad_flag() == 0 and bool(torch.isfinite(x).all()), "expert-parallel prefill raised the error flag"
-    return {"seconds": a.elapsed_time(b) / 1e3, "batch": batch, "layers": layers, "chunk": chunk}
+    return {"seconds": a.elapsed_time(b) / 1e3, "batch": batch, "layers": layers, "chunk": chunk, "exchange": exchange}
 
 
 def run_ours(args):
@@ -401,7 +408,7 @@ def run_ours(args):
     e2e_seconds = time.perf_counter() - t0
     barrier()
 
-    ep = expert_parallel_leg(k, dev, world, rank, layers) if EXPERTS % world == 0 and not args.no_ep else None
+    ep = expert_parallel_leg(k, dev, world, rank, layers, args.ep_exchange) if EXPERTS % world == 0 and not args.no_ep else None
     if world > 1:
         t = torch.tensor([seconds, e2e_seconds, ep["seconds"] if ep else 0.0], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -445,7 +452,9 @@ def run_ours(args):
         flops = ep["batch"] * TOPK * 3 * 2 * HIDDEN * INTER * ep["layers"]
         line["expert_parallel_prefill"] = {
             "workload": f"configs[4]: {ep['batch']}-token batch through {ep['layers']} K{RATE} MoE layers, experts sharded 64/{world} per GPU "
-                        "by measured popularity, Zipf(1.1) routing, NCCL all-to-all dispatch and combine" if world > 1 else
+                        "by measured popularity, Zipf(1.1) routing, dispatch and return " +
+                        ("by kernels storing into peer memory over NVLink (symmetric memory, epoch flags)" if ep["exchange"] == "peer"
+                         else "by NCCL all-to-all, chunks pipelined over two streams") if world > 1 else
                         f"configs[4] at one GPU: {ep['batch']}-token batch through {ep['layers']} K{RATE} MoE layers in chunks of {ep['chunk']}",
             "n_gpus": world, "scaling": "strong", "tokens_per_s": ep["batch"] / ep["seconds"], "ms_per_batch": ep["seconds"] * 1e3,
             "tflops_all_gpus": flops / ep["seconds"] / 1e12, "timing": "CUDA events on each rank, maximum over ranks"}
@@ -471,6 +480,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-ep", action="store_true", help="skip the expert-parallel prefill leg")
+    ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
+                    help="expert-parallel exchange: kernels over NVLink peer memory (default) or NCCL all-to-all")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers of distinct weights to rotate over (profiling: fewer)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

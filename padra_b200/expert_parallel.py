@@ -274,14 +274,16 @@ class PeerExchangePrefill:
     def set_owner(self, owner) -> None:
         self.owner.copy_(torch.from_numpy(np.asarray(owner, dtype=np.int32)))
 
-    def layer(self, layer: int, ids: torch.Tensor, routing: torch.Tensor, normalized: torch.Tensor, x: torch.Tensor) -> None:
+    def layer(self, layer: int, ids: torch.Tensor, routing: torch.Tensor, normalized: torch.Tensor, x: torch.Tensor,
+              owner: torch.Tensor | None = None) -> None:
+        """owner: int32 [64] on the device, if this layer's placement differs from the engine's."""
         B, lib, k = self.B, self.lib, self.k
         self.epoch += 1
         stream, bad = B.stream_handle(), B.ptr(k.bad)
         tokens, pairs = x.shape[0], ids.numel()
         geometry = (self.world, self.cap, self.hidden)
         base = self.block.data_ptr()
-        plan = self.backend.plan(ids, self.owner, self.world)
+        plan = self.backend.plan(ids, self.owner if owner is None else owner, self.world)
         B.check(lib.padra_ep_dispatch(B.ptr(normalized), B.ptr(plan.order), B.ptr(plan.send_ids), B.ptr(plan.send_counts), self.bases,
                                       self.rank, self.world, self.cap, pairs, self.hidden, self.epoch, bad, stream), "padra_ep_dispatch")
         if self.between_phases:
