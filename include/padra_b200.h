@@ -160,6 +160,9 @@ PADRA_API int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer,
  *     index space to padra_exl3_prefill_rows_launch: rows = world*cap, input_rows = block + offsets[0].
  *   padra_ep_return: down rows (same index space) go back into their source's block at the send rows they came
  *     from, then a flag with `epoch`; after padra_ep_wait(which = 1), padra_ep_combine reads block + offsets[3].
+ *   padra_ep_down_return: the down projection (part 2 of padra_exl3_prefill_rows_launch on the received index space)
+ *     fused with padra_ep_return: the epilogue of the grouped GEMM stores every finished row straight into its source's
+ *     block, so the transfer overlaps the remaining tiles, and the CTA that finishes last raises the flags.
  * epoch must differ from call to call (count up from 1).  A rank may start call n+1 only after its own combine of call
  * n has been enqueued on the same stream: that order is what makes reuse of the blocks safe. */
 PADRA_API size_t padra_ep_exchange_bytes(int world, int cap, int hidden, size_t *offsets);
@@ -172,6 +175,11 @@ PADRA_API int padra_ep_group_received(const void *block, int world, int cap, int
                                       int group_stride, int *bad, padra_stream stream);
 PADRA_API int padra_ep_return(const unsigned short *down_rows, const unsigned long long *peer_blocks, int rank, int world,
                               int cap, int hidden, unsigned epoch, int *bad, padra_stream stream);
+PADRA_API int padra_ep_down_return(const padra_matrix *matrices, int layer, const int *groups, const int *counts,
+                                   int group_stride, const unsigned short *gate, const unsigned short *up,
+                                   const unsigned short *table, void *transformed, const unsigned long long *peer_blocks,
+                                   int rank, int world, int cap, unsigned epoch, int *bad, padra_stream stream, int rate,
+                                   int hidden, int inter);
 PADRA_API int padra_ep_plan(const int *ids, const int *owner, int *order, int *position, int *send_ids,
                             long long *send_counts, int pairs, int world, int *bad, padra_stream stream);
 PADRA_API int padra_ep_pack_rows(const float *activations, const int *order, unsigned short *packed, int rows, int hidden,

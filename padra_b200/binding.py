@@ -42,6 +42,7 @@ SIGNATURES = {
     "padra_ep_wait": ([_p, _i, _i, _i, _i, C.c_uint, _p, _p], _i),
     "padra_ep_group_received": ([_p, _i, _i, _i, _p, _p, _i, _p, _p], _i),
     "padra_ep_return": ([_p, _p, _i, _i, _i, _i, C.c_uint, _p, _p], _i),
+    "padra_ep_down_return": ([_p, _i, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, C.c_uint, _p, _p, _i, _i, _i], _i),
     "padra_ep_plan": ([_p, _p, _p, _p, _p, _p, _i, _i, _p, _p], _i),
     "padra_ep_pack_rows": ([_p, _p, _p, _i, _i, _p, _p], _i),
     "padra_ep_group_rows": ([_p, _p, _p, _i, _i, _p, _p], _i),

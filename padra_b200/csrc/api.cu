@@ -145,6 +145,19 @@ int padra_ep_return(const unsigned short *down_rows, const unsigned long long *p
   return LaunchReturn(down_rows, peer_blocks, rank, world, cap, hidden, epoch, bad, S(stream));
 }
 
+int padra_ep_down_return(const padra_matrix *matrices, int layer, const int *groups, const int *counts, int group_stride,
+                         const unsigned short *gate, const unsigned short *up, const unsigned short *table, void *transformed,
+                         const unsigned long long *peer_blocks, int rank, int world, int cap, unsigned epoch, int *bad,
+                         padra_stream stream, int rate, int hidden, int inter) {
+  if (!RateOk(rate))
+    return PADRA_UNSUPPORTED;
+  if (!matrices || !groups || !counts || !gate || !up || !table || !transformed || !peer_blocks || !bad || layer < 0 || hidden < 128 ||
+      inter < 128 || (hidden % 128) || (inter % 128))
+    return PADRA_INVALID_ARGUMENT;
+  return LaunchPrefillDownReturn(matrices, layer, groups, counts, group_stride, gate, up, table, transformed, peer_blocks, rank, world,
+                                 cap, epoch, bad, S(stream), rate, hidden, inter);
+}
+
 int padra_ep_plan(const int *ids, const int *owner, int *order, int *position, int *send_ids, long long *send_counts, int pairs,
                   int world, int *bad, padra_stream stream) {
   return LaunchPlan(ids, owner, order, position, send_ids, send_counts, pairs, world, bad, S(stream));

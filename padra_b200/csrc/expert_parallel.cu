@@ -16,13 +16,13 @@
 // sending kernel; a one-CTA wait kernel on the receiving side polls its own flags, bounded in time.  Nothing in this
 // form touches the host: row counts stay on the device, next to the flags.
 #include "common.cuh"
+#include "exchange.cuh"
 #include "kernels.cuh"
 
 namespace padra {
 namespace {
 
 constexpr int kMaxRows = 4096 * kTopK; // rows one grouped-projection call takes (received rows may exceed a rank's own)
-constexpr int kMaxRanks = 8;
 
 // One CTA per expert walks the rows in order and appends those routed to it (stable, like GroupKernel).  `ids` are
 // expert ids 0..63 per row; experts this rank does not own simply get no rows.
@@ -187,44 +187,7 @@ __global__ void __launch_bounds__(128) CombineIndexedKernel(float *x, const unsi
   *target = v;
 }
 
-// ---- the exchange over peer memory ------------------------------------------------------------------------------
-struct ExchangeLayout {
-  size_t rows, ids, meta, returned, arrived, came_back, tickets, total;
-};
-// One block per rank: rows/ids = what others sent me, region s (cap rows) for source rank s; meta[s] = {rows source s
-// sent me, the send row its first row came from}; returned = the down rows of MY pairs, in my send order;
-// arrived[s] / came_back[d] = epoch flags written by peers; tickets = two CTA counters of my own kernels.
-__host__ __device__ inline ExchangeLayout MakeExchangeLayout(int world, int cap, int hidden) {
-  ExchangeLayout l{};
-  size_t at = 0;
-#define PADRA_ALIGN_256(n) (((n) + 255) & ~static_cast<size_t>(255))
-  l.rows = at, at += PADRA_ALIGN_256(static_cast<size_t>(world) * cap * hidden * 2);
-  l.ids = at, at += PADRA_ALIGN_256(static_cast<size_t>(world) * cap * 4);
-  l.meta = at, at += PADRA_ALIGN_256(static_cast<size_t>(world) * 16);
-  l.returned = at, at += PADRA_ALIGN_256(static_cast<size_t>(cap) * hidden * 2);
-  l.arrived = at, at += PADRA_ALIGN_256(static_cast<size_t>(world) * 4);
-  l.came_back = at, at += PADRA_ALIGN_256(static_cast<size_t>(world) * 4);
-#undef PADRA_ALIGN_256
-  l.tickets = at, at += 256;
-  l.total = at;
-  return l;
-}
-
-struct PeerBlocks {
-  unsigned char *base[kMaxRanks];
-};
-
-constexpr unsigned long long kFlagWaitNs = 2000000000ull;
-
-__device__ __forceinline__ void StoreFlagSystem(unsigned *flag, unsigned value) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
-}
-__device__ __forceinline__ unsigned LoadFlagSystem(const unsigned *flag) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-  return v;
-}
-
+// ---- the exchange over peer memory (block layout and flag helpers: exchange.cuh) ------------------------------
 // Fused pack + dispatch: send row j (pair order[j]) goes to rank d = the destination whose range of the send order
 // holds j, as row rank*cap + (j - first row for d) of d's block.
 __global__ void __launch_bounds__(256) DispatchKernel(const float *activations, const int *order, const int *send_ids,

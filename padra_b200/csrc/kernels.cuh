@@ -52,6 +52,10 @@ int LaunchReturn(const unsigned short *down, const unsigned long long *bases, in
                  int *bad, cudaStream_t stream);
 int LaunchPlan(const int *ids, const int *owner, int *order, int *position, int *send_ids, long long *send_counts, int pairs,
                int world, int *bad, cudaStream_t stream);
+int LaunchPrefillDownReturn(const Matrix *matrices, int layer, const int *groups, const int *counts, int group_stride,
+                            const unsigned short *gate, const unsigned short *up, const unsigned short *table, void *transformed,
+                            const unsigned long long *bases, int rank, int world, int cap, unsigned epoch, int *bad, cudaStream_t stream,
+                            int rate, int hidden, int inter);
 int LaunchGroupRows(const int *ids, int *groups, int *counts, int rows, int group_stride, int *bad, cudaStream_t stream);
 int LaunchPackRows(const float *activations, const int *order, unsigned short *packed, int rows, int hidden, int *bad,
                    cudaStream_t stream);

@@ -26,6 +26,7 @@
 // its work, frees its tensor memory and leaves.
 #include "codec.cuh"
 #include "common.cuh"
+#include "exchange.cuh"
 #include "kernels.cuh"
 
 namespace padra {
@@ -64,8 +65,9 @@ struct PrefillSmem {
   TileInfo tile[kMaxTiles], unsorted[kMaxTiles];
   int pairs[2][kMaxTileN]; // (token*8+slot) of the rows of the item being drained / the next one
   int scan[4];
+  int from[kMaxRanks]; // return_to_peers: first send row of each source's region
   unsigned tmem_base;
-  int abort, tiles;
+  int abort, tiles, last;
 };
 
 struct PrefillArgs {
@@ -78,6 +80,14 @@ struct PrefillArgs {
   int pairs_total;  // pairs (rows of `output`) in the call
   int hidden, inter;
   int *bad;
+  // Expert-parallel down projection: the rows do not go to `output` but straight back to the ranks that sent them,
+  // into their exchange blocks over NVLink (pair index = source*cap + k -> row from[source] + k of that rank's
+  // `returned` area); the CTA that finishes last announces them with the epoch flag.
+  int return_to_peers;
+  PeerBlocks peers;
+  ExchangeLayout layout;
+  int rank, world, cap;
+  unsigned epoch;
 };
 
 __device__ __forceinline__ unsigned SmemAddress(const void *p) {
@@ -183,6 +193,25 @@ __device__ __forceinline__ void TmemLoad4x8(unsigned taddr, float (&v)[4][8]) {
 }
 
 
+// return_to_peers: every CTA fences its peer stores and draws a ticket; the last one tells the sources that their
+// rows have come back.  All threads of the CTA call it.
+__device__ __forceinline__ void AnnounceReturn(const PrefillArgs &a, int *last) {
+  if (!a.return_to_peers)
+    return;
+  __threadfence_system();
+  __syncthreads();
+  unsigned *ticket = reinterpret_cast<unsigned *>(a.peers.base[a.rank] + a.layout.tickets) + 1;
+  if (!threadIdx.x)
+    *last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (*last && threadIdx.x < a.world) {
+    __threadfence_system();
+    StoreFlagSystem(reinterpret_cast<unsigned *>(a.peers.base[threadIdx.x] + a.layout.came_back) + a.rank, a.epoch);
+    if (!threadIdx.x)
+      *ticket = 0;
+  }
+}
+
 // Item `sequence` of this CTA: tiles sorted by size are dealt out forwards and backwards in turn.
 __device__ __forceinline__ int ItemIndex(int sequence) {
   const int g = gridDim.x, c = blockIdx.x;
@@ -203,6 +232,14 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
   if (tid == 0) {
     sm.abort = *a.bad != 0;
     sm.tiles = 0;
+  }
+  if (a.return_to_peers && tid < a.world) {
+    const int4 meta = reinterpret_cast<const int4 *>(a.peers.base[a.rank] + a.layout.meta)[tid];
+    sm.from[tid] = meta.y;
+    if (meta.x < 0 || meta.x > a.cap || meta.y < 0 || meta.y + meta.x > a.cap) {
+      Raise(a.bad);
+      sm.from[tid] = 0; // stays inside the source's area; the rows are garbage and the flag says so
+    }
   }
   __syncthreads();
   int my_count = 0, my_tiles = 0, tile_prefix = 0, pair_prefix = 0;
@@ -275,8 +312,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
   }
   __syncthreads();
   const int items = tiles * row_blocks;
-  if (sm.abort || ItemIndex(0) >= items)
-    return; // nothing allocated yet
+  if (sm.abort || ItemIndex(0) >= items) { // nothing allocated yet
+    AnnounceReturn(a, &sm.last);
+    return;
+  }
   if (warp == kMmaWarp) { // one warp allocates the accumulator columns and gives the permit back
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddress(&sm.tmem_base)), "r"(kTmemColumns)
                  : "memory");
@@ -485,7 +524,14 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         // stages d = 32 and 64 combine the four pieces column by column
-        unsigned short *out = a.output + (n < valid ? static_cast<size_t>(pairs[n]) : 0) * rows + block * kTileM;
+        unsigned short *out;
+        if (a.return_to_peers) {
+          const int pair = n < valid ? pairs[n] : 0, source = pair / a.cap;
+          out = reinterpret_cast<unsigned short *>(a.peers.base[source] + a.layout.returned) +
+                static_cast<size_t>(sm.from[source] + (pair - source * a.cap)) * rows + block * kTileM;
+        } else {
+          out = a.output + (n < valid ? static_cast<size_t>(pairs[n]) : 0) * rows + block * kTileM;
+        }
 #pragma unroll 1
         for (int c0 = 0; c0 < 32; c0 += 8) {
           float v[4][8];
@@ -527,6 +573,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
   }
+  AnnounceReturn(a, &sm.last);
 }
 
 // x~ rows in expert-grouped order: row (offset of expert e) + i holds the transform of the i-th pair routed to e.
@@ -643,13 +690,19 @@ template <int Rate> int LaunchGemm(const PrefillArgs &a, dim3 grid, cudaStream_t
 
 // `pair_rows` null: the reference's layout, pairs = tokens*8 and input row pair/8.  Otherwise one BF16 input row per
 // pair, any number of pairs per expert up to group_stride (rows that other ranks routed to this rank's experts).
+struct ReturnSpec {
+  const unsigned long long *bases;
+  int rank, world, cap;
+  unsigned epoch;
+};
+
 static int LaunchPrefillGemm(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, const float *input,
                              const unsigned short *pair_rows, unsigned short *output, const unsigned short *gate,
                              const unsigned short *up, const unsigned short *table, void *transformed, int group_stride, int pairs,
-                             int *bad, cudaStream_t stream, int rate, int hidden, int inter) {
+                             int *bad, cudaStream_t stream, int rate, int hidden, int inter, const ReturnSpec *ret = nullptr) {
   if (pairs < 1 || pairs > kMaxPairIndex || group_stride < 1 || group_stride > kMaxPairs || !transformed)
     return PADRA_INVALID_ARGUMENT;
-  if (reinterpret_cast<uintptr_t>(output) % 16 || reinterpret_cast<uintptr_t>(transformed) % 16)
+  if ((!ret && (!output || reinterpret_cast<uintptr_t>(output) % 16)) || reinterpret_cast<uintptr_t>(transformed) % 16)
     return PADRA_INVALID_ARGUMENT;
   PrefillInputKernel<<<((pairs < kMaxPairs ? pairs : kMaxPairs) + 7) / 8, 256, 0, stream>>>(matrices, layer, part, groups, counts, input, gate, up, pair_rows, table,
                                                           static_cast<__half *>(transformed), group_stride, pairs, hidden, inter, bad);
@@ -659,6 +712,18 @@ static int LaunchPrefillGemm(const Matrix *matrices, int layer, int part, const 
   a.matrices = matrices, a.layer = layer, a.part = part, a.groups = groups, a.counts = counts;
   a.transformed = static_cast<const __half *>(transformed), a.output = output, a.group_stride = group_stride;
   a.pairs_total = pairs, a.hidden = hidden, a.inter = inter, a.bad = bad;
+  if (ret) {
+    if (part != 2 || ret->world < 1 || ret->world > kMaxRanks || ret->rank < 0 || ret->rank >= ret->world || ret->cap < 1 ||
+        static_cast<long long>(ret->world) * ret->cap != pairs || !ret->bases)
+      return PADRA_INVALID_ARGUMENT;
+    for (int r = 0; r < kMaxRanks; ++r) {
+      a.peers.base[r] = r < ret->world ? reinterpret_cast<unsigned char *>(static_cast<uintptr_t>(ret->bases[r])) : nullptr;
+      if (r < ret->world && (!a.peers.base[r] || ret->bases[r] % 256))
+        return PADRA_INVALID_ARGUMENT;
+    }
+    a.return_to_peers = 1, a.layout = MakeExchangeLayout(ret->world, ret->cap, hidden);
+    a.rank = ret->rank, a.world = ret->world, a.cap = ret->cap, a.epoch = ret->epoch;
+  }
   int device = 0, sms = 0;
   if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 1)
     return PADRA_INTERNAL;
@@ -693,6 +758,18 @@ int LaunchPrefillRows(const Matrix *matrices, int layer, int part, const int *gr
     return PADRA_INVALID_ARGUMENT;
   return LaunchPrefillGemm(matrices, layer, part, groups, counts, nullptr, input_rows, output, gate, up, table, transformed,
                            group_stride, rows, bad, stream, rate, hidden, inter);
+}
+
+// The down projection of received rows with its results stored straight into the source ranks' exchange blocks.
+int LaunchPrefillDownReturn(const Matrix *matrices, int layer, const int *groups, const int *counts, int group_stride,
+                            const unsigned short *gate, const unsigned short *up, const unsigned short *table, void *transformed,
+                            const unsigned long long *bases, int rank, int world, int cap, unsigned epoch, int *bad, cudaStream_t stream,
+                            int rate, int hidden, int inter) {
+  if (world < 1 || cap < 1)
+    return PADRA_INVALID_ARGUMENT;
+  const ReturnSpec ret{bases, rank, world, cap, epoch};
+  return LaunchPrefillGemm(matrices, layer, 2, groups, counts, nullptr, nullptr, nullptr, gate, up, table, transformed, group_stride,
+                           world * cap, bad, stream, rate, hidden, inter, &ret);
 }
 
 } // namespace padra

@@ -221,7 +221,8 @@ class PeerExchangePrefill:
 
     MAX_GROUPED = 4096 * TOPK
 
-    def __init__(self, kernels, owner, rank: int, world: int, cap: int, block: torch.Tensor, blocks, between_phases=None):
+    def __init__(self, kernels, owner, rank: int, world: int, cap: int, block: torch.Tensor, blocks, between_phases=None,
+                 fused_return: bool = True):
         import ctypes as C
 
         from . import binding as B
@@ -230,7 +231,7 @@ class PeerExchangePrefill:
         self.rank, self.world, self.cap = rank, world, cap
         self.device = kernels.t.device
         self.hidden, self.inter = kernels.dims
-        self.block, self.between_phases = block, between_phases
+        self.block, self.between_phases, self.fused_return = block, between_phases, fused_return
         offsets = (C.c_size_t * 6)()
         total = self.lib.padra_ep_exchange_bytes(world, cap, self.hidden, offsets)
         assert total and block.numel() >= total and block.dtype == torch.uint8
@@ -242,7 +243,7 @@ class PeerExchangePrefill:
         self.counts = torch.empty(EXPERTS, dtype=torch.int32, device=dev)
         self.gate = torch.empty((rows, self.inter), dtype=torch.uint16, device=dev)
         self.up = torch.empty((rows, self.inter), dtype=torch.uint16, device=dev)
-        self.down = torch.empty((rows, self.hidden), dtype=torch.uint16, device=dev)
+        self.down = None if fused_return else torch.empty((rows, self.hidden), dtype=torch.uint16, device=dev)
         self.transformed = torch.empty((self.MAX_GROUPED, max(self.hidden, self.inter)), dtype=torch.float16, device=dev)
         self.backend = KernelBackend(kernels)
         self.epoch = 0
@@ -291,13 +292,20 @@ class PeerExchangePrefill:
         B.check(lib.padra_ep_wait(base, 0, *geometry, self.epoch, bad, stream), "padra_ep_wait")
         B.check(lib.padra_ep_group_received(base, *geometry, B.ptr(self.groups), B.ptr(self.counts), self.MAX_GROUPED, bad, stream),
                 "padra_ep_group_received")
-        for part, target in ((0, self.gate), (1, self.up), (2, self.down)):
+        parts = ((0, self.gate), (1, self.up)) if self.fused_return else ((0, self.gate), (1, self.up), (2, self.down))
+        for part, target in parts:
             B.check(lib.padra_exl3_prefill_rows_launch(
                 k.t.descriptors.data_ptr(), layer, part, B.ptr(self.groups), B.ptr(self.counts), self.MAX_GROUPED, self.world * self.cap,
                 base + self.offsets[0], B.ptr(target), B.ptr(self.gate), B.ptr(self.up), B.ptr(k.table), B.ptr(self.transformed), bad,
                 stream, k.t.rate, self.hidden, self.inter), "padra_exl3_prefill_rows_launch")
-        B.check(lib.padra_ep_return(B.ptr(self.down), self.bases, self.rank, self.world, self.cap, self.hidden, self.epoch, bad, stream),
-                "padra_ep_return")
+        if self.fused_return:  # the down projection's epilogue stores the rows into their sources' blocks itself
+            B.check(lib.padra_ep_down_return(k.t.descriptors.data_ptr(), layer, B.ptr(self.groups), B.ptr(self.counts), self.MAX_GROUPED,
+                                             B.ptr(self.gate), B.ptr(self.up), B.ptr(k.table), B.ptr(self.transformed), self.bases,
+                                             self.rank, self.world, self.cap, self.epoch, bad, stream, k.t.rate, self.hidden, self.inter),
+                    "padra_ep_down_return")
+        else:
+            B.check(lib.padra_ep_return(B.ptr(self.down), self.bases, self.rank, self.world, self.cap, self.hidden, self.epoch, bad,
+                                        stream), "padra_ep_return")
         if self.between_phases:
             self.between_phases()
         B.check(lib.padra_ep_wait(base, 1, *geometry, self.epoch, bad, stream), "padra_ep_wait")
