@@ -71,12 +71,15 @@ __global__ void __launch_bounds__(256) GroupRowsKernel(const int *ids, int *grou
 // Thread t owns the 16 consecutive pairs from 16*t on; a scan over (destination, thread) keeps the order stable.
 __global__ void __launch_bounds__(1024) PlanKernel(const int *ids, const int *owner, int *order, int *position, int *send_ids,
                                                    long long *send_counts, int pairs, int world, int *bad) {
-  __shared__ int s_owner[kExperts], s_scan[kMaxRanks][1024 + 1], s_base[kMaxRanks + 1];
-  const int t = threadIdx.x, per = (pairs + 1023) / 1024, first = t * per;
+  __shared__ int s_owner[kExperts], s_warp_total[kMaxRanks][32], s_base[kMaxRanks + 1];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5, per = (pairs + 1023) / 1024, first = t * per;
   if (t < kExperts)
     s_owner[t] = owner[t];
   __syncthreads();
-  int mine[kMaxRanks] = {};
+  int mine[kMaxRanks];
+#pragma unroll
+  for (int r = 0; r < kMaxRanks; ++r)
+    mine[r] = 0;
   for (int i = 0; i < per; ++i) {
     const int pair = first + i;
     if (pair < pairs) {
@@ -84,43 +87,69 @@ __global__ void __launch_bounds__(1024) PlanKernel(const int *ids, const int *ow
       const int r = (e >= 0 && e < kExperts) ? s_owner[e] : -1;
       if (r < 0 || r >= world)
         Raise(bad);
-      else
-        ++mine[r];
+#pragma unroll
+      for (int q = 0; q < kMaxRanks; ++q)
+        mine[q] += (q == r);
     }
   }
-  for (int r = 0; r < world; ++r)
-    s_scan[r][t] = mine[r];
-  __syncthreads();
-  if (t < world) { // one thread per destination: exclusive scan over the 1024 threads' counts
-    int sum = 0;
-    for (int i = 0; i < 1024; ++i) {
-      const int v = s_scan[t][i];
-      s_scan[t][i] = sum;
-      sum += v;
+  // exclusive scan over the 1024 threads, all destinations at once: inside the warp with shuffles, across the warps
+  // through the warps' totals
+  int before[kMaxRanks];
+#pragma unroll
+  for (int r = 0; r < kMaxRanks; ++r) {
+    int inclusive = mine[r];
+#pragma unroll
+    for (int d = 1; d < 32; d *= 2) {
+      const int other = __shfl_up_sync(0xffffffffu, inclusive, d);
+      if (lane >= d)
+        inclusive += other;
     }
-    s_scan[t][1024] = sum;
+    before[r] = inclusive - mine[r];
+    if (lane == 31)
+      s_warp_total[r][warp] = inclusive;
+  }
+  __syncthreads();
+  if (warp < kMaxRanks) { // warp r turns the 32 warp totals of destination r into exclusive prefixes
+    const int total = s_warp_total[warp][lane];
+    int inclusive = total;
+#pragma unroll
+    for (int d = 1; d < 32; d *= 2) {
+      const int other = __shfl_up_sync(0xffffffffu, inclusive, d);
+      if (lane >= d)
+        inclusive += other;
+    }
+    s_warp_total[warp][lane] = inclusive - total;
+    if (lane == 31)
+      s_base[warp] = inclusive; // rows for destination `warp`, turned into first rows below
   }
   __syncthreads();
   if (t == 0) {
     int sum = 0;
-    for (int r = 0; r < world; ++r) {
+    for (int r = 0; r < kMaxRanks; ++r) {
+      const int n = r < world ? s_base[r] : 0;
+      if (r < world)
+        send_counts[r] = n;
       s_base[r] = sum;
-      sum += s_scan[r][1024];
-      send_counts[r] = s_scan[r][1024];
+      sum += n;
     }
-    s_base[world] = sum;
+    s_base[kMaxRanks] = sum;
   }
   __syncthreads();
   int cursor[kMaxRanks];
-  for (int r = 0; r < world; ++r)
-    cursor[r] = s_base[r] + s_scan[r][t];
+#pragma unroll
+  for (int r = 0; r < kMaxRanks; ++r)
+    cursor[r] = s_base[r] + s_warp_total[r][warp] + before[r];
   for (int i = 0; i < per; ++i) {
     const int pair = first + i;
     if (pair < pairs) {
       const int e = ids[pair];
       const int r = (e >= 0 && e < kExperts) ? s_owner[e] : -1;
       if (r >= 0 && r < world) {
-        const int at = cursor[r]++;
+        int at = 0;
+#pragma unroll
+        for (int q = 0; q < kMaxRanks; ++q)
+          if (q == r)
+            at = cursor[q]++;
         order[at] = pair, send_ids[at] = e, position[pair] = at;
       } else {
         position[pair] = 0;

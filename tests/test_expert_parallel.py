@@ -236,3 +236,20 @@ def test_peer_memory_exchange_on_one_gpu_equals_the_single_gpu_prefill(oracle, g
         torch.cuda.synchronize()
         assert kernels[rank].bad_flag() == 0
         assert np.array_equal(outputs[rank].cpu().numpy(), want.cpu().numpy()), f"rank {rank} differs from the single-GPU path"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world,tokens", [(1, 8), (2, 333), (8, 2048)])
+def test_plan_kernel_equals_the_host_plan(gpu, world, tokens):
+    from padra_b200.experts import ExpertKernels, ExpertTable, zipf_routing
+
+    table = ExpertTable(1, 256, 128, 4, gpu).fill_random(1)
+    backend = EP.KernelBackend(ExpertKernels(table))
+    ids, _ = zipf_routing(tokens, seed=world, device=gpu)
+    popularity = np.bincount(ids.reshape(-1).cpu().numpy(), minlength=64)
+    owner = EP.balanced_placement(popularity, world)
+    want = EP.make_plan(ids.reshape(-1), torch.from_numpy(owner.astype(np.int64)).to(gpu), world)
+    got = backend.plan(ids.reshape(-1), torch.from_numpy(owner).to(gpu), world)
+    torch.cuda.synchronize()
+    assert torch.equal(got.order, want.order) and torch.equal(got.position, want.position)
+    assert torch.equal(got.send_ids, want.send_ids) and got.send_counts.tolist() == want.send_counts.tolist()
