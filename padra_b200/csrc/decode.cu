@@ -557,12 +557,45 @@ int LaunchCombine(float *x, const float *down, const float *weights, int *bad, i
   return CudaStatus(cudaGetLastError());
 }
 
+// The same with four columns per thread (8-byte loads of BF16 rows, 16-byte accesses of x) for aligned buffers.
+__global__ void __launch_bounds__(128) CombinePackedWideKernel(float *x, const unsigned short *down, const float *weights, int rows, int hidden,
+                                                               int *bad, bool residual) {
+  const int row = blockIdx.y, col = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (row >= rows || col >= hidden)
+    return;
+  float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int s = 0; s < kTopK; ++s) {
+    const uint2 bits = *reinterpret_cast<const uint2 *>(down + (static_cast<size_t>(row) * kTopK + s) * hidden + col);
+    const float w = weights[row * kTopK + s];
+    const float d[4] = {FromBF16Bits(bits.x & 0xffffu), FromBF16Bits(bits.x >> 16), FromBF16Bits(bits.y & 0xffffu),
+                        FromBF16Bits(bits.y >> 16)};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      sum[j] = RoundBF16(__fadd_rn(sum[j], RoundBF16(__fmul_rn(d[j], w))));
+  }
+  float4 *target = reinterpret_cast<float4 *>(x + static_cast<size_t>(row) * hidden + col);
+  const float4 old = *target;
+  float4 v;
+  v.x = residual ? RoundBF16(__fadd_rn(old.x, sum[0])) : sum[0];
+  v.y = residual ? RoundBF16(__fadd_rn(old.y, sum[1])) : sum[1];
+  v.z = residual ? RoundBF16(__fadd_rn(old.z, sum[2])) : sum[2];
+  v.w = residual ? RoundBF16(__fadd_rn(old.w, sum[3])) : sum[3];
+  if (!isfinite(v.x) || !isfinite(v.y) || !isfinite(v.z) || !isfinite(v.w))
+    Raise(bad);
+  *target = v;
+}
+
 int LaunchCombinePacked(float *x, const unsigned short *down, const float *weights, int tokens, int *bad, int residual,
                         int hidden, cudaStream_t stream) {
   if (!x || !down || !weights || !bad || tokens < 1 || hidden < 1)
     return PADRA_INVALID_ARGUMENT;
-  CombineKernel<unsigned short>
-      <<<dim3((hidden + 127) / 128, tokens), 128, 0, stream>>>(x, down, weights, tokens, hidden, bad, residual != 0);
+  if (hidden % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(down) % 8 == 0)
+    CombinePackedWideKernel<<<dim3((hidden / 4 + 127) / 128, tokens), 128, 0, stream>>>(x, down, weights, tokens, hidden, bad,
+                                                                                       residual != 0);
+  else
+    CombineKernel<unsigned short>
+        <<<dim3((hidden + 127) / 128, tokens), 128, 0, stream>>>(x, down, weights, tokens, hidden, bad, residual != 0);
   return CudaStatus(cudaGetLastError());
 }
 

@@ -76,21 +76,30 @@ __global__ void __launch_bounds__(1024) PlanKernel(const int *ids, const int *ow
   if (t < kExperts)
     s_owner[t] = owner[t];
   __syncthreads();
+  // the thread's pairs: at most 16 (2048 tokens), fetched up front so that the loads overlap
+  constexpr int kPer = 16;
+  int dest[kPer], expert[kPer];
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int pair = first + i;
+    expert[i] = (i < per && pair < pairs) ? ids[pair] : -1;
+  }
   int mine[kMaxRanks];
 #pragma unroll
   for (int r = 0; r < kMaxRanks; ++r)
     mine[r] = 0;
-  for (int i = 0; i < per; ++i) {
-    const int pair = first + i;
-    if (pair < pairs) {
-      const int e = ids[pair];
-      const int r = (e >= 0 && e < kExperts) ? s_owner[e] : -1;
-      if (r < 0 || r >= world)
-        Raise(bad);
 #pragma unroll
-      for (int q = 0; q < kMaxRanks; ++q)
-        mine[q] += (q == r);
+  for (int i = 0; i < kPer; ++i) {
+    const int e = expert[i];
+    int r = (e >= 0 && e < kExperts) ? s_owner[e] : -1;
+    if ((i < per && first + i < pairs) && (r < 0 || r >= world)) {
+      Raise(bad);
+      r = -1;
     }
+    dest[i] = r;
+#pragma unroll
+    for (int q = 0; q < kMaxRanks; ++q)
+      mine[q] += (q == r);
   }
   // exclusive scan over the 1024 threads, all destinations at once: inside the warp with shuffles, across the warps
   // through the warps' totals
@@ -139,21 +148,18 @@ __global__ void __launch_bounds__(1024) PlanKernel(const int *ids, const int *ow
 #pragma unroll
   for (int r = 0; r < kMaxRanks; ++r)
     cursor[r] = s_base[r] + s_warp_total[r][warp] + before[r];
-  for (int i = 0; i < per; ++i) {
-    const int pair = first + i;
-    if (pair < pairs) {
-      const int e = ids[pair];
-      const int r = (e >= 0 && e < kExperts) ? s_owner[e] : -1;
-      if (r >= 0 && r < world) {
-        int at = 0;
 #pragma unroll
-        for (int q = 0; q < kMaxRanks; ++q)
-          if (q == r)
-            at = cursor[q]++;
-        order[at] = pair, send_ids[at] = e, position[pair] = at;
-      } else {
-        position[pair] = 0;
-      }
+  for (int i = 0; i < kPer; ++i) {
+    const int pair = first + i, r = dest[i];
+    if (i < per && pair < pairs) {
+      int at = 0;
+#pragma unroll
+      for (int q = 0; q < kMaxRanks; ++q)
+        if (q == r)
+          at = cursor[q]++;
+      if (r >= 0)
+        order[at] = pair, send_ids[at] = expert[i];
+      position[pair] = r >= 0 ? at : 0;
     }
   }
 }
@@ -254,14 +260,26 @@ __global__ void __launch_bounds__(256) DispatchKernel(const float *activations, 
       const size_t slot = static_cast<size_t>(rank) * cap + (row - s_first[d]);
       const float *from = activations + static_cast<size_t>(pair >> 3) * hidden;
       unsigned short *to = reinterpret_cast<unsigned short *>(peers.base[d] + layout.rows) + slot * hidden;
-      for (int k = lane * 8; k < hidden; k += 256) {
-        const float4 a = *reinterpret_cast<const float4 *>(from + k), b = *reinterpret_cast<const float4 *>(from + k + 4);
-        uint4 bits;
-        bits.x = static_cast<unsigned>(BF16Bits(a.x)) | (static_cast<unsigned>(BF16Bits(a.y)) << 16);
-        bits.y = static_cast<unsigned>(BF16Bits(a.z)) | (static_cast<unsigned>(BF16Bits(a.w)) << 16);
-        bits.z = static_cast<unsigned>(BF16Bits(b.x)) | (static_cast<unsigned>(BF16Bits(b.y)) << 16);
-        bits.w = static_cast<unsigned>(BF16Bits(b.z)) | (static_cast<unsigned>(BF16Bits(b.w)) << 16);
-        *reinterpret_cast<uint4 *>(to + k) = bits;
+      for (int k0 = lane * 8; k0 < hidden; k0 += 1024) { // four 16-byte pieces per lane in flight
+        float4 a[4], b[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int k = k0 + 256 * u;
+          if (k < hidden)
+            a[u] = *reinterpret_cast<const float4 *>(from + k), b[u] = *reinterpret_cast<const float4 *>(from + k + 4);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int k = k0 + 256 * u;
+          if (k < hidden) {
+            uint4 bits;
+            bits.x = static_cast<unsigned>(BF16Bits(a[u].x)) | (static_cast<unsigned>(BF16Bits(a[u].y)) << 16);
+            bits.y = static_cast<unsigned>(BF16Bits(a[u].z)) | (static_cast<unsigned>(BF16Bits(a[u].w)) << 16);
+            bits.z = static_cast<unsigned>(BF16Bits(b[u].x)) | (static_cast<unsigned>(BF16Bits(b[u].y)) << 16);
+            bits.w = static_cast<unsigned>(BF16Bits(b[u].z)) | (static_cast<unsigned>(BF16Bits(b[u].w)) << 16);
+            *reinterpret_cast<uint4 *>(to + k) = bits;
+          }
+        }
       }
       if (!lane)
         reinterpret_cast<int *>(peers.base[d] + layout.ids)[slot] = send_ids[row];
@@ -381,8 +399,17 @@ __global__ void __launch_bounds__(256) ReturnKernel(const unsigned short *down, 
     const uint4 *from = reinterpret_cast<const uint4 *>(down + (static_cast<size_t>(s) * cap + k) * hidden);
     uint4 *to = reinterpret_cast<uint4 *>(reinterpret_cast<unsigned short *>(peers.base[s] + layout.returned) +
                                           static_cast<size_t>(s_from[s] + k) * hidden);
-    for (int c = lane; c < hidden / 8; c += 32)
-      to[c] = from[c];
+    for (int c0 = lane; c0 < hidden / 8; c0 += 128) { // four 16-byte pieces per lane in flight
+      uint4 piece[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (c0 + 32 * u < hidden / 8)
+          piece[u] = from[c0 + 32 * u];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (c0 + 32 * u < hidden / 8)
+          to[c0 + 32 * u] = piece[u];
+    }
   }
   __threadfence_system();
   __syncthreads();
@@ -471,7 +498,7 @@ int LaunchGroupRows(const int *ids, int *groups, int *counts, int rows, int grou
 
 int LaunchPlan(const int *ids, const int *owner, int *order, int *position, int *send_ids, long long *send_counts, int pairs,
                int world, int *bad, cudaStream_t stream) {
-  if (!ids || !owner || !order || !position || !send_ids || !send_counts || !bad || pairs < 1 || pairs > 2048 * kTopK ||
+  if (!ids || !owner || !order || !position || !send_ids || !send_counts || !bad || pairs < 1 || pairs > 16 * 1024 ||
       world < 1 || world > kMaxRanks)
     return PADRA_INVALID_ARGUMENT;
   PlanKernel<<<1, 1024, 0, stream>>>(ids, owner, order, position, send_ids, send_counts, pairs, world, bad);

@@ -36,29 +36,58 @@ __global__ void __launch_bounds__(256) GroupKernel(const int *ids, int *groups, 
     }
   }
   __syncthreads();
-  for (int base = 0; base < pairs; base += 256) {
-    const int pair = base + threadIdx.x;
-    const bool mine = pair < pairs && ids[pair] == expert;
-    const unsigned votes = __ballot_sync(0xffffffffu, mine);
-    if (!lane)
-      warp_counts[warp] = __popc(votes);
-    __syncthreads();
-    if (!threadIdx.x) {
-      int n = total;
-      for (int w = 0; w < 8; ++w) {
-        warp_offsets[w] = n;
-        n += warp_counts[w];
-      }
-      total = n;
+  // thread t owns the consecutive pairs [t*per, (t+1)*per): count its matches, scan the counts over the CTA (stable in
+  // pair order), then write
+  const int per = (pairs + 255) / 256, first = threadIdx.x * per;
+  const int last = first + per < pairs ? first + per : pairs;
+  const bool wide = per % 4 == 0 && first + per <= pairs && (reinterpret_cast<uintptr_t>(ids) & 15) == 0; // 16-byte groups
+  int mine = 0;
+  if (wide) {
+    for (int pair = first; pair < last; pair += 4) {
+      const int4 e = *reinterpret_cast<const int4 *>(ids + pair);
+      mine += (e.x == expert) + (e.y == expert) + (e.z == expert) + (e.w == expert);
     }
-    __syncthreads();
-    if (mine) {
-      const int at = warp_offsets[warp] + __popc(votes & ((1u << lane) - 1u));
+  } else {
+    for (int pair = first; pair < last; ++pair)
+      mine += ids[pair] == expert;
+  }
+  int inclusive = mine;
+#pragma unroll
+  for (int d = 1; d < 32; d *= 2) {
+    const int other = __shfl_up_sync(0xffffffffu, inclusive, d);
+    if (lane >= d)
+      inclusive += other;
+  }
+  if (lane == 31)
+    warp_counts[warp] = inclusive;
+  __syncthreads();
+  if (!threadIdx.x) {
+    int n = 0;
+    for (int w = 0; w < 8; ++w) {
+      warp_offsets[w] = n;
+      n += warp_counts[w];
+    }
+    total = n;
+  }
+  __syncthreads();
+  int at = warp_offsets[warp] + inclusive - mine;
+  auto append = [&](int id, int pair) {
+    if (id == expert) {
       if (at < tokens)
         groups[expert * tokens + at] = pair;
+      ++at;
     }
-    __syncthreads();
+  };
+  if (wide) {
+    for (int pair = first; pair < last && mine; pair += 4) {
+      const int4 e = *reinterpret_cast<const int4 *>(ids + pair);
+      append(e.x, pair), append(e.y, pair + 1), append(e.z, pair + 2), append(e.w, pair + 3);
+    }
+  } else {
+    for (int pair = first; pair < last; ++pair)
+      append(ids[pair], pair);
   }
+  __syncthreads();
   if (!threadIdx.x) {
     if (total > tokens)
       Raise(bad);

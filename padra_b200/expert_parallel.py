@@ -248,6 +248,7 @@ class PeerExchangePrefill:
         self.up = torch.empty((rows, self.inter), dtype=torch.uint16, device=dev)
         self.down = None if fused_return else torch.empty((rows, self.hidden), dtype=torch.uint16, device=dev)
         self.transformed = torch.empty((self.MAX_GROUPED, max(self.hidden, self.inter)), dtype=torch.float16, device=dev)
+        self.transformed_up = torch.empty((self.MAX_GROUPED, self.hidden), dtype=torch.float16, device=dev)
         self.backend = KernelBackend(kernels)
         self.epoch = 0
 
@@ -295,12 +296,23 @@ class PeerExchangePrefill:
         B.check(lib.padra_ep_wait(base, 0, *geometry, self.epoch, bad, stream), "padra_ep_wait")
         B.check(lib.padra_ep_group_received(base, *geometry, B.ptr(self.groups), B.ptr(self.counts), self.MAX_GROUPED, bad, stream),
                 "padra_ep_group_received")
-        parts = ((0, self.gate), (1, self.up)) if self.fused_return else ((0, self.gate), (1, self.up), (2, self.down))
-        for part, target in parts:
+        def project(part, target, transformed, on):
             B.check(lib.padra_exl3_prefill_rows_launch(
                 k.t.descriptors.data_ptr(), layer, part, B.ptr(self.groups), B.ptr(self.counts), self.MAX_GROUPED, self.world * self.cap,
-                base + self.offsets[0], B.ptr(target), B.ptr(self.gate), B.ptr(self.up), B.ptr(k.table), B.ptr(self.transformed), bad,
-                stream, k.t.rate, self.hidden, self.inter), "padra_exl3_prefill_rows_launch")
+                base + self.offsets[0], B.ptr(target), B.ptr(self.gate), B.ptr(self.up), B.ptr(k.table), B.ptr(transformed), bad,
+                on, k.t.rate, self.hidden, self.inter), "padra_exl3_prefill_rows_launch")
+
+        # the up projection runs on a second stream beside the gate projection; both join before the down projection
+        main, side = torch.cuda.current_stream(), k.side_stream()
+        fork, join = torch.cuda.Event(), torch.cuda.Event()
+        fork.record(main)
+        side.wait_event(fork)
+        project(1, self.up, self.transformed_up, side.cuda_stream)
+        join.record(side)
+        project(0, self.gate, self.transformed, stream)
+        main.wait_event(join)
+        if not self.fused_return:
+            project(2, self.down, self.transformed, stream)
         if self.fused_return:  # the down projection's epilogue stores the rows into their sources' blocks itself
             B.check(lib.padra_ep_down_return(k.t.descriptors.data_ptr(), layer, B.ptr(self.groups), B.ptr(self.counts), self.MAX_GROUPED,
                                              B.ptr(self.gate), B.ptr(self.up), B.ptr(k.table), B.ptr(self.transformed), self.bases,

@@ -231,8 +231,10 @@ class ExpertKernels:
                                                 self.t.rate, *self.dims)
         B.check(st, "padra_exl3_prefill_launch")
 
-    def prefill_layer(self, layer, ids, routing, normalized, x, tokens, stream=None, tensor_memory=True):
-        """gate, up, down (SwiGLU inside) and combine with residual for a prefill chunk; x updated in place."""
+    def prefill_layer(self, layer, ids, routing, normalized, x, tokens, stream=None, tensor_memory=True, overlap=True):
+        """gate, up, down (SwiGLU inside) and combine with residual for a prefill chunk; x updated in place.
+        overlap: the up projection runs on a second stream beside the gate projection (its input transform under the
+        gate GEMM, its first CTAs in the gate GEMM's tail); both join before the down projection."""
         dev, (hidden, inter) = self.t.device, self.dims
         pairs = tokens * TOPK
         key = ("prefill", tokens)
@@ -240,13 +242,31 @@ class ExpertKernels:
             self._workspace[key] = (torch.empty((pairs, inter), dtype=torch.uint16, device=dev),
                                     torch.empty((pairs, inter), dtype=torch.uint16, device=dev),
                                     torch.empty((pairs, hidden), dtype=torch.uint16, device=dev),
-                                    torch.empty((pairs, max(hidden, inter)), dtype=torch.float16, device=dev))
-        gate, up, down, transformed = self._workspace[key]
+                                    torch.empty((pairs, max(hidden, inter)), dtype=torch.float16, device=dev),
+                                    torch.empty((pairs, hidden), dtype=torch.float16, device=dev))
+        gate, up, down, transformed, transformed_up = self._workspace[key]
         sched = self.group_and_schedule(ids, tokens, stream)
-        for part, target in ((0, gate), (1, up), (2, down)):
-            self.prefill_launch(layer, part, ids, sched, normalized, target, gate, up, transformed, tokens, stream, tensor_memory)
+        if overlap and tensor_memory:
+            main = stream or torch.cuda.current_stream()
+            side = self.side_stream()
+            fork, join = torch.cuda.Event(), torch.cuda.Event()
+            fork.record(main)
+            side.wait_event(fork)
+            self.prefill_launch(layer, 1, ids, sched, normalized, up, gate, up, transformed_up, tokens, side, tensor_memory)
+            join.record(side)
+            self.prefill_launch(layer, 0, ids, sched, normalized, gate, gate, up, transformed, tokens, main, tensor_memory)
+            main.wait_event(join)
+            self.prefill_launch(layer, 2, ids, sched, normalized, down, gate, up, transformed, tokens, main, tensor_memory)
+        else:
+            for part, target in ((0, gate), (1, up), (2, down)):
+                self.prefill_launch(layer, part, ids, sched, normalized, target, gate, up, transformed, tokens, stream, tensor_memory)
         self.combine_packed(x, down, routing, tokens, True, stream)
         return gate, up, down
+
+    def side_stream(self):
+        if getattr(self, "_side_stream", None) is None:
+            self._side_stream = torch.cuda.Stream(device=self.t.device)
+        return self._side_stream
 
     # whole decode layer
     def decode_workspace(self, tokens):
