@@ -325,43 +325,65 @@ __global__ void WaitFlagsKernel(const unsigned *flags, int world, unsigned epoch
 __global__ void __launch_bounds__(256) GroupRegionsKernel(const int *ids, const int4 *meta, int world, int cap, int *groups, int *counts,
                                                           int stride, int *bad) {
   const int expert = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  __shared__ int warp_counts[8], warp_offsets[8], total;
-  if (!threadIdx.x)
-    total = 0;
-  __syncthreads();
-  for (int s = 0; s < world; ++s) {
-    int n = meta[s].x;
-    if (n < 0 || n > cap) {
-      if (!threadIdx.x && !expert)
-        Raise(bad);
-      n = 0;
+  __shared__ int s_first[kMaxRanks + 1], warp_counts[8], warp_offsets[8], total;
+  if (!threadIdx.x) {
+    int sum = 0;
+    for (int s = 0; s < world; ++s) {
+      int n = meta[s].x;
+      if (n < 0 || n > cap) {
+        if (!expert)
+          Raise(bad);
+        n = 0;
+      }
+      s_first[s] = sum;
+      sum += n;
     }
-    for (int base = 0; base < n; base += 256) {
-      const int k = base + threadIdx.x;
-      const int row = s * cap + k;
-      const int id = k < n ? ids[row] : -1;
-      if (k < n && (id < 0 || id >= kExperts) && expert == 0)
-        Raise(bad);
-      const bool mine = id == expert;
-      const unsigned votes = __ballot_sync(0xffffffffu, mine);
-      if (!lane)
-        warp_counts[warp] = __popc(votes);
-      __syncthreads();
-      if (!threadIdx.x) {
-        int at = total;
-        for (int w = 0; w < 8; ++w) {
-          warp_offsets[w] = at;
-          at += warp_counts[w];
-        }
-        total = at;
-      }
-      __syncthreads();
-      if (mine) {
-        const int at = warp_offsets[warp] + __popc(votes & ((1u << lane) - 1u));
-        if (at < stride)
-          groups[static_cast<size_t>(expert) * stride + at] = row;
-      }
-      __syncthreads();
+    s_first[world] = sum;
+  }
+  __syncthreads();
+  // the valid rows of all regions, in region order, form one list; thread t owns a contiguous piece of it
+  const int valid = s_first[world], per = (valid + 255) / 256;
+  const int first = threadIdx.x * per, last = first + per < valid ? first + per : valid;
+  int region = 0;
+  while (region + 1 < world && s_first[region + 1] <= first)
+    ++region;
+  int mine = 0;
+  for (int v = first, s = region; v < last; ++v) {
+    while (s + 1 < world && s_first[s + 1] <= v)
+      ++s;
+    const int id = ids[s * cap + (v - s_first[s])];
+    if ((id < 0 || id >= kExperts) && !expert)
+      Raise(bad);
+    mine += id == expert;
+  }
+  int inclusive = mine;
+#pragma unroll
+  for (int d = 1; d < 32; d *= 2) {
+    const int other = __shfl_up_sync(0xffffffffu, inclusive, d);
+    if (lane >= d)
+      inclusive += other;
+  }
+  if (lane == 31)
+    warp_counts[warp] = inclusive;
+  __syncthreads();
+  if (!threadIdx.x) {
+    int n = 0;
+    for (int w = 0; w < 8; ++w) {
+      warp_offsets[w] = n;
+      n += warp_counts[w];
+    }
+    total = n;
+  }
+  __syncthreads();
+  int at = warp_offsets[warp] + inclusive - mine;
+  for (int v = first, s = region; v < last && mine; ++v) {
+    while (s + 1 < world && s_first[s + 1] <= v)
+      ++s;
+    const int row = s * cap + (v - s_first[s]);
+    if (ids[row] == expert) {
+      if (at < stride)
+        groups[static_cast<size_t>(expert) * stride + at] = row;
+      ++at;
     }
   }
   if (!threadIdx.x) {
@@ -453,7 +475,7 @@ int LaunchDispatch(const float *activations, const int *order, const int *send_i
       reinterpret_cast<uintptr_t>(activations) % 16)
     return PADRA_INVALID_ARGUMENT;
   const int blocks = (pairs + 7) / 8;
-  DispatchKernel<<<blocks < 148 * 4 ? blocks : 148 * 4, 256, 0, stream>>>(activations, order, send_ids, send_counts, peers,
+  DispatchKernel<<<blocks < 148 * 8 ? blocks : 148 * 8, 256, 0, stream>>>(activations, order, send_ids, send_counts, peers,
                                                                           MakeExchangeLayout(world, cap, hidden), rank, world, cap, pairs,
                                                                           hidden, epoch, bad);
   return CudaStatus(cudaGetLastError());
@@ -485,7 +507,7 @@ int LaunchReturn(const unsigned short *down, const unsigned long long *bases, in
   if (!down || !bases || !bad || rank < 0 || rank >= world || !ExchangeBytes(world, cap, hidden, nullptr) ||
       !FillPeers(peers, bases, world) || reinterpret_cast<uintptr_t>(down) % 16)
     return PADRA_INVALID_ARGUMENT;
-  ReturnKernel<<<148 * 4, 256, 0, stream>>>(down, peers, MakeExchangeLayout(world, cap, hidden), rank, world, cap, hidden, epoch, bad);
+  ReturnKernel<<<148 * 8, 256, 0, stream>>>(down, peers, MakeExchangeLayout(world, cap, hidden), rank, world, cap, hidden, epoch, bad);
   return CudaStatus(cudaGetLastError());
 }
 
