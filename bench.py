@@ -216,7 +216,8 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
     x0 = bf16_values(torch.randn((local, HIDDEN), device=dev, generator=g))
     routing, owners = {}, []
     for layer in range(layers):
-        sample, _ = zipf_routing(2048, seed=layer, device="cpu", popularity_seed=layer)
+        # popularity as a server would have measured it over earlier traffic: a long sample of the layer's routing
+        sample, _ = zipf_routing(16384, seed=layer, device="cpu", popularity_seed=layer)
         popularity = np.bincount(sample.reshape(-1).numpy(), minlength=EXPERTS)
         owners.append(EP.balanced_placement(popularity, world))
         for c, n in chunks:

@@ -160,6 +160,11 @@ PADRA_API int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer,
  *     index space to padra_exl3_prefill_rows_launch: rows = world*cap, input_rows = block + offsets[0].
  *   padra_ep_return: down rows (same index space) go back into their source's block at the send rows they came
  *     from, then a flag with `epoch`; after padra_ep_wait(which = 1), padra_ep_combine reads block + offsets[3].
+ *   Splitting a projection: block_begin / block_count of padra_exl3_prefill_rows_launch select the 128-output blocks a
+ *     launch computes (0, 0 = all); only the launch with block_begin == 0 runs the input transform, later launches of
+ *     the same call reuse `transformed`.  column_begin / column_count of padra_ep_return select the columns that are
+ *     sent (0, 0 = all) and announce says whether this launch raises the flags (the last one of a call must).  With
+ *     the two, the first half of the down rows can travel while the second half is still being computed.
  *   padra_ep_down_return: the down projection (part 2 of padra_exl3_prefill_rows_launch on the received index space)
  *     fused with padra_ep_return: the epilogue of the grouped GEMM stores every finished row straight into its source's
  *     block, so the transfer overlaps the remaining tiles, and the CTA that finishes last raises the flags.
@@ -174,7 +179,8 @@ PADRA_API int padra_ep_wait(const void *block, int which, int world, int cap, in
 PADRA_API int padra_ep_group_received(const void *block, int world, int cap, int hidden, int *groups, int *counts,
                                       int group_stride, int *bad, padra_stream stream);
 PADRA_API int padra_ep_return(const unsigned short *down_rows, const unsigned long long *peer_blocks, int rank, int world,
-                              int cap, int hidden, unsigned epoch, int *bad, padra_stream stream);
+                              int cap, int hidden, unsigned epoch, int *bad, padra_stream stream, int column_begin,
+                              int column_count, int announce);
 PADRA_API int padra_ep_down_return(const padra_matrix *matrices, int layer, const int *groups, const int *counts,
                                    int group_stride, const unsigned short *gate, const unsigned short *up,
                                    const unsigned short *table, void *transformed, const unsigned long long *peer_blocks,
@@ -191,7 +197,8 @@ PADRA_API int padra_exl3_prefill_rows_launch(const padra_matrix *matrices, int l
                                              const unsigned short *input_rows, unsigned short *output,
                                              const unsigned short *gate, const unsigned short *up,
                                              const unsigned short *table, void *transformed, int *bad,
-                                             padra_stream stream, int rate, int hidden, int inter);
+                                             padra_stream stream, int rate, int hidden, int inter, int block_begin,
+                                             int block_count);
 PADRA_API int padra_ep_combine(float *x, const unsigned short *down_rows, const int *position, const float *weights,
                                int tokens, int *bad, int residual, int hidden, padra_stream stream);
 

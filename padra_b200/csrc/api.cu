@@ -141,8 +141,8 @@ int padra_ep_group_received(const void *block, int world, int cap, int hidden, i
 }
 
 int padra_ep_return(const unsigned short *down_rows, const unsigned long long *peer_blocks, int rank, int world, int cap, int hidden,
-                    unsigned epoch, int *bad, padra_stream stream) {
-  return LaunchReturn(down_rows, peer_blocks, rank, world, cap, hidden, epoch, bad, S(stream));
+                    unsigned epoch, int *bad, padra_stream stream, int column_begin, int column_count, int announce) {
+  return LaunchReturn(down_rows, peer_blocks, rank, world, cap, hidden, epoch, bad, S(stream), column_begin, column_count, announce);
 }
 
 int padra_ep_down_return(const padra_matrix *matrices, int layer, const int *groups, const int *counts, int group_stride,
@@ -175,14 +175,15 @@ int padra_ep_group_rows(const int *ids, int *groups, int *counts, int rows, int 
 int padra_exl3_prefill_rows_launch(const padra_matrix *matrices, int layer, int part, const int *groups, const int *counts,
                                    int group_stride, int rows, const unsigned short *input_rows, unsigned short *output,
                                    const unsigned short *gate, const unsigned short *up, const unsigned short *table,
-                                   void *transformed, int *bad, padra_stream stream, int rate, int hidden, int inter) {
+                                   void *transformed, int *bad, padra_stream stream, int rate, int hidden, int inter,
+                                   int block_begin, int block_count) {
   if (!RateOk(rate))
     return PADRA_UNSUPPORTED;
   if (!matrices || !groups || !counts || !output || !transformed || !bad || part < 0 || part > 2 || layer < 0 || hidden < 128 ||
       inter < 128 || (hidden % 128) || (inter % 128) || (part == 2 ? (!gate || !up || !table) : !input_rows))
     return PADRA_INVALID_ARGUMENT;
   return LaunchPrefillRows(matrices, layer, part, groups, counts, group_stride, rows, input_rows, output, gate, up, table,
-                           transformed, bad, S(stream), rate, hidden, inter);
+                           transformed, bad, S(stream), rate, hidden, inter, block_begin, block_count);
 }
 
 int padra_ep_combine(float *x, const unsigned short *down_rows, const int *position, const float *weights, int tokens, int *bad,

@@ -395,7 +395,8 @@ __global__ void __launch_bounds__(256) GroupRegionsKernel(const int *ids, const 
 
 // The down rows of region s go back to rank s, to the send rows they came from.
 __global__ void __launch_bounds__(256) ReturnKernel(const unsigned short *down, PeerBlocks peers, ExchangeLayout layout, int rank, int world,
-                                                    int cap, int hidden, unsigned epoch, int *bad) {
+                                                    int cap, int hidden, unsigned epoch, int *bad, int column_begin, int column_count,
+                                                    int announce) {
   __shared__ int s_first[kMaxRanks + 1], s_from[kMaxRanks], s_last;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (!threadIdx.x) {
@@ -418,21 +419,23 @@ __global__ void __launch_bounds__(256) ReturnKernel(const unsigned short *down, 
     while (s + 1 < world && s_first[s + 1] <= item)
       ++s;
     const int k = item - s_first[s];
-    const uint4 *from = reinterpret_cast<const uint4 *>(down + (static_cast<size_t>(s) * cap + k) * hidden);
+    const uint4 *from = reinterpret_cast<const uint4 *>(down + (static_cast<size_t>(s) * cap + k) * hidden + column_begin);
     uint4 *to = reinterpret_cast<uint4 *>(reinterpret_cast<unsigned short *>(peers.base[s] + layout.returned) +
-                                          static_cast<size_t>(s_from[s] + k) * hidden);
-    for (int c0 = lane; c0 < hidden / 8; c0 += 128) { // four 16-byte pieces per lane in flight
+                                          static_cast<size_t>(s_from[s] + k) * hidden + column_begin);
+    for (int c0 = lane; c0 < column_count / 8; c0 += 128) { // four 16-byte pieces per lane in flight
       uint4 piece[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u)
-        if (c0 + 32 * u < hidden / 8)
+        if (c0 + 32 * u < column_count / 8)
           piece[u] = from[c0 + 32 * u];
 #pragma unroll
       for (int u = 0; u < 4; ++u)
-        if (c0 + 32 * u < hidden / 8)
+        if (c0 + 32 * u < column_count / 8)
           to[c0 + 32 * u] = piece[u];
     }
   }
+  if (!announce) // a later launch on the same stream sends the rest of the columns and raises the flags
+    return;
   __threadfence_system();
   __syncthreads();
   unsigned *ticket = reinterpret_cast<unsigned *>(peers.base[rank] + layout.tickets) + 1;
@@ -502,12 +505,16 @@ int LaunchGroupRegions(const void *block, int world, int cap, int hidden, int *g
 }
 
 int LaunchReturn(const unsigned short *down, const unsigned long long *bases, int rank, int world, int cap, int hidden, unsigned epoch,
-                 int *bad, cudaStream_t stream) {
+                 int *bad, cudaStream_t stream, int column_begin, int column_count, int announce) {
   PeerBlocks peers;
+  if (column_count == 0)
+    column_begin = 0, column_count = hidden;
   if (!down || !bases || !bad || rank < 0 || rank >= world || !ExchangeBytes(world, cap, hidden, nullptr) ||
-      !FillPeers(peers, bases, world) || reinterpret_cast<uintptr_t>(down) % 16)
+      !FillPeers(peers, bases, world) || reinterpret_cast<uintptr_t>(down) % 16 || column_begin < 0 || column_count < 8 ||
+      (column_begin % 8) || (column_count % 8) || column_begin + column_count > hidden)
     return PADRA_INVALID_ARGUMENT;
-  ReturnKernel<<<148 * 8, 256, 0, stream>>>(down, peers, MakeExchangeLayout(world, cap, hidden), rank, world, cap, hidden, epoch, bad);
+  ReturnKernel<<<148 * 8, 256, 0, stream>>>(down, peers, MakeExchangeLayout(world, cap, hidden), rank, world, cap, hidden, epoch, bad,
+                                            column_begin, column_count, announce);
   return CudaStatus(cudaGetLastError());
 }
 

@@ -40,7 +40,7 @@ int LaunchTileProjection(const Matrix *matrices, int layer, int part, const int 
 int LaunchPrefillRows(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, int group_stride, int rows,
                       const unsigned short *input_rows, unsigned short *output, const unsigned short *gate,
                       const unsigned short *up, const unsigned short *table, void *transformed, int *bad, cudaStream_t stream,
-                      int rate, int hidden, int inter);
+                      int rate, int hidden, int inter, int block_begin = 0, int block_count = 0);
 size_t ExchangeBytes(int world, int cap, int hidden, size_t *offsets);
 int LaunchDispatch(const float *activations, const int *order, const int *send_ids, const long long *send_counts,
                    const unsigned long long *bases, int rank, int world, int cap, int pairs, int hidden, unsigned epoch, int *bad,
@@ -49,7 +49,7 @@ int LaunchWaitFlags(const void *block, int which, int world, int cap, int hidden
 int LaunchGroupRegions(const void *block, int world, int cap, int hidden, int *groups, int *counts, int group_stride, int *bad,
                        cudaStream_t stream);
 int LaunchReturn(const unsigned short *down, const unsigned long long *bases, int rank, int world, int cap, int hidden, unsigned epoch,
-                 int *bad, cudaStream_t stream);
+                 int *bad, cudaStream_t stream, int column_begin = 0, int column_count = 0, int announce = 1);
 int LaunchPlan(const int *ids, const int *owner, int *order, int *position, int *send_ids, long long *send_counts, int pairs,
                int world, int *bad, cudaStream_t stream);
 int LaunchPrefillDownReturn(const Matrix *matrices, int layer, const int *groups, const int *counts, int group_stride,

@@ -79,6 +79,7 @@ struct PrefillArgs {
   int group_stride; // rows of `groups` per expert = the most pairs one expert can hold
   int pairs_total;  // pairs (rows of `output`) in the call
   int hidden, inter;
+  int block_begin, block_count; // the 128-output blocks this launch computes (a launch may take a part of them)
   int *bad;
   // Expert-parallel down projection: the rows do not go to `output` but straight back to the ranks that sent them,
   // into their exchange blocks over NVLink (pair index = source*cap + k -> row from[source] + k of that rank's
@@ -226,7 +227,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rows = a.part == 2 ? a.hidden : a.inter, cols = a.part == 2 ? a.inter : a.hidden;
   const int pairs_total = a.pairs_total;
-  const int row_blocks = rows / kTileM, stages = cols / kStageK;
+  const int row_blocks = a.block_count, stages = cols / kStageK;
 
   // ---- the tile list: every CTA builds the same one ----
   if (tid == 0) {
@@ -340,7 +341,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
     auto lane_base_of = [&](int index) -> const unsigned char * {
       const TileInfo t = sm.tile[index / row_blocks];
       const unsigned char *data = a.matrices[(static_cast<size_t>(a.layer) * kExperts + t.expert) * 3 + a.part].data;
-      return data + (static_cast<size_t>(kstep) * tiles_per_kstep + (index % row_blocks) * 8 + column) * L::kTileBytes + g * L::kBytes;
+      return data + (static_cast<size_t>(kstep) * tiles_per_kstep + (a.block_begin + index % row_blocks) * 8 + column) * L::kTileBytes + g * L::kBytes;
     };
     // The look-ahead runs through the same (item, stage) sequence as the loop below, kAhead own stages in front of
     // it, across item boundaries; the matrix address of the item after the cursor's is fetched one item early.
@@ -475,7 +476,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
       if (index >= items)
         break;
       const TileInfo t = sm.tile[index / row_blocks];
-      const int block = index % row_blocks, valid = t.valid, buffer = sequence & 1;
+      const int block = a.block_begin + index % row_blocks, valid = t.valid, buffer = sequence & 1;
       const Matrix &m = a.matrices[(static_cast<size_t>(a.layer) * kExperts + t.expert) * 3 + a.part];
       sm.scale[buffer][o] = HalfBitsToFloat(m.svh[block * kTileM + o]);
       int *pairs = sm.pairs[buffer];
@@ -699,19 +700,30 @@ struct ReturnSpec {
 static int LaunchPrefillGemm(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, const float *input,
                              const unsigned short *pair_rows, unsigned short *output, const unsigned short *gate,
                              const unsigned short *up, const unsigned short *table, void *transformed, int group_stride, int pairs,
-                             int *bad, cudaStream_t stream, int rate, int hidden, int inter, const ReturnSpec *ret = nullptr) {
+                             int *bad, cudaStream_t stream, int rate, int hidden, int inter, const ReturnSpec *ret = nullptr,
+                             int block_begin = 0, int block_count = 0) {
   if (pairs < 1 || pairs > kMaxPairIndex || group_stride < 1 || group_stride > kMaxPairs || !transformed)
     return PADRA_INVALID_ARGUMENT;
   if ((!ret && (!output || reinterpret_cast<uintptr_t>(output) % 16)) || reinterpret_cast<uintptr_t>(transformed) % 16)
     return PADRA_INVALID_ARGUMENT;
-  PrefillInputKernel<<<((pairs < kMaxPairs ? pairs : kMaxPairs) + 7) / 8, 256, 0, stream>>>(matrices, layer, part, groups, counts, input, gate, up, pair_rows, table,
-                                                          static_cast<__half *>(transformed), group_stride, pairs, hidden, inter, bad);
-  if (cudaGetLastError() != cudaSuccess)
-    return PADRA_INTERNAL;
+  const int all_blocks = (part == 2 ? hidden : inter) / kTileM;
+  if (block_count == 0)
+    block_begin = 0, block_count = all_blocks;
+  if (block_begin < 0 || block_count < 1 || block_begin + block_count > all_blocks)
+    return PADRA_INVALID_ARGUMENT;
+  // a launch that starts at a later block continues a call whose first launch has filled `transformed` already
+  if (block_begin == 0) {
+    PrefillInputKernel<<<((pairs < kMaxPairs ? pairs : kMaxPairs) + 7) / 8, 256, 0, stream>>>(
+        matrices, layer, part, groups, counts, input, gate, up, pair_rows, table, static_cast<__half *>(transformed), group_stride, pairs,
+        hidden, inter, bad);
+    if (cudaGetLastError() != cudaSuccess)
+      return PADRA_INTERNAL;
+  }
   PrefillArgs a{};
   a.matrices = matrices, a.layer = layer, a.part = part, a.groups = groups, a.counts = counts;
   a.transformed = static_cast<const __half *>(transformed), a.output = output, a.group_stride = group_stride;
   a.pairs_total = pairs, a.hidden = hidden, a.inter = inter, a.bad = bad;
+  a.block_begin = block_begin, a.block_count = block_count;
   if (ret) {
     if (part != 2 || ret->world < 1 || ret->world > kMaxRanks || ret->rank < 0 || ret->rank >= ret->world || ret->cap < 1 ||
         static_cast<long long>(ret->world) * ret->cap != pairs || !ret->bases)
@@ -753,11 +765,11 @@ int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const
 int LaunchPrefillRows(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, int group_stride, int rows,
                       const unsigned short *input_rows, unsigned short *output, const unsigned short *gate,
                       const unsigned short *up, const unsigned short *table, void *transformed, int *bad, cudaStream_t stream,
-                      int rate, int hidden, int inter) {
+                      int rate, int hidden, int inter, int block_begin, int block_count) {
   if (part != 2 && !input_rows)
     return PADRA_INVALID_ARGUMENT;
   return LaunchPrefillGemm(matrices, layer, part, groups, counts, nullptr, input_rows, output, gate, up, table, transformed,
-                           group_stride, rows, bad, stream, rate, hidden, inter);
+                           group_stride, rows, bad, stream, rate, hidden, inter, nullptr, block_begin, block_count);
 }
 
 // The down projection of received rows with its results stored straight into the source ranks' exchange blocks.

@@ -200,7 +200,7 @@ class KernelBackend:
                 B.check(self.lib.padra_exl3_prefill_rows_launch(
                     k.t.descriptors.data_ptr(), layer, part, B.ptr(w["groups"]), B.ptr(w["counts"]), n, n,
                     B.ptr(rows[begin:begin + n]), B.ptr(target), B.ptr(w["gate"]), B.ptr(w["up"]), B.ptr(k.table),
-                    B.ptr(w["transformed"]), B.ptr(k.bad), stream, k.t.rate, self.hidden, self.inter),
+                    B.ptr(w["transformed"]), B.ptr(k.bad), stream, k.t.rate, self.hidden, self.inter, 0, 0),
                     "padra_exl3_prefill_rows_launch")
         return down
 
@@ -225,7 +225,7 @@ class PeerExchangePrefill:
     MAX_GROUPED = 4096 * TOPK
 
     def __init__(self, kernels, owner, rank: int, world: int, cap: int, block: torch.Tensor, blocks, between_phases=None,
-                 fused_return: bool = False):
+                 fused_return: bool = False, split_return: bool = True):
         import ctypes as C
 
         from . import binding as B
@@ -235,6 +235,7 @@ class PeerExchangePrefill:
         self.device = kernels.t.device
         self.hidden, self.inter = kernels.dims
         self.block, self.between_phases, self.fused_return = block, between_phases, fused_return
+        self.split_return = split_return
         offsets = (C.c_size_t * 6)()
         total = self.lib.padra_ep_exchange_bytes(world, cap, self.hidden, offsets)
         assert total and block.numel() >= total and block.dtype == torch.uint8
@@ -296,11 +297,11 @@ class PeerExchangePrefill:
         B.check(lib.padra_ep_wait(base, 0, *geometry, self.epoch, bad, stream), "padra_ep_wait")
         B.check(lib.padra_ep_group_received(base, *geometry, B.ptr(self.groups), B.ptr(self.counts), self.MAX_GROUPED, bad, stream),
                 "padra_ep_group_received")
-        def project(part, target, transformed, on):
+        def project(part, target, transformed, on, blocks=(0, 0)):
             B.check(lib.padra_exl3_prefill_rows_launch(
                 k.t.descriptors.data_ptr(), layer, part, B.ptr(self.groups), B.ptr(self.counts), self.MAX_GROUPED, self.world * self.cap,
                 base + self.offsets[0], B.ptr(target), B.ptr(self.gate), B.ptr(self.up), B.ptr(k.table), B.ptr(transformed), bad,
-                on, k.t.rate, self.hidden, self.inter), "padra_exl3_prefill_rows_launch")
+                on, k.t.rate, self.hidden, self.inter, *blocks), "padra_exl3_prefill_rows_launch")
 
         # the up projection runs on a second stream beside the gate projection; both join before the down projection
         main, side = torch.cuda.current_stream(), k.side_stream()
@@ -311,16 +312,29 @@ class PeerExchangePrefill:
         join.record(side)
         project(0, self.gate, self.transformed, stream)
         main.wait_event(join)
-        if not self.fused_return:
-            project(2, self.down, self.transformed, stream)
         if self.fused_return:  # the down projection's epilogue stores the rows into their sources' blocks itself
             B.check(lib.padra_ep_down_return(k.t.descriptors.data_ptr(), layer, B.ptr(self.groups), B.ptr(self.counts), self.MAX_GROUPED,
                                              B.ptr(self.gate), B.ptr(self.up), B.ptr(k.table), B.ptr(self.transformed), self.bases,
                                              self.rank, self.world, self.cap, self.epoch, bad, stream, k.t.rate, self.hidden, self.inter),
                     "padra_ep_down_return")
-        else:
+        elif self.split_return and self.world > 1:
+            # the first half of the down rows' columns travels (second stream) while the second half is computed
+            half = self.hidden // 256  # 128-output blocks per half
+            sent, computed = torch.cuda.Event(), torch.cuda.Event()
+            project(2, self.down, self.transformed, stream, (0, half))
+            computed.record(main)
+            side.wait_event(computed)
             B.check(lib.padra_ep_return(B.ptr(self.down), self.bases, self.rank, self.world, self.cap, self.hidden, self.epoch, bad,
-                                        stream), "padra_ep_return")
+                                        side.cuda_stream, 0, half * 128, 0), "padra_ep_return")
+            sent.record(side)
+            project(2, self.down, self.transformed, stream, (half, self.hidden // 128 - half))
+            main.wait_event(sent)
+            B.check(lib.padra_ep_return(B.ptr(self.down), self.bases, self.rank, self.world, self.cap, self.hidden, self.epoch, bad,
+                                        stream, half * 128, self.hidden - half * 128, 1), "padra_ep_return")
+        else:
+            project(2, self.down, self.transformed, stream)
+            B.check(lib.padra_ep_return(B.ptr(self.down), self.bases, self.rank, self.world, self.cap, self.hidden, self.epoch, bad,
+                                        stream, 0, 0, 1), "padra_ep_return")
         if self.between_phases:
             self.between_phases()
         B.check(lib.padra_ep_wait(base, 1, *geometry, self.epoch, bad, stream), "padra_ep_wait")

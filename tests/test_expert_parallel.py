@@ -182,8 +182,8 @@ def test_ranks_on_one_gpu_equal_the_single_gpu_prefill(oracle, gpu, world, chunk
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("world,fused_return", [(2, True), (4, True), (2, False)])
-def test_peer_memory_exchange_on_one_gpu_equals_the_single_gpu_prefill(oracle, gpu, world, fused_return):
+@pytest.mark.parametrize("world,fused_return,split_return", [(2, True, False), (4, False, True), (2, False, True), (2, False, False)])
+def test_peer_memory_exchange_on_one_gpu_equals_the_single_gpu_prefill(oracle, gpu, world, fused_return, split_return):
     """The exchange over peer memory with the ranks as threads of one process: every rank's block is a plain allocation
     of the shared GPU, and a thread barrier between the announcing and the waiting launches keeps the stream order that
     a single GPU needs.  Three layer calls in a row reuse the blocks."""
@@ -210,7 +210,7 @@ def test_peer_memory_exchange_on_one_gpu_equals_the_single_gpu_prefill(oracle, g
             torch.cuda.set_device(gpu)
             x, ids, w = inputs[rank]
             engine = EP.PeerExchangePrefill(kernels[rank], owner, rank, world, cap, blocks[rank], [b.data_ptr() for b in blocks],
-                                            between_phases=barrier.wait, fused_return=fused_return)
+                                            between_phases=barrier.wait, fused_return=fused_return, split_return=split_return)
             got = torch.from_numpy(x.copy()).to(gpu)
             dids, dw, dx = torch.from_numpy(ids.reshape(-1)).to(gpu), torch.from_numpy(w.reshape(-1)).to(gpu), torch.from_numpy(x).to(gpu)
             for layer in range(layers):
