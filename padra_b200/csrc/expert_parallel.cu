@@ -247,7 +247,11 @@ __global__ void __launch_bounds__(256) DispatchKernel(const float *activations, 
   }
   __syncthreads();
   if (s_ok) {
-    for (int row = blockIdx.x * 8 + warp; row < pairs; row += gridDim.x * 8) {
+    // every rank starts with the rows of its right-hand neighbour and walks round the ring, so that the ranks do not
+    // all store into the same destination at the same time
+    const int start = s_first[(rank + 1) % world];
+    for (int turn = blockIdx.x * 8 + warp; turn < pairs; turn += gridDim.x * 8) {
+      const int row = turn + start < pairs ? turn + start : turn + start - pairs;
       int d = 0;
       while (d + 1 < world && s_first[d + 1] <= row)
         ++d;
@@ -414,7 +418,9 @@ __global__ void __launch_bounds__(256) ReturnKernel(const unsigned short *down, 
     s_first[world] = sum;
   }
   __syncthreads();
-  for (int item = blockIdx.x * 8 + warp; item < s_first[world]; item += gridDim.x * 8) {
+  const int total = s_first[world], start = s_first[(rank + 1) % world]; // ring order, like the dispatch
+  for (int turn = blockIdx.x * 8 + warp; turn < total; turn += gridDim.x * 8) {
+    const int item = turn + start < total ? turn + start : turn + start - total;
     int s = 0;
     while (s + 1 < world && s_first[s + 1] <= item)
       ++s;
@@ -478,7 +484,7 @@ int LaunchDispatch(const float *activations, const int *order, const int *send_i
       reinterpret_cast<uintptr_t>(activations) % 16)
     return PADRA_INVALID_ARGUMENT;
   const int blocks = (pairs + 7) / 8;
-  DispatchKernel<<<blocks < 148 * 8 ? blocks : 148 * 8, 256, 0, stream>>>(activations, order, send_ids, send_counts, peers,
+  DispatchKernel<<<blocks < 148 * 4 ? blocks : 148 * 4, 256, 0, stream>>>(activations, order, send_ids, send_counts, peers,
                                                                           MakeExchangeLayout(world, cap, hidden), rank, world, cap, pairs,
                                                                           hidden, epoch, bad);
   return CudaStatus(cudaGetLastError());
@@ -513,7 +519,7 @@ int LaunchReturn(const unsigned short *down, const unsigned long long *bases, in
       !FillPeers(peers, bases, world) || reinterpret_cast<uintptr_t>(down) % 16 || column_begin < 0 || column_count < 8 ||
       (column_begin % 8) || (column_count % 8) || column_begin + column_count > hidden)
     return PADRA_INVALID_ARGUMENT;
-  ReturnKernel<<<148 * 8, 256, 0, stream>>>(down, peers, MakeExchangeLayout(world, cap, hidden), rank, world, cap, hidden, epoch, bad,
+  ReturnKernel<<<148 * 4, 256, 0, stream>>>(down, peers, MakeExchangeLayout(world, cap, hidden), rank, world, cap, hidden, epoch, bad,
                                             column_begin, column_count, announce);
   return CudaStatus(cudaGetLastError());
 }
