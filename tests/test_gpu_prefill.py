@@ -162,3 +162,53 @@ def test_against_reference_prefill_kernels_mellum_dims(oracle, gpu, rate):
     assert_close_rows(bf16_bits_to_f32(u16(up)), bf16_bits_to_f32(u16(rup)), "up vs reference prefill")
     assert_close_rows(bf16_bits_to_f32(u16(down)), bf16_bits_to_f32(u16(rdown)), "down vs reference prefill", chained=True)
     assert_close_rows(xs.cpu().numpy(), rx.cpu().numpy(), "layer vs reference prefill", chained=True)
+
+
+@pytest.mark.parametrize("rate", [3, 4, 6])
+def test_prefill_maximum_chunk_with_empty_and_full_experts(oracle, gpu, rate):
+    """The largest chunk the entry points take (2048 tokens), routed so that eight experts receive every token (2048
+    pairs each: eight full 256-token items per output block) and fifty-six experts receive none; both prefill kernels
+    against each other on the whole layer and, for pairs of the first, a middle and the last item, against the oracle."""
+    from padra_b200.experts import bf16_values
+
+    hidden, inter, tokens = 256, 128, 2048
+    host, table, k = make(1, hidden, inter, rate, 300 + rate, gpu)
+    chosen = torch.tensor([1, 5, 12, 20, 33, 47, 58, 63], dtype=torch.int32, device=gpu)
+    ids = chosen.repeat(tokens)
+    g = torch.Generator(device=gpu)
+    g.manual_seed(9)
+    w = torch.rand((tokens, 8), device=gpu, generator=g) + 0.1
+    w = bf16_values(w / w.sum(dim=-1, keepdim=True)).reshape(-1)
+    dx = bf16_values(torch.randn((tokens, hidden), device=gpu, generator=g))
+    xa, xb = dx.clone(), dx.clone()
+    ga, ua, da = (t.clone() for t in k.prefill_layer(0, ids, w, dx, xa, tokens, tensor_memory=True))
+    k.prefill_layer(0, ids, w, dx, xb, tokens, tensor_memory=False)
+    torch.cuda.synchronize()
+    assert k.bad_flag() == 0
+    # two summation orders on a chained result, half a million elements: compared in the row 2-norm (1e-2) and element
+    # by element against max(|ref|, rms) (3e-2); the worst single element of 2048 rows sits at the 1e-2 line itself
+    a, b = xa.cpu().numpy().astype(np.float64), xb.cpu().numpy().astype(np.float64)
+    assert (np.linalg.norm(a - b, axis=1) <= 1e-2 * np.linalg.norm(b, axis=1)).all()
+    floor = np.maximum(np.abs(b), np.sqrt((b ** 2).mean(axis=1, keepdims=True)))
+    assert (np.abs(a - b) <= 3e-2 * floor).all()
+    h_x, gate = dx.cpu().numpy(), bf16_bits_to_f32(u16(ga))
+    for pair in (0, 8 * 1000 + 3, 8 * 2047 + 7):
+        e = int(chosen[pair % 8])
+        data, suh, svh = host.get(0, e, 0)
+        want, bad = oracle.linear(oracle.matrix(data, suh, svh, inter, hidden, rate), h_x[pair // 8])
+        assert not bad
+        assert_close_rows(gate[pair][None], want[None], f"gate row of pair {pair} vs oracle")
+
+
+def test_prefill_smallest_chunk(oracle, gpu):
+    """Four tokens, the fewest the prefill launchers take: 32 pairs, most experts empty, against the oracle's layer."""
+    hidden, inter, tokens = 256, 128, 4
+    host, table, k = make(1, hidden, inter, 4, 97, gpu)
+    x, ids, w = routed_inputs(oracle, tokens, hidden, 23)
+    dids, dw, dx = torch.from_numpy(ids.reshape(-1)).to(gpu), torch.from_numpy(w.reshape(-1)).to(gpu), torch.from_numpy(x).to(gpu)
+    got = dx.clone()
+    k.prefill_layer(0, dids, dw, dx, got, tokens)
+    torch.cuda.synchronize()
+    want, bad = oracle.moe_layer(host.table, 0, ids, w, x, hidden, inter)
+    assert not bad and k.bad_flag() == 0
+    assert_close_rows(got.cpu().numpy(), want, "four-token prefill layer vs oracle", chained=True)
