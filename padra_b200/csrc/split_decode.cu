@@ -269,21 +269,29 @@ __global__ void __launch_bounds__(128) GateUpEpilogueKernel(const Matrix *matric
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int pair = blockIdx.y, nb = blockIdx.x * 4 + warp;
   LetSuccessorLaunch();
+  // what does not depend on the projection kernel (ids, descriptors, sidecars: the caller's inputs, complete before
+  // the pipeline's first kernel started) is fetched before waiting for it: three dependent round trips to L2 less
+  const bool in_range = pair < pairs && nb < inter / 128;
+  const int expert = in_range ? ids[pair] : -1;
+  const bool valid = expert >= 0 && expert < kExperts;
+  const Matrix *m = matrices + (static_cast<size_t>(layer) * kExperts + (valid ? expert : 0)) * 3;
+  const int out = nb * 128 + lane * 4;
+  float svg[4], svu[4], shd[4];
+  // a descriptor that does not fit the call was rejected by the projection kernel (sticky flag, checked below); do not
+  // read through it here
+  if (valid && m[0].svh && m[1].svh && m[2].suh && m[0].rows == inter && m[1].rows == inter && m[2].cols == inter) {
+    Unpack4(__ldg(reinterpret_cast<const uint2 *>(m[0].svh + out)), svg);
+    Unpack4(__ldg(reinterpret_cast<const uint2 *>(m[1].svh + out)), svu);
+    Unpack4(__ldg(reinterpret_cast<const uint2 *>(m[2].suh + out)), shd);
+  }
   WaitForPredecessor();
-  if (*bad || pair >= pairs || nb >= inter / 128)
+  if (*bad || !in_range)
     return;
-  const int expert = ids[pair];
-  if (expert < 0 || expert >= kExperts) {
+  if (!valid) {
     if (!lane)
       Raise(bad);
     return;
   }
-  const Matrix *m = matrices + (static_cast<size_t>(layer) * kExperts + expert) * 3;
-  const int out = nb * 128 + lane * 4;
-  float svg[4], svu[4], shd[4];
-  Unpack4(__ldg(reinterpret_cast<const uint2 *>(m[0].svh + out)), svg);
-  Unpack4(__ldg(reinterpret_cast<const uint2 *>(m[1].svh + out)), svu);
-  Unpack4(__ldg(reinterpret_cast<const uint2 *>(m[2].suh + out)), shd);
   float gsum[4] = {0.f, 0.f, 0.f, 0.f}, usum[4] = {0.f, 0.f, 0.f, 0.f};
   const float *pg = partials + (static_cast<size_t>(pair) * 2 + 0) * slices * inter + out;
   const float *pu = partials + (static_cast<size_t>(pair) * 2 + 1) * slices * inter + out;
@@ -338,19 +346,23 @@ __global__ void __launch_bounds__(256) DownEpilogueKernel(const Matrix *matrices
   const int lane = threadIdx.x & 31, slot = threadIdx.x >> 5;
   const int token = blockIdx.y, nb = blockIdx.x;
   LetSuccessorLaunch();
+  // ids, descriptors and sidecars do not depend on the projection kernel: fetched before waiting for it
+  const int pair = token * kTopK + slot, out = nb * 128 + lane * 4;
+  const int expert = token < tokens ? ids[pair] : -1;
+  const bool valid = expert >= 0 && expert < kExperts;
+  float sc[4] = {0.f, 0.f, 0.f, 0.f};
+  if (valid) { // a descriptor that does not fit was rejected by the projection kernel: do not read through it here
+    const Matrix &m = matrices[(static_cast<size_t>(layer) * kExperts + expert) * 3 + 2];
+    if (m.svh && m.rows == hidden)
+      Unpack4(__ldg(reinterpret_cast<const uint2 *>(m.svh + out)), sc);
+  }
   WaitForPredecessor();
   if (*bad || token >= tokens)
     return;
-  const int pair = token * kTopK + slot, out = nb * 128 + lane * 4;
-  const int expert = ids[pair];
-  const bool valid = expert >= 0 && expert < kExperts;
   if (!valid && !lane)
     Raise(bad);
   float d[4] = {0.f, 0.f, 0.f, 0.f};
   if (valid) {
-    const Matrix *m = matrices + (static_cast<size_t>(layer) * kExperts + expert) * 3 + 2;
-    float sc[4];
-    Unpack4(__ldg(reinterpret_cast<const uint2 *>(m->svh + out)), sc);
     const float *pd = partials + static_cast<size_t>(pair) * slices * hidden + out;
     float4 vd[kMaxSlices];
 #pragma unroll
