@@ -1,4 +1,4 @@
-"""Benchmark of the EXL3 MoE expert layer at decode (BASELINE configs[1]).
+"""Benchmark of the EXL3 MoE expert layer: decode (the headline), a prefill chunk, expert-parallel prefill.
 
 Workload: one K4 MoE layer, hidden 2048, expert-intermediate 1024, 64 experts, top-8, ONE token per step.
 A step is one pass of the whole expert layer (gate/up projections, SwiGLU, down projection, combine with
@@ -15,6 +15,10 @@ memory and its result read back, copies and synchronisation inside the timed reg
 
 With N > 1 (torchrun, one rank per GPU) every rank runs an independent replica of the decode workload (the
 decode path does not shard); the value is the sum over ranks, timed as the maximum over ranks.
+
+Two more objects ride on the same JSON line: `prefill_chunk` (N = 1: a 2048-token chunk, Zipf(1.1) routing, through
+the tcgen05 grouped GEMM, with its tensor roofline) and `expert_parallel_prefill` (a 16384-token batch through all
+layers with the experts sharded 64/N per GPU and the rows exchanged over NVLink peer memory; strong scaling).
 `--impl reference` times the CPU restatement of the reference arithmetic (the reference has no CPU
 implementation and no B200 build of this path) on the host cores, same metric and workload.
 """
