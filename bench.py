@@ -232,8 +232,22 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
         backend, group_exchange = EP.KernelBackend(k), EP.GroupExchange()
         engines = [EP.ExpertParallelPrefill(backend, group_exchange, owners[layer]) for layer in range(layers)]
     elif world > 1:
-        peer = EP.PeerExchangePrefill.over_group(k, owners[0], cap=chunk * TOPK)
-        device_owners = [torch.from_numpy(o.astype(np.int32)).to(dev) for o in owners]
+        # symmetric memory may be unavailable on a host (no peer access, no handle exchange): every rank then takes the
+        # NCCL exchange, and the JSON line says which exchange ran
+        try:
+            peer = EP.PeerExchangePrefill.over_group(k, owners[0], cap=chunk * TOPK)
+            failed = 0
+        except Exception as error:  # noqa: BLE001 - any failure of the rendezvous means "not available here"
+            print(f"rank {rank}: peer exchange unavailable ({type(error).__name__}: {error}); using NCCL all-to-all", file=sys.stderr)
+            peer, failed = None, 1
+        vote = torch.tensor([failed], device=dev)
+        dist.all_reduce(vote, op=dist.ReduceOp.MAX)
+        if int(vote.item()):
+            peer, exchange = None, "nccl"
+            backend, group_exchange = EP.KernelBackend(k), EP.GroupExchange()
+            engines = [EP.ExpertParallelPrefill(backend, group_exchange, owners[layer]) for layer in range(layers)]
+        else:
+            device_owners = [torch.from_numpy(o.astype(np.int32)).to(dev) for o in owners]
 
     def normalise(rows):  # stand-in for the model's RMSNorm between layers (outside the measured path's scope)
         return torch.nn.functional.rms_norm(rows, (HIDDEN,), eps=1e-6).to(torch.bfloat16).float()
