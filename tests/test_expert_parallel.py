@@ -253,3 +253,23 @@ def test_plan_kernel_equals_the_host_plan(gpu, world, tokens):
     torch.cuda.synchronize()
     assert torch.equal(got.order, want.order) and torch.equal(got.position, want.position)
     assert torch.equal(got.send_ids, want.send_ids) and got.send_counts.tolist() == want.send_counts.tolist()
+
+
+def test_exchange_block_layout_is_consistent():
+    """Host-only: the byte layout of an exchange block (no GPU needed, the function only computes sizes)."""
+    import ctypes as C
+
+    from padra_b200 import binding as B
+
+    lib = B.load()
+    offsets = (C.c_size_t * 6)()
+    world, cap, hidden = 8, 16384, 2048
+    total = lib.padra_ep_exchange_bytes(world, cap, hidden, offsets)
+    rows, ids, meta, returned, arrived, came_back = list(offsets)
+    assert rows == 0 and ids == world * cap * hidden * 2                      # received rows first, BF16
+    assert meta - ids >= world * cap * 4 and returned - meta >= world * 16   # ids, then one 16-byte record per source
+    assert arrived - returned >= cap * hidden * 2 and came_back - arrived >= world * 4
+    assert total > came_back and all(o % 256 == 0 for o in offsets) and total % 256 == 0
+    assert lib.padra_ep_exchange_bytes(9, cap, hidden, None) == 0             # at most eight ranks
+    assert lib.padra_ep_exchange_bytes(world, cap, 100, None) == 0            # hidden must be a multiple of 128
+    assert lib.padra_ep_exchange_bytes(world, 4, hidden, None) == 0           # at least one token's pairs
