@@ -1,27 +1,27 @@
 // Prefill: the grouped per-expert projection on the 5th-generation tensor cores (tcgen05.mma, accumulators in
 // tensor memory), with the trellis decode fused into the producer side of the pipeline.
 //
-// A work item is a 128-output x N-token tile (N <= 256) of one expert:  D[n][o] = sum_k x~[n][k] * W[k][o].
-// The kernel is persistent: one CTA per SM walks a list of items (token tiles sorted by size, dealt out in snake
-// order so that every CTA gets a similar load; the row blocks of one token tile run at the same time on
-// neighbouring CTAs and share the tile's activation rows through L2).
-//   * the weights are the MMA's N side.  Two sets of eight producer warps (one warp per 16-output tile column; the
-//     sets take alternate 64-input stages, which gives every warp two stage times to hide its load and decode
-//     latencies) read packed words several stages ahead, decode 32 weights per lane in registers (codec.cuh) and
-//     store them as 16-byte rows of 8x8 FP16 core matrices into the canonical K-major, no-swizzle shared-memory
-//     layout: with the lane <-> (row pair, K-step) ownership of the codec the four 16-byte stores of a quarter-warp
-//     are 128 contiguous bytes.
+// A work item is a tile of up to 128 tokens x 256 outputs (two 128-output blocks) of one expert:
+// D[n][o] = sum_k x~[n][k] * W[k][o].  The kernel is persistent: one CTA per SM walks a list of items (token tiles
+// sorted by size, dealt out in snake order so that every CTA gets a similar load; the items of one token tile run at the
+// same time on neighbouring CTAs and share the tile's activation rows through L2).  The shape is chosen for the two
+// things that bound the kernel: an SM pulls 16 KB of activations per 64-input stage for 256 output columns (half the L2
+// traffic per MAC of a 256-token x 128-output item), and every producer warp sees all four ring slots.
+//   * the weights are the MMA's N side.  Two sets of eight producer warps, one set per output block of the item and one
+//     warp per 16-output tile column, read packed words several stages ahead, decode 32 weights per lane in registers
+//     (codec.cuh) and store them as 16-byte rows of 8x8 FP16 core matrices into the canonical K-major, no-swizzle
+//     shared-memory layout: with the lane <-> (row pair, K-step) ownership of the codec the four 16-byte stores of a
+//     quarter-warp are 128 contiguous bytes.
 //   * the tokens are the M side: the expert's transformed activation rows (FP16, written in expert-grouped order by
-//     PrefillInputKernel), copied with cp.async into the same canonical layout, one or two tiles of 128 rows.
-//   * one elected thread issues tcgen05.mma (M = 128 tokens, N = 128 outputs, K = 16), four per stage and token
-//     tile, and commits each stage back to the producers; a 4-stage ring of (16 KB weights + up to 32 KB
-//     activations) that runs on across items.
-//   * a thread of the four epilogue warps owns one TOKEN row of the accumulator, so the 128-point output Hadamard
-//     runs over the columns it reads from tensor memory: stages d = 1..16 in registers on 32-column pieces (written
-//     back in place), stages d = 32, 64 between the four pieces, then svh, BF16 rounding and 16-byte stores to the
-//     row of the (token, slot) pair.  No shuffles, no barriers.
-//   * the 512 tensor-memory columns hold TWO accumulators of two token tiles each: the epilogue drains item i while
-//     the producers and the MMA thread already work on item i+1.
+//     PrefillInputKernel), copied with cp.async into the same canonical layout, one tile of up to 128 rows.
+//   * one elected thread issues tcgen05.mma (M = 128 tokens, N = 256 outputs, K = 16), four per stage, and commits each
+//     stage back to the producers; a 4-stage ring of (32 KB weights + 16 KB activations) that runs on across items.
+//   * a thread of the four epilogue warps owns one TOKEN row of the accumulator, so the 128-point output Hadamard of
+//     each output block runs over the columns it reads from tensor memory: stages d = 1..16 in registers on 32-column
+//     pieces (written back in place), stages d = 32, 64 between the four pieces, then svh, BF16 rounding and 16-byte
+//     stores to the row of the (token, slot) pair.  No shuffles, no barriers.
+//   * the 512 tensor-memory columns hold TWO accumulators of 256 columns: the epilogue drains item i while the
+//     producers and the MMA thread already work on item i+1.
 // Every wait on an mbarrier is bounded in time: on expiry the CTA raises the sticky error flag, skips the rest of
 // its work, frees its tensor memory and leaves.
 #include "codec.cuh"
@@ -35,17 +35,19 @@ namespace {
 constexpr int kStages = 4;
 constexpr int kStageK = 64;    // inputs per pipeline stage (four K16 steps)
 constexpr int kTileM = 128;    // outputs per item (the MMA's N), and token rows per MMA (its M)
-constexpr int kMaxTileN = 256; // tokens per item
-constexpr int kStageABytes = kTileM * kStageK * 2; // 16 KB
+constexpr int kMaxTileN = 128; // tokens per item (one MMA token tile)
+constexpr int kItemBlocks = 2; // 128-output blocks per item: 256 accumulator columns
+constexpr int kStageABytes = kItemBlocks * kTileM * kStageK * 2; // 32 KB of decoded weights
 // B stage: eight 16-byte K pieces per row; consecutive pieces are (tile_n*16 + 16) bytes apart -- the extra 16 bytes
 // put the eight pieces of one row on eight different bank groups, so the coalesced copy (eight lanes per row) is
 // free of bank conflicts.
 constexpr int kStageBBytes = 8 * (kMaxTileN * 16 + 16) + 896; // 32 KB + padding, kept a multiple of 1 KB
-constexpr int kEpilogueWarps = 4, kProducerSets = 2, kWarpsPerSet = 8;
+constexpr int kEpilogueWarps = 4, kProducerSets = 2, kWarpsPerSet = 8; // set b decodes output block b of the item
 constexpr int kMmaWarp = kEpilogueWarps;
 constexpr int kFirstProducerWarp = kMmaWarp + 1;
 constexpr int kPrefillThreads = (kEpilogueWarps + 1 + kProducerSets * kWarpsPerSet) * 32; // 672
-constexpr int kTmemColumns = 512;                   // two accumulators of 256 columns
+constexpr int kTmemColumns = 512;                   // two accumulators of 256 columns (128 tokens x 256 outputs)
+constexpr int kBufferColumns = 256;
 constexpr int kMaxPairs = 4096 * kTopK;              // grouped pairs (rows) one call works on
 constexpr int kMaxPairIndex = 1 << 20;              // pair indices may be sparse (received rows in per-source regions)
 constexpr int kMaxTiles = kExperts + kMaxPairs / kMaxTileN; // sum over experts of ceil(n_e / 256)
@@ -60,7 +62,7 @@ struct TileInfo {
 struct PrefillSmem {
   alignas(128) unsigned char a[kStages][kStageABytes];
   alignas(128) unsigned char b[kStages][kStageBBytes];
-  alignas(16) float scale[2][kTileM]; // svh of the item being drained / the next one
+  alignas(16) float scale[2][kItemBlocks * kTileM]; // svh of the item being drained / the next one
   alignas(8) unsigned long long full[kStages], empty[kStages], accumulator_ready[2], accumulator_free[2];
   TileInfo tile[kMaxTiles], unsorted[kMaxTiles];
   int pairs[2][kMaxTileN]; // (token*8+slot) of the rows of the item being drained / the next one
@@ -135,9 +137,9 @@ __device__ __forceinline__ unsigned long long OperandDescriptor(unsigned smem_ad
   return static_cast<unsigned long long>((smem_address & 0x3ffffu) >> 4) | (static_cast<unsigned long long>(leading_bytes >> 4) << 16) |
          (static_cast<unsigned long long>(stride_bytes >> 4) << 32) | (1ull << 46);
 }
-__device__ __forceinline__ unsigned InstructionDescriptor() {
+__device__ __forceinline__ unsigned InstructionDescriptor(int n) {
   // kind::f16: FP32 accumulate (bits 4-5 = 1), A and B FP16 (0), both K-major (0), N>>3 at [17,23), M>>4 at [24,29)
-  return (1u << 4) | (static_cast<unsigned>(kTileM >> 3) << 17) | (static_cast<unsigned>(128 >> 4) << 24);
+  return (1u << 4) | (static_cast<unsigned>(n >> 3) << 17) | (static_cast<unsigned>(128 >> 4) << 24);
 }
 __device__ __forceinline__ void MmaSS(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc, unsigned idesc, bool accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
@@ -227,7 +229,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rows = a.part == 2 ? a.hidden : a.inter, cols = a.part == 2 ? a.inter : a.hidden;
   const int pairs_total = a.pairs_total;
-  const int row_blocks = a.block_count, stages = cols / kStageK;
+  const int row_blocks = (a.block_count + kItemBlocks - 1) / kItemBlocks; // items per token tile: pairs of output blocks
+  const int stages = cols / kStageK;
 
   // ---- the tile list: every CTA builds the same one ----
   if (tid == 0) {
@@ -302,7 +305,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
   }
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
-      BarrierInit(&sm.full[s], kWarpsPerSet * 32 + kWarpsPerSet); // every producer thread's copies + one arrival per warp
+      BarrierInit(&sm.full[s], kProducerSets * kWarpsPerSet * 33); // every producer thread's copies + one arrival per warp
       BarrierInit(&sm.empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -330,28 +333,31 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
 
   if (warp >= kFirstProducerWarp) {
     // =============================== producers ===============================
-    const int set = (warp - kFirstProducerWarp) / kWarpsPerSet;   // takes the stages i with (i & 1) == set
+    const int set = (warp - kFirstProducerWarp) / kWarpsPerSet;   // output block of the item this warp decodes
     const int column = (warp - kFirstProducerWarp) % kWarpsPerSet; // 16-output tile column inside the 128-output block
-    const int ptid = tid - (kFirstProducerWarp + set * kWarpsPerSet) * 32; // 0..255 inside the set
+    const int ptid = tid - kFirstProducerWarp * 32; // 0..511
     const int g = lane & 7, kstep = lane >> 3; // row pair, K16 step inside the stage
     const size_t tiles_per_kstep = rows / 16;
     const size_t stage_bytes = static_cast<size_t>(4) * tiles_per_kstep * L::kTileBytes;
-    const int piece = ptid & 7; // this thread copies K piece `piece` of rows (ptid >> 3) + 32*j
+    const int piece = ptid & 7; // this thread copies K piece `piece` of rows (ptid >> 3) + 64*j
     // address of this lane's packed words for stage 0 of an item
     auto lane_base_of = [&](int index) -> const unsigned char * {
       const TileInfo t = sm.tile[index / row_blocks];
       const unsigned char *data = a.matrices[(static_cast<size_t>(a.layer) * kExperts + t.expert) * 3 + a.part].data;
-      return data + (static_cast<size_t>(kstep) * tiles_per_kstep + (a.block_begin + index % row_blocks) * 8 + column) * L::kTileBytes + g * L::kBytes;
+      int block = a.block_begin + (index % row_blocks) * kItemBlocks + set;
+      if (block >= a.block_begin + a.block_count)
+        block = a.block_begin + a.block_count - 1; // odd block count: the last item has one block, this set idles there
+      return data + (static_cast<size_t>(kstep) * tiles_per_kstep + block * 8 + column) * L::kTileBytes + g * L::kBytes;
     };
     // The look-ahead runs through the same (item, stage) sequence as the loop below, kAhead own stages in front of
     // it, across item boundaries; the matrix address of the item after the cursor's is fetched one item early.
-    int ahead_sequence = 0, ahead_stage = set;
+    int ahead_sequence = 0, ahead_stage = 0;
     const unsigned char *ahead_base = lane_base_of(ItemIndex(0));
     const unsigned char *ahead_next = ItemIndex(1) < items ? lane_base_of(ItemIndex(1)) : nullptr;
     auto fetch = [&](uint32_t(&into)[Rate]) {
       if (ahead_base)
         codec::LoadWords<Rate>(ahead_base + static_cast<size_t>(ahead_stage) * stage_bytes, into);
-      ahead_stage += 2;
+      ahead_stage += 1;
       if (ahead_stage >= stages) {
         ahead_stage -= stages;
         ++ahead_sequence;
@@ -373,14 +379,15 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
       const TileInfo t = sm.tile[index / row_blocks];
       const int valid = t.valid, tile_n = (valid + 15) & ~15;
       const __half *b_rows = a.transformed + static_cast<size_t>(t.row_base) * cols;
-      int b_source[kMaxTileN / 32];
+      const bool decodes = (index % row_blocks) * kItemBlocks + set < a.block_count; // false: single-block last item
+      int b_source[kMaxTileN / 64];
 #pragma unroll
-      for (int j = 0; j < kMaxTileN / 32; ++j) {
-        const int n = (ptid >> 3) + 32 * j;
+      for (int j = 0; j < kMaxTileN / 64; ++j) {
+        const int n = (ptid >> 3) + 64 * j;
         b_source[j] = (n < valid ? n : valid - 1) * cols + piece * 8;
       }
       const int b_piece_bytes = tile_n * 16 + 16;
-      for (int i = set; i < stages; i += 2) {
+      for (int i = 0; i < stages; ++i) {
         const int s = (q + i) % kStages;
         uint32_t words[Rate];
 #pragma unroll
@@ -402,18 +409,20 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
         const unsigned b_target = SmemAddress(sm.b[s]) + piece * b_piece_bytes + (ptid >> 3) * 16;
         const __half *b_stage_rows = b_rows + i * kStageK;
 #pragma unroll
-        for (int j = 0; j < kMaxTileN / 32; ++j)
-          if ((ptid >> 3) + 32 * j < tile_n
-          )
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_target + j * 512), "l"(b_stage_rows + b_source[j]) : "memory");
+        for (int j = 0; j < kMaxTileN / 64; ++j)
+          if ((ptid >> 3) + 64 * j < tile_n)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_target + j * 1024), "l"(b_stage_rows + b_source[j]) : "memory");
         // the stage's barrier counts this thread's copies as one arrival of their own, once they have landed
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(SmemAddress(&sm.full[s])) : "memory");
         // weights: this lane's four 16-byte core-matrix rows (fragment f: K half f>>1, output group f&1)
+        // (K piece 2*kstep + f>>1 holds 256 rows = 4096 bytes; output block `set` starts 2048 bytes into it)
         unsigned char *a_stage = sm.a[s];
+        if (decodes) {
 #pragma unroll
-        for (int f = 0; f < 4; ++f) {
-          const uint4 row = make_uint4(frag[0][f], frag[1][f], frag[2][f], frag[3][f]);
-          *reinterpret_cast<uint4 *>(a_stage + (2 * kstep + (f >> 1)) * 2048 + (2 * column + (f & 1)) * 128 + g * 16) = row;
+          for (int f = 0; f < 4; ++f) {
+            const uint4 row = make_uint4(frag[0][f], frag[1][f], frag[2][f], frag[3][f]);
+            *reinterpret_cast<uint4 *>(a_stage + (2 * kstep + (f >> 1)) * 4096 + set * 2048 + (2 * column + (f & 1)) * 128 + g * 16) = row;
+          }
         }
         // publish at once (release); the MMA thread orders these generic-proxy writes before its tensor-core reads
         // with a proxy fence after its wait, so nobody waits here for the copies
@@ -433,8 +442,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
         if (index >= items)
           break;
         const int valid = sm.tile[index / row_blocks].valid, tile_n = (valid + 15) & ~15;
-        const int token_tiles = (valid + 127) / 128;
-        const unsigned idesc = InstructionDescriptor();
+        const int left = a.block_count - (index % row_blocks) * kItemBlocks;
+        const unsigned idesc = InstructionDescriptor((left < kItemBlocks ? left : kItemBlocks) * kTileM);
         const unsigned piece_bytes = tile_n * 16 + 16;
         const int buffer = sequence & 1;
         // the accumulator must have been drained by the epilogue of the item two before
@@ -448,15 +457,13 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // producers' stores and copies -> tensor-core reads
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const unsigned w_base = SmemAddress(sm.a[s]), x_base = SmemAddress(sm.b[s]);
-          // rows of the last token tile past tile_n hold whatever the ring held before: they only reach accumulator
-          // rows that nobody reads
-          for (int mt = 0; mt < token_tiles; ++mt)
+          // token rows past tile_n hold whatever the ring held before: they only reach accumulator rows nobody reads
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              const unsigned long long x_desc = OperandDescriptor(x_base + ks * 2 * piece_bytes + mt * 2048, piece_bytes, 128);
-              const unsigned long long w_desc = OperandDescriptor(w_base + ks * 4096, 2048, 128);
-              MmaSS(tmem + buffer * kMaxTileN + mt * kTileM, x_desc, w_desc, idesc, i > 0 || ks > 0);
-            }
+          for (int ks = 0; ks < 4; ++ks) {
+            const unsigned long long x_desc = OperandDescriptor(x_base + ks * 2 * piece_bytes, piece_bytes, 128);
+            const unsigned long long w_desc = OperandDescriptor(w_base + ks * 8192, 4096, 128);
+            MmaSS(tmem + buffer * kBufferColumns, x_desc, w_desc, idesc, i > 0 || ks > 0);
+          }
           MmaCommit(&sm.empty[s]); // arrives when the MMAs above have finished reading the stage
         }
         if (alive)
@@ -476,9 +483,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
       if (index >= items)
         break;
       const TileInfo t = sm.tile[index / row_blocks];
-      const int block = a.block_begin + index % row_blocks, valid = t.valid, buffer = sequence & 1;
+      const int first_block = a.block_begin + (index % row_blocks) * kItemBlocks, valid = t.valid, buffer = sequence & 1;
+      const int left = a.block_begin + a.block_count - first_block, item_blocks = left < kItemBlocks ? left : kItemBlocks;
       const Matrix &m = a.matrices[(static_cast<size_t>(a.layer) * kExperts + t.expert) * 3 + a.part];
-      sm.scale[buffer][o] = HalfBitsToFloat(m.svh[block * kTileM + o]);
+      for (int b = 0; b < item_blocks; ++b)
+        sm.scale[buffer][b * kTileM + o] = HalfBitsToFloat(m.svh[(first_block + b) * kTileM + o]);
       int *pairs = sm.pairs[buffer];
       for (int n = o; n < valid; n += kEpilogueWarps * 32) {
         const int pair = a.groups[static_cast<size_t>(t.expert) * a.group_stride + t.begin + n];
@@ -502,10 +511,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
       if (any_failed)
         break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float *scale = sm.scale[buffer];
-      for (int mt = 0; mt * 128 + warp * 32 < valid; ++mt) { // warp-uniform: token tiles that hold rows of this warp
-        const int n = mt * 128 + o;
-        const unsigned lane_address = tmem + buffer * kMaxTileN + mt * kTileM + (static_cast<unsigned>(warp * 32) << 16);
+      // one token row per thread; the item's output blocks are separate 128-point transforms of that row
+      for (int b = 0; b < item_blocks && warp * 32 < valid; ++b) { // warp-uniform
+        const int n = o, block = first_block + b;
+        const float *scale = sm.scale[buffer] + b * kTileM;
+        const unsigned lane_address = tmem + buffer * kBufferColumns + b * kTileM + (static_cast<unsigned>(warp * 32) << 16);
         // output Hadamard over the 128 outputs of the row, stages in ascending order like the reference
         // (src/cuda/expert_exl3.cuh:102-109).  Stages d = 1..16 stay inside a 32-column piece:
 #pragma unroll 1
