@@ -1,5 +1,5 @@
 """configs[2]: rate and batch sweep of the decode layer call (K3, K4, K6 at M = 1, 2, 5, 16 tokens; M = 5 is an MTP D4
-verify pass).  Run as `python -m tests.decode_sweep_timing` from the repository root; prints one JSON object with the
+verify pass), and the prefill chunk at the three rates.  Run as `python -m tests.decode_sweep_timing` from the repository root; prints one JSON object with the
 device time per layer step (CUDA graph of 28 steps over 28 layers of distinct weights, CUDA events) and the algorithmic
 bytes per second.  Not collected by pytest (no test functions); parity of the same calls is in tests/test_gpu_decode.py."""
 import json
@@ -54,6 +54,28 @@ def main():
             out["results"].append({"rate": rate, "tokens": tokens, "us_per_layer_step": us, "distinct_experts": distinct,
                                    "algorithmic_gb_per_s": nbytes / us / 1e3})
             assert k.bad_flag() == 0
+        # the same weights through the prefill entry points: one 2048-token chunk per layer, Zipf(1.1) routing
+        from padra_b200.experts import zipf_routing
+
+        tokens = 2048
+        chunks = []
+        for layer in range(layers):
+            ids, w = zipf_routing(tokens, seed=layer, device=gpu)
+            chunks.append((layer, ids.reshape(-1), w.reshape(-1), bf16_values(torch.randn((tokens, hidden), device=gpu, generator=g)),
+                           bf16_values(torch.randn((tokens, hidden), device=gpu, generator=g))))
+        for c in chunks[:3]:
+            k.prefill_layer(*c, tokens)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for c in chunks:
+            k.prefill_layer(*c, tokens)
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) / layers * 1e3
+        out.setdefault("prefill_2048_tokens", []).append({"rate": rate, "us_per_layer_chunk": us,
+                                                          "tflops": tokens * 8 * 3 * 2 * hidden * inter / us / 1e6})
+        assert k.bad_flag() == 0
         del k, table
     print(json.dumps(out))
 
