@@ -212,3 +212,39 @@ def test_prefill_smallest_chunk(oracle, gpu):
     want, bad = oracle.moe_layer(host.table, 0, ids, w, x, hidden, inter)
     assert not bad and k.bad_flag() == 0
     assert_close_rows(got.cpu().numpy(), want, "four-token prefill layer vs oracle", chained=True)
+
+
+@pytest.mark.parametrize("hidden,inter,tokens,rate", [
+    (128, 128, 5, 4),      # one output block per part, two 64-input stages: fewer stages than the look-ahead
+    (384, 256, 129, 3),    # three blocks in the down part (odd: the last item has a single block)
+    (256, 384, 300, 6),    # three blocks in gate/up, experts with one and with several token tiles
+    (640, 128, 1111, 4),   # five blocks, long K for gate/up and two stages for down
+])
+def test_tensor_memory_gemm_odd_shapes(oracle, gpu, hidden, inter, tokens, rate):
+    """Shapes that exercise the item list's corners: odd numbers of output blocks, very short K, token tiles of every
+    filling.  The tensor-memory GEMM against the small-tile kernel (an independent implementation) on gate, up and the
+    whole layer, and against the oracle for a few pairs."""
+    from padra_b200.experts import bf16_values, zipf_routing
+
+    host, table, k = make(1, hidden, inter, rate, 500 + hidden + tokens, gpu)
+    ids, w = zipf_routing(tokens, seed=tokens, device=gpu)
+    g = torch.Generator(device=gpu)
+    g.manual_seed(tokens)
+    dx = bf16_values(torch.randn((tokens, hidden), device=gpu, generator=g))
+    xa, xb = dx.clone(), dx.clone()
+    ga, ua, da = (t.clone() for t in k.prefill_layer(0, ids.reshape(-1), w.reshape(-1), dx, xa, tokens, tensor_memory=True))
+    gb, ub, db = k.prefill_layer(0, ids.reshape(-1), w.reshape(-1), dx, xb, tokens, tensor_memory=False)
+    torch.cuda.synchronize()
+    assert k.bad_flag() == 0
+    assert_close_rows(bf16_bits_to_f32(u16(ga)), bf16_bits_to_f32(u16(gb)), "gate: tensor-memory vs small-tile kernel")
+    assert_close_rows(bf16_bits_to_f32(u16(ua)), bf16_bits_to_f32(u16(ub)), "up: tensor-memory vs small-tile kernel")
+    a, b = xa.cpu().numpy().astype(np.float64), xb.cpu().numpy().astype(np.float64)
+    assert (np.linalg.norm(a - b, axis=1) <= 1e-2 * np.linalg.norm(b, axis=1)).all()
+    floor = np.maximum(np.abs(b), np.sqrt((b ** 2).mean(axis=1, keepdims=True)))
+    assert (np.abs(a - b) <= 3e-2 * floor).all()
+    h_ids, h_x, gate = ids.cpu().numpy().reshape(-1), dx.cpu().numpy(), bf16_bits_to_f32(u16(ga))
+    for pair in (0, tokens * 4 + 1, tokens * 8 - 1):
+        data, suh, svh = host.get(0, int(h_ids[pair]), 0)
+        want, bad = oracle.linear(oracle.matrix(data, suh, svh, inter, hidden, rate), h_x[pair // 8])
+        assert not bad
+        assert_close_rows(gate[pair][None], want[None], f"gate row of pair {pair} vs oracle")
