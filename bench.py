@@ -324,7 +324,7 @@ def run_ours(args):
         for s in slots[:2]:
             layer_call(s, stream)
     stream.synchronize()
-    kernels_per_step = 4  # split-K gate+up projection, its epilogue, split-K down projection, its epilogue
+    kernels_per_step = 2  # split-K gate+up projection and split-K down projection, each with its epilogue inside
     for s in slots:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(stream):
@@ -372,18 +372,6 @@ def run_ours(args):
             ev_b.record(stream)
         ev_b.synchronize()
         kernel_ms = [ev_a.elapsed_time(ev_b) / (kernel_reps * layers)]
-        # for comparison: the persistent single-kernel form of the layer call
-        persistent_graphs = []
-        for s in slots[:min(len(slots), 28)]:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.stream(stream):
-                k.moe_decode_layer_persistent(s["layer"], s["ids"], s["w"], s["normalized"], s["x"], TOKENS, stream=stream)
-                stream.synchronize()
-                with torch.cuda.graph(graph, stream=stream):
-                    k.moe_decode_layer_persistent(s["layer"], s["ids"], s["w"], s["normalized"], s["x"], TOKENS, stream=stream)
-            persistent_graphs.append(graph)
-        persistent_steps = min(args.steps, 280)  # (TOKENS == 1: the persistent form takes single-token steps only)
-        persistent_seconds = timed(persistent_steps, lambda i: persistent_graphs[i % len(persistent_graphs)].replay())
         # for comparison: the same layer as the reference's call sequence of separate launches (per-part entry points)
         unfused_graphs = []
         for s in slots[:min(len(slots), 28)]:
@@ -462,11 +450,9 @@ def run_ours(args):
                    "l2": f"inputs larger than L2: {layers} layers x 203 MB of expert weights rotate, 126 MB L2",
                    "bytes_per_step": bytes_per_step, "multi_gpu": "independent replicas (decode does not shard)"},
         "frac_of_hbm_peak": value / world / peak,
-        "roofline": {"bound": "hbm", "kernel": "SplitProjectionKernel<4,1>, gate+up launch (dominant kernel of the step)",
+        "roofline": {"bound": "hbm", "kernel": "LayerProjectionKernel<4,1,0>, gate+up launch (dominant kernel of the step)",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_source,
                      "bytes_per_launch": kernel_bytes, "us_per_launch": kernel_s * 1e6, "traffic": TRAFFIC_PER_LAUNCH},
-        "persistent_kernel_form": {"value": bytes_per_step * persistent_steps / persistent_seconds / 1e9, "unit": "GB/s",
-                                   "ms_per_step": persistent_seconds / persistent_steps * 1e3, "kernels_per_step": 1},
         "unfused_call_sequence": {"value": bytes_per_step * unfused_steps / unfused_seconds / 1e9, "unit": "GB/s",
                                   "ms_per_step": unfused_seconds / unfused_steps * 1e3, "kernels_per_step": 4},
         "e2e": {"value": total_bytes / e2e_seconds / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -216,38 +216,26 @@ PADRA_API int padra_exl3_expert_launch(const padra_matrix *matrices, int layer, 
  * x [tokens][hidden] the residual stream updated in place.  workspace must hold
  * padra_exl3_moe_decode_workspace_bytes() bytes; one workspace serves one stream at a time.
  *
- * padra_exl3_moe_decode_layer enqueues four launches (split-K projection of gate+up, their epilogue with
- * SwiGLU and the down input transform, split-K projection of down, its epilogue with combine); its workspace
- * needs no initialisation.
- * padra_exl3_moe_decode_layer_persistent does the same work in ONE persistent cooperative kernel (one CTA per
- * SM, needs the device otherwise idle on that stream's turn); tokens must be 1 (PADRA_UNSUPPORTED otherwise).  The leading control words of its workspace must
- * be zero before the first call (padra_exl3_moe_decode_workspace_init, once after allocation); every call
- * leaves them zero again. */
+ * padra_exl3_moe_decode_layer enqueues two launches: the split-K projection of gate+up, whose CTA that delivers the
+ * last K-slice of an (expert, 128-output block) runs the block's epilogue (SwiGLU and the down input transform), and the
+ * split-K projection of down with the combine done the same way.  The ticket counters at the start of the workspace must
+ * be zero before the first call on it: call padra_exl3_moe_decode_workspace_init once after allocating it (it zero-fills
+ * the workspace; stream-ordered, not graph-captured work of every step).  Every call leaves the counters zero again, also
+ * when it raised *bad. */
 PADRA_API size_t padra_exl3_moe_decode_workspace_bytes(int tokens, int hidden, int inter);
 PADRA_API int padra_exl3_moe_decode_workspace_init(void *workspace, size_t workspace_bytes, padra_stream stream);
 PADRA_API int padra_exl3_moe_decode_layer(const padra_matrix *matrices, int layer, const int *ids,
                                           const float *routing, const float *normalized, float *x, int tokens,
                                           int rate, int hidden, int inter, const unsigned short *table,
                                           void *workspace, size_t workspace_bytes, int *bad, padra_stream stream);
-/* Diagnostic: the same pipeline with only the selected launches enqueued (bit 0 gate+up projection, 1 its
- * epilogue, 2 down projection, 3 its epilogue), so that one kernel can be timed or profiled alone on buffers a
- * complete call has filled before. */
+/* Diagnostic: the same pipeline with only the selected launches enqueued (bit 0 the gate+up kernel, bit 1 the down
+ * kernel), so that one kernel can be timed or profiled alone on buffers a complete call has filled before. */
 PADRA_API int padra_exl3_moe_decode_layer_launches(const padra_matrix *matrices, int layer, const int *ids,
                                                    const float *routing, const float *normalized, float *x,
                                                    int tokens, int rate, int hidden, int inter,
                                                    const unsigned short *table, void *workspace,
                                                    size_t workspace_bytes, int *bad, padra_stream stream,
                                                    unsigned launches);
-PADRA_API int padra_exl3_moe_decode_layer_persistent(const padra_matrix *matrices, int layer, const int *ids,
-                                                     const float *routing, const float *normalized, float *x,
-                                                     int tokens, int rate, int hidden, int inter,
-                                                     const unsigned short *table, void *workspace,
-                                                     size_t workspace_bytes, int *bad, padra_stream stream);
-/* Diagnostic timeline of the layer kernel, off by default (the reference's counterpart is its capture_trace
- * option, src/cuda/inference.cu:608-624).  buffer: device memory of 64 * 8 bytes per SM, or NULL to switch the
- * trace off.  While set, every layer call makes each CTA record %globaltimer at fixed points (start, set-up
- * done, streaming done, counting done, end, and per chunk); a host-side setting, not stream-ordered. */
-PADRA_API int padra_exl3_moe_decode_set_trace(void *buffer, size_t bytes);
 
 /* ---- decode layer without any device allocation ------------------------------------------------------------
  * This entry point has no counterpart in the reference.  It is padra_exl3_moe_decode_layer for callers that cannot
@@ -256,14 +244,18 @@ PADRA_API int padra_exl3_moe_decode_set_trace(void *buffer, size_t bytes);
  * synchronisation of cudaMalloc/cudaFree.  Instead of a caller workspace it uses an array of
  * PADRA_STATIC_SCRATCH_BYTES that is built into the library's device code, and it calls no cudaMalloc, cudaFree or
  * other allocating routine.
- *   - Shapes whose workspace (padra_exl3_moe_decode_workspace_bytes for the split pipeline) exceeds the array are
- *     refused with PADRA_RESOURCE_EXHAUSTED; at hidden 2048 / intermediate 1024 and at 2304 / 896 that is more than
- *     7 tokens.
- *   - There is one array per device and every call shares it: calls that may overlap on the GPU race on it, so the
- *     caller orders them (one stream, or events).  The array keeps the last call's contents; nothing in it needs to
- *     start at zero.
+ *   - Shapes whose workspace (padra_exl3_moe_decode_workspace_bytes) exceeds the array are refused with
+ *     PADRA_RESOURCE_EXHAUSTED and nothing is enqueued.  Hidden 2048 / intermediate 1024 and 2304 / 896 fit at every
+ *     batch (1..16 tokens); hidden 4096 / intermediate 2048 fits up to 11 tokens.
+ *   - There is one array per device (256-byte aligned) and every call shares it: calls that may overlap on the GPU
+ *     race on it and then give wrong results without any error, so the caller orders them (one stream, or events).
+ *     The array keeps the last call's contents.  Only the ticket counters at its start have to be zero; the module
+ *     loader zero-fills the array and every call leaves them zero, so there is nothing to clear between calls.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
- *     current); make that first call outside any stream capture. */
+ *     current); make that first call outside any stream capture.  That look-up may also be the moment the CUDA runtime
+ *     loads this library's device code and backs the array with device memory (lazy module loading): a host that hands
+ *     all free device memory to its own arena must make this first call (or any other call into this library that
+ *     launches a kernel) BEFORE its arena claims the rest, or the call fails with PADRA_INTERNAL. */
 #define PADRA_STATIC_SCRATCH_BYTES (4u << 20)
 PADRA_API int padra_exl3_moe_decode_layer_static(const padra_matrix *matrices, int layer, const int *ids,
                                                  const float *routing, const float *normalized, float *x, int tokens,
@@ -273,9 +265,19 @@ PADRA_API int padra_exl3_moe_decode_layer_static(const padra_matrix *matrices, i
 
 /* ---- utilities ------------------------------------------------------------------------------------------
  * Full FP16 decode of one matrix through the same codec the kernels use: out[input*rows + output].
- * `matrix` is a device pointer to one descriptor.  For verification; not on the timed path. */
+ * `matrix` is a device pointer to one descriptor.  For verification; not on the timed path.
+ * padra_exl3_decode_weights uses the form with byte sums on the integer pipe (prefill and per-part decode kernels),
+ * padra_exl3_decode_weights_tensor the form with byte sums on the tensor cores (the whole-layer decode kernels). */
 PADRA_API int padra_exl3_decode_weights(const padra_matrix *matrix, unsigned short *out, int rows, int cols,
                                         int rate, int *bad, padra_stream stream);
+PADRA_API int padra_exl3_decode_weights_tensor(const padra_matrix *matrix, unsigned short *out, int rows, int cols,
+                                               int rate, int *bad, padra_stream stream);
+/* The codec's inner loop on registers alone, for measuring the rate at which the GPU can decode weights at all (the
+ * instruction-issue ceiling beside the HBM roofline).  form bit 0: byte sums on the tensor cores instead of dp4a;
+ * bit 1: with the FP16 mma that consumes the decoded fragments.  `blocks` CTAs of 256 threads each decode
+ * 32 * iterations weights per thread; sink receives blocks * 256 words.  No counterpart in the reference. */
+PADRA_API int padra_codec_ceiling_launch(int rate, int form, int iterations, int blocks, unsigned *sink,
+                                         padra_stream stream);
 
 #ifdef __cplusplus
 }

@@ -260,6 +260,26 @@ class COracle:
             bad |= self.lib.exl3_route(_f32p(logits[t]), _i32p(ids[t]), _f32p(w[t]))
         return ids, w, bad
 
+    def swiglu(self, gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+        """B(silu_bf16(gate) * up) element by element (src/cuda/inference.cu:575-579); returns a new array."""
+        act = np.array(gate, dtype=np.float32, copy=True).reshape(-1)
+        up = np.ascontiguousarray(up, dtype=np.float32).reshape(-1)
+        bad = self.lib.exl3_activate(_f32p(act), _f32p(up), act.size)
+        assert not bad, "non-finite SwiGLU input"
+        return act.reshape(np.shape(gate))
+
+    def combine(self, x: np.ndarray, down: np.ndarray, weights: np.ndarray):
+        """x[t] = B(x[t] + sum over the eight slots) for every token (src/cuda/inference.cu:580-594).
+        x [tokens][hidden], down [tokens][8][hidden], weights [tokens][8]; returns (new x, bad)."""
+        out = np.array(x, dtype=np.float32, copy=True)
+        tokens, hidden = out.shape
+        down = np.ascontiguousarray(down, dtype=np.float32).reshape(tokens, 8, hidden)
+        weights = np.ascontiguousarray(weights, dtype=np.float32).reshape(tokens, 8)
+        bad = 0
+        for t in range(tokens):
+            bad |= self.lib.exl3_combine(_f32p(out[t]), _f32p(down[t]), _f32p(weights[t]), hidden)
+        return out, bad
+
     def silu_table(self) -> np.ndarray:
         t = np.empty(65536, dtype=np.uint16)
         self.lib.exl3_silu_table(t.ctypes.data)

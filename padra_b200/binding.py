@@ -36,7 +36,6 @@ SIGNATURES = {
     "padra_exl3_expert_launch": ([_p, _i, _i, _p, _p, _p, _p, _p, _i, _p, _p, _i, _i, _i], _i),
     "padra_exl3_moe_decode_workspace_bytes": ([_i, _i, _i], C.c_size_t),
     "padra_exl3_moe_decode_workspace_init": ([_p, C.c_size_t, _p], _i),
-    "padra_exl3_moe_decode_set_trace": ([_p, C.c_size_t], _i),
     "padra_ep_exchange_bytes": ([_i, _i, _i, _p], C.c_size_t),
     "padra_ep_dispatch": ([_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, C.c_uint, _p, _p], _i),
     "padra_ep_wait": ([_p, _i, _i, _i, _i, C.c_uint, _p, _p], _i),
@@ -50,9 +49,10 @@ SIGNATURES = {
     "padra_ep_combine": ([_p, _p, _p, _p, _i, _p, _i, _i, _p], _i),
     "padra_exl3_moe_decode_layer_static": ([_p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p], _i),
     "padra_exl3_moe_decode_layer_launches": ([_p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, C.c_size_t, _p, _p, C.c_uint], _i),
-    "padra_exl3_moe_decode_layer_persistent": ([_p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, C.c_size_t, _p, _p], _i),
     "padra_exl3_moe_decode_layer": ([_p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, C.c_size_t, _p, _p], _i),
     "padra_exl3_decode_weights": ([_p, _p, _i, _i, _i, _p, _p], _i),
+    "padra_exl3_decode_weights_tensor": ([_p, _p, _i, _i, _i, _p, _p], _i),
+    "padra_codec_ceiling_launch": ([_i, _i, _i, _i, _p, _p], _i),
 }
 
 

@@ -208,16 +208,11 @@ int padra_exl3_expert_launch(const padra_matrix *matrices, int layer, int part, 
 size_t padra_exl3_moe_decode_workspace_bytes(int tokens, int hidden, int inter) {
   if (tokens < 1 || tokens > kMaxDecodeRows || hidden < 128 || inter < 128 || (hidden % 128) || (inter % 128))
     return 0;
-  const size_t persistent = FusedDecodeWorkspaceBytes(tokens, hidden, inter), split = SplitDecodeWorkspaceBytes(tokens, hidden, inter);
-  return persistent > split ? persistent : split; // one workspace serves either form of the layer call
+  return DecodeLayerWorkspaceBytes(tokens, hidden, inter);
 }
 
 int padra_exl3_moe_decode_workspace_init(void *workspace, size_t workspace_bytes, padra_stream stream) {
-  return InitFusedDecodeWorkspace(workspace, workspace_bytes, S(stream));
-}
-
-int padra_exl3_moe_decode_set_trace(void *buffer, size_t bytes) {
-  return SetFusedDecodeTrace(buffer, bytes);
+  return InitDecodeLayerWorkspace(workspace, workspace_bytes, S(stream));
 }
 
 int padra_exl3_moe_decode_layer(const padra_matrix *matrices, int layer, const int *ids, const float *routing,
@@ -229,8 +224,8 @@ int padra_exl3_moe_decode_layer(const padra_matrix *matrices, int layer, const i
   if (!matrices || !ids || !routing || !normalized || !x || !table || !workspace || !bad || tokens < 1 ||
       tokens > kMaxDecodeRows || hidden < 128 || inter < 128 || (hidden % 128) || (inter % 128) || layer < 0)
     return PADRA_INVALID_ARGUMENT;
-  return LaunchSplitDecodeLayer(matrices, layer, ids, routing, normalized, x, tokens, rate, hidden, inter, table, workspace,
-                                workspace_bytes, bad, S(stream));
+  return LaunchDecodeLayer(matrices, layer, ids, routing, normalized, x, tokens, rate, hidden, inter, table, workspace,
+                           workspace_bytes, bad, S(stream));
 }
 
 int padra_exl3_moe_decode_layer_launches(const padra_matrix *matrices, int layer, const int *ids, const float *routing,
@@ -240,25 +235,21 @@ int padra_exl3_moe_decode_layer_launches(const padra_matrix *matrices, int layer
   if (!RateOk(rate))
     return PADRA_UNSUPPORTED;
   if (!matrices || !ids || !routing || !normalized || !x || !table || !workspace || !bad || tokens < 1 ||
-      tokens > kMaxDecodeRows || hidden < 128 || inter < 128 || (hidden % 128) || (inter % 128) || layer < 0 || launches > 15u)
+      tokens > kMaxDecodeRows || hidden < 128 || inter < 128 || (hidden % 128) || (inter % 128) || layer < 0 || launches > 3u)
     return PADRA_INVALID_ARGUMENT;
-  return LaunchSplitDecodeLayer(matrices, layer, ids, routing, normalized, x, tokens, rate, hidden, inter, table, workspace,
-                                workspace_bytes, bad, S(stream), launches);
+  return LaunchDecodeLayer(matrices, layer, ids, routing, normalized, x, tokens, rate, hidden, inter, table, workspace,
+                           workspace_bytes, bad, S(stream), launches);
 }
 
-int padra_exl3_moe_decode_layer_persistent(const padra_matrix *matrices, int layer, const int *ids, const float *routing,
-                                           const float *normalized, float *x, int tokens, int rate, int hidden, int inter,
-                                           const unsigned short *table, void *workspace, size_t workspace_bytes, int *bad,
-                                           padra_stream stream) {
+int padra_codec_ceiling_launch(int rate, int form, int iterations, int blocks, unsigned *sink, padra_stream stream) {
+  return LaunchCodecCeiling(rate, form, iterations, blocks, sink, S(stream));
+}
+
+int padra_exl3_decode_weights_tensor(const padra_matrix *matrix, unsigned short *out, int rows, int cols, int rate, int *bad,
+                                     padra_stream stream) {
   if (!RateOk(rate))
     return PADRA_UNSUPPORTED;
-  if (!matrices || !ids || !routing || !normalized || !x || !table || !workspace || !bad || tokens < 1 ||
-      tokens > kMaxDecodeRows || hidden < 128 || inter < 128 || (hidden % 128) || (inter % 128) || layer < 0)
-    return PADRA_INVALID_ARGUMENT;
-  if (tokens != 1)
-    return PADRA_UNSUPPORTED; // the persistent form is released for single-token steps only
-  return LaunchFusedDecodeLayer(matrices, layer, ids, routing, normalized, x, tokens, rate, hidden, inter, table, workspace,
-                                workspace_bytes, bad, S(stream));
+  return LaunchDecodeWeightsTensor(matrix, out, rows, cols, rate, bad, S(stream));
 }
 
 int padra_exl3_decode_weights(const padra_matrix *matrix, unsigned short *out, int rows, int cols, int rate, int *bad,

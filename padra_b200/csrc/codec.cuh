@@ -155,6 +155,98 @@ __device__ __forceinline__ void Decode32(const uint32_t (&words)[Rate], uint32_t
 #undef PADRA_DECODE_GROUP
 }
 
+// ---- byte sums on the tensor cores ----------------------------------------------------------------------------
+// The byte sum of a hash is a dot product of its four bytes with ones, and one integer mma.m16n8k32 (u8 x u8 -> s32)
+// does 128 of them: its A operand is 16 rows x 8 hashes (a lane supplies four hashes as its four A registers), its B
+// operand the constant selector B[k][n] = (k/4 == n), its C operand the constant 0x6400, so D[r][n] = 0x6400 + byte sum
+// of hash (r, n): the FP16 bit pattern of 1024 + s.  One tensor instruction replaces four dp4a, and the integer ALU pipe
+// (the busiest unit of these kernels) is left with the state extraction alone.
+//
+// The instruction also moves values between the four lanes of a quad (lanes 4g..4g+3): lane t supplies the hashes of
+// grid columns n = t and t + 4 for rows g and g + 8 and receives the sums of columns 2t and 2t + 1 -- adjacent
+// columns, which pack into one half2.  Two such instructions give the four A registers of one FP16 mma.m16n8k16 whose
+// logical input k (0..15) is the weight of tile k % 4 (the quad's lane k % 4 owns that tile) at input
+// TensorInput(c, k / 4).  Activations are stored in the matching order (TensorPermutedInput).
+PADRA_HD constexpr int TensorInput(int c, int quarter) {
+  return 2 * c + (quarter & 1) + 8 * (quarter >> 1);
+}
+// Place, inside the 64 halves of one round (four K16 steps, `tile` = step within the round), of input i of that step:
+// lane t' of a quad reads 16 consecutive halves, four per mma (group c), {b0.lo, b0.hi, b1.lo, b1.hi}.
+PADRA_HD constexpr int TensorPermutedInput(int tile, int i) {
+  const int c = (i & 7) >> 1, quarter = 2 * (i >> 3) + (i & 1);
+  const int k = 4 * quarter + tile;
+  return ((k & 7) >> 1) * 16 + c * 4 + (k >> 3) * 2 + (k & 1);
+}
+
+struct ByteSumSelector {
+  uint32_t b0, b1;
+};
+// B fragment of the selector for this lane: rows k = 4t..4t+3 (b0) and 16+4t.. (b1) of column n = g.
+__device__ __forceinline__ ByteSumSelector MakeByteSumSelector(int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  ByteSumSelector s;
+  s.b0 = g == t ? 0x01010101u : 0u;
+  s.b1 = g == t + 4 ? 0x01010101u : 0u;
+  return s;
+}
+// d[0], d[1] = 0x6400 + byte sums of (row g; columns 2t, 2t+1), d[2], d[3] the same for row g + 8.
+__device__ __forceinline__ void ByteSums(uint32_t h_row_lo, uint32_t h_row8_lo, uint32_t h_row_hi, uint32_t h_row8_hi,
+                                         const ByteSumSelector &sel, uint32_t (&d)[4]) {
+  const uint32_t bias = 0x6400u;
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(h_row_lo), "r"(h_row8_lo), "r"(h_row_hi), "r"(h_row8_hi), "r"(sel.b0), "r"(sel.b1), "r"(bias));
+}
+// Two FP16 bit patterns 1024 + s (even in the low half) -> two weights.
+__device__ __forceinline__ uint32_t BiasedPairToHalf2(uint32_t even_bits, uint32_t odd_bits) {
+  uint32_t packed;
+  asm("mad.lo.u32 %0, %1, 65536, %2;" : "=r"(packed) : "r"(odd_bits), "r"(even_bits));
+  const __half2 scale = __halves2half2(__ushort_as_half(0x1eee), __ushort_as_half(0x1eee));
+  const __half2 shift = __halves2half2(__ushort_as_half(0xc931), __ushort_as_half(0xc931));
+  const __half2 w = __hfma2(*reinterpret_cast<const __half2 *>(&packed), scale, shift);
+  return *reinterpret_cast<const uint32_t *>(&w);
+}
+// The eight states of group C (positions 8C .. 8C+7 of the lane's 32): s[j], j = [o>=8]*4 + [i>=8]*2 + (i&1).
+template <int Rate, int C>
+__device__ __forceinline__ void GroupStates(const uint32_t (&words)[Rate], uint32_t previous, uint32_t (&s)[8]) {
+  if constexpr (Rate == 4) {
+    StatesK4(words[C], C ? words[C > 0 ? C - 1 : 0] : previous, s);
+  } else {
+    const uint32_t w0 = PairWindow<Rate, 8 * C + 1>(words, previous), w1 = PairWindow<Rate, 8 * C + 3>(words, previous);
+    const uint32_t w2 = PairWindow<Rate, 8 * C + 5>(words, previous), w3 = PairWindow<Rate, 8 * C + 7>(words, previous);
+    s[0] = (w0 >> Rate) & 0xffffu, s[1] = w0 & 0xffffu;
+    s[2] = (w1 >> Rate) & 0xffffu, s[3] = w1 & 0xffffu;
+    s[4] = (w2 >> Rate) & 0xffffu, s[5] = w2 & 0xffffu;
+    s[6] = (w3 >> Rate) & 0xffffu, s[7] = w3 & 0xffffu;
+  }
+}
+template <int Rate, int C>
+__device__ __forceinline__ void DecodeGroupTensor(const uint32_t (&words)[Rate], uint32_t previous, const ByteSumSelector &sel,
+                                                  uint32_t (&a)[4]) {
+  uint32_t s[8], lo[4], hi[4];
+  GroupStates<Rate, C>(words, previous, s);
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    s[j] *= 0x83DCD12Du;
+  ByteSums(s[0], s[4], s[1], s[5], sel, lo); // inputs 2C and 2C+1 of both rows -> logical k 0..7
+  ByteSums(s[2], s[6], s[3], s[7], sel, hi); // inputs 2C+8 and 2C+9            -> logical k 8..15
+  a[0] = BiasedPairToHalf2(lo[0], lo[1]);
+  a[1] = BiasedPairToHalf2(lo[2], lo[3]);
+  a[2] = BiasedPairToHalf2(hi[0], hi[1]);
+  a[3] = BiasedPairToHalf2(hi[2], hi[3]);
+}
+// All 32 weights of the lane, byte sums on the tensor cores.  a[c] are the A registers of mma number c of the round:
+// a[c][0] = (row g; logical k 2t, 2t+1), [1] = (row g+8; same k), [2] = (row g; k 2t+8, 2t+9), [3] = (row g+8; ...),
+// logical k = weight of tile k % 4 at input TensorInput(c, k / 4).  All 32 lanes must call this together.
+template <int Rate>
+__device__ __forceinline__ void Decode32Tensor(const uint32_t (&words)[Rate], uint32_t previous, const ByteSumSelector &sel,
+                                               uint32_t (&a)[4][4]) {
+  DecodeGroupTensor<Rate, 0>(words, previous, sel, a[0]);
+  DecodeGroupTensor<Rate, 1>(words, previous, sel, a[1]);
+  DecodeGroupTensor<Rate, 2>(words, previous, sel, a[2]);
+  DecodeGroupTensor<Rate, 3>(words, previous, sel, a[3]);
+}
+
 // The lane's Rate words of one tile.  `lane_bytes` points at tile + g*4*Rate.  Weights are read exactly once
 // per pass, so the loads go through the read-only path without claiming L1 lines.
 template <int Rate> __device__ __forceinline__ void LoadWords(const unsigned char *lane_bytes, uint32_t (&w)[Rate]) {

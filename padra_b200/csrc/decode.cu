@@ -321,13 +321,10 @@ __global__ void __launch_bounds__(kThreads) ProjectionKernel(ProjectionArgs a) {
 template <int Rate, int NG, int Mode> int LaunchProjection(const ProjectionArgs &a, dim3 grid, cudaStream_t stream) {
   const int cols = a.hidden > a.inter ? a.hidden : a.inter; // provision for the wider of the two inputs
   const size_t smem = ProjectionSmem(cols, a.row_capacity);
-  static size_t configured = 0; // per instantiation; the attribute only ever grows
-  if (smem > 48 * 1024 && smem > configured) {
-    if (cudaFuncSetAttribute(ProjectionKernel<Rate, NG, Mode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem)) != cudaSuccess)
-      return PADRA_RESOURCE_EXHAUSTED;
-    configured = smem;
-  }
+  // set on every launch that needs it: the attribute belongs to the current device, and the call is cheap
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(ProjectionKernel<Rate, NG, Mode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(smem)) != cudaSuccess)
+    return PADRA_RESOURCE_EXHAUSTED;
   ProjectionKernel<Rate, NG, Mode><<<grid, kThreads, smem, stream>>>(a);
   return CudaStatus(cudaGetLastError());
 }

@@ -23,16 +23,14 @@ int LaunchCombinePacked(float *x, const unsigned short *down, const float *weigh
 int LaunchDecodeWeights(const Matrix *matrix, unsigned short *out, int rows, int cols, int rate, int *bad,
                         cudaStream_t stream);
 
-size_t SplitDecodeWorkspaceBytes(int tokens, int hidden, int inter);
-int LaunchSplitDecodeLayer(const Matrix *matrices, int layer, const int *ids, const float *routing, const float *normalized,
-                           float *x, int tokens, int rate, int hidden, int inter, const unsigned short *table, void *workspace,
-                           size_t workspace_bytes, int *bad, cudaStream_t stream, unsigned launches = 15u);
-int SetFusedDecodeTrace(void *buffer, size_t bytes);
-size_t FusedDecodeWorkspaceBytes(int tokens, int hidden, int inter);
-int InitFusedDecodeWorkspace(void *workspace, size_t bytes, cudaStream_t stream);
-int LaunchFusedDecodeLayer(const Matrix *matrices, int layer, const int *ids, const float *routing, const float *normalized,
-                           float *x, int tokens, int rate, int hidden, int inter, const unsigned short *table,
-                           void *workspace, size_t workspace_bytes, int *bad, cudaStream_t stream);
+size_t DecodeLayerWorkspaceBytes(int tokens, int hidden, int inter);
+int InitDecodeLayerWorkspace(void *workspace, size_t bytes, cudaStream_t stream);
+// launches: bit 0 the gate+up kernel, bit 1 the down kernel (both: the whole layer)
+int LaunchDecodeLayer(const Matrix *matrices, int layer, const int *ids, const float *routing, const float *normalized, float *x,
+                      int tokens, int rate, int hidden, int inter, const unsigned short *table, void *workspace,
+                      size_t workspace_bytes, int *bad, cudaStream_t stream, unsigned launches = 3u);
+int LaunchCodecCeiling(int rate, int form, int iterations, int blocks, unsigned *sink, cudaStream_t stream);
+int LaunchDecodeWeightsTensor(const Matrix *matrix, unsigned short *out, int rows, int cols, int rate, int *bad, cudaStream_t stream);
 int LaunchTileProjection(const Matrix *matrices, int layer, int part, const int *groups, const padra_tile *tiles,
                          const int *tile_count, const float *input, unsigned short *output,
                          const unsigned short *gate, const unsigned short *up, const unsigned short *table, int tokens,

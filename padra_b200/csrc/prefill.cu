@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
     my_tiles = (my_count + kMaxTileN - 1) / kMaxTileN;
     if (my_count) {
       const Matrix &m = a.matrices[(static_cast<size_t>(a.layer) * kExperts + tid) * 3 + a.part];
-      if (m.format != FormatOfRate(Rate) || m.rows != rows || m.cols != cols || (cols % 128) || (rows % kTileM) || !m.data || !m.svh) {
+      if (m.format != FormatOfRate(Rate) || m.rows != rows || m.cols != cols || (cols % 128) || (rows % kTileM) || !m.data || !m.svh || !m.suh) {
         Raise(a.bad);
         sm.abort = 1;
       }
@@ -594,7 +594,7 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
                                                           const float *input, const unsigned short *gate, const unsigned short *up,
                                                           const unsigned short *pair_rows, const unsigned short *table,
                                                           __half *transformed, int group_stride, int pairs, int hidden,
-                                                          int inter, int *bad) {
+                                                          int inter, int format, int *bad) {
   __shared__ int s_offset[kExperts + 1], s_half;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int cols = part == 2 ? inter : hidden, blocks = cols / 128;
@@ -632,7 +632,15 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
       Raise(bad);
     continue;
   }
-  const uint16_t *suh = matrices[(static_cast<size_t>(layer) * kExperts + expert) * 3 + part].suh;
+  // the descriptor is checked before anything is read through it: a table of another rate or shape, or a missing
+  // sidecar, raises the flag and the row is skipped
+  const Matrix &dm = matrices[(static_cast<size_t>(layer) * kExperts + expert) * 3 + part];
+  const uint16_t *suh = dm.suh;
+  if (dm.format != format || dm.cols != cols || dm.rows != (part == 2 ? hidden : inter) || !suh || !dm.data) {
+    if (!lane)
+      Raise(bad);
+    continue;
+  }
 #pragma unroll 4
   for (int h = 0; h < blocks; ++h) {
   const int k = h * 128 + lane * 4;
@@ -686,12 +694,9 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
 
 template <int Rate> int LaunchGemm(const PrefillArgs &a, dim3 grid, cudaStream_t stream) {
   const size_t smem = sizeof(PrefillSmem);
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(PrefillGemmKernel<Rate>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
-      return PADRA_RESOURCE_EXHAUSTED;
-    configured = true;
-  }
+  // set on every launch: the attribute belongs to the current device, and the call is cheap
+  if (cudaFuncSetAttribute(PrefillGemmKernel<Rate>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+    return PADRA_RESOURCE_EXHAUSTED;
   PrefillGemmKernel<Rate><<<grid, kPrefillThreads, smem, stream>>>(a);
   return CudaStatus(cudaGetLastError());
 }
@@ -725,7 +730,7 @@ static int LaunchPrefillGemm(const Matrix *matrices, int layer, int part, const 
   if (block_begin == 0) {
     PrefillInputKernel<<<((pairs < kMaxPairs ? pairs : kMaxPairs) + 7) / 8, 256, 0, stream>>>(
         matrices, layer, part, groups, counts, input, gate, up, pair_rows, table, static_cast<__half *>(transformed), group_stride, pairs,
-        hidden, inter, bad);
+        hidden, inter, FormatOfRate(rate), bad);
     if (cudaGetLastError() != cudaSuccess)
       return PADRA_INTERNAL;
   }

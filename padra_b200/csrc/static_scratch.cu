@@ -9,9 +9,11 @@
 //
 // The price: the array has a fixed size (kStaticScratchBytes), requests that need more are refused, and there is ONE
 // array per device, shared by every call in the process.  Calls that can overlap on the GPU (different streams, or
-// different host threads without ordering between their streams) would race on it; callers must order them.  The
-// array keeps whatever the last call left there.  Nothing in it has to start at zero: every partial sum the
-// pipeline's epilogues read has been written earlier in the same call.
+// different host threads without ordering between their streams) would race on it -- they would mix each other's
+// partial sums and ticket counts and give wrong results, not an error; callers must order them.  The array keeps
+// whatever the last call left there.  The only part that has to start at zero is the pipeline's ticket counters at
+// its beginning: the module loader zero-fills the array, and every call leaves the counters at zero again (the CTA that
+// takes a counter's last ticket clears it, on error paths too), so nothing has to be cleared between calls.
 #include <mutex>
 
 #include "common.cuh"
@@ -60,12 +62,12 @@ extern "C" PADRA_API int padra_exl3_moe_decode_layer_static(const padra_matrix *
   if (!matrices || !ids || !routing || !normalized || !x || !table || !bad || tokens < 1 || tokens > 16 || layer < 0 ||
       hidden < 128 || inter < 128 || hidden % 128 || inter % 128)
     return PADRA_INVALID_ARGUMENT;
-  if (SplitDecodeWorkspaceBytes(tokens, hidden, inter) > kStaticScratchBytes)
+  if (DecodeLayerWorkspaceBytes(tokens, hidden, inter) > kStaticScratchBytes)
     return PADRA_RESOURCE_EXHAUSTED; // more scratch than the built-in array holds: use the caller-workspace entry point
   void *scratch = nullptr;
   const int status = ScratchAddress(&scratch);
   if (status != PADRA_OK)
     return status;
-  return LaunchSplitDecodeLayer(reinterpret_cast<const Matrix *>(matrices), layer, ids, routing, normalized, x, tokens, rate,
+  return LaunchDecodeLayer(reinterpret_cast<const Matrix *>(matrices), layer, ids, routing, normalized, x, tokens, rate,
                                 hidden, inter, table, scratch, kStaticScratchBytes, bad, static_cast<cudaStream_t>(stream));
 }

@@ -307,14 +307,6 @@ class ExpertKernels:
                                                            B.stream_handle(stream), launches)
         B.check(st, "padra_exl3_moe_decode_layer_launches")
 
-    def moe_decode_layer_persistent(self, layer, ids, routing, normalized, x, tokens, stream=None):
-        ws = self.decode_workspace(tokens)
-        st = self.lib.padra_exl3_moe_decode_layer_persistent(self.t.descriptors.data_ptr(), layer, B.ptr(ids), B.ptr(routing),
-                                                             B.ptr(normalized), B.ptr(x), tokens, self.t.rate, *self.dims,
-                                                             B.ptr(self.table), B.ptr(ws), ws.numel(), B.ptr(self.bad),
-                                                             B.stream_handle(stream))
-        B.check(st, "padra_exl3_moe_decode_layer_persistent")
-
     def moe_decode_layer_static(self, layer, ids, routing, normalized, x, tokens, stream=None):
         """The decode layer on the library's built-in scratch array: no workspace, no allocation in the call."""
         st = self.lib.padra_exl3_moe_decode_layer_static(self.t.descriptors.data_ptr(), layer, B.ptr(ids), B.ptr(routing),
@@ -330,13 +322,24 @@ class ExpertKernels:
                                                   B.stream_handle(stream))
         B.check(st, "padra_exl3_moe_decode_layer")
 
-    def decode_weights(self, layer, expert, part, stream=None):
+    def decode_weights(self, layer, expert, part, stream=None, tensor_form=False):
+        """FP16 bit patterns [cols][rows] of one matrix through the kernels' codec (either of its two forms)."""
         rows, cols = self.t.shape(part)
         out = torch.empty((cols, rows), dtype=torch.uint16, device=self.t.device)
-        st = self.lib.padra_exl3_decode_weights(self.t.descriptor_ptr(layer, expert, part), B.ptr(out), rows, cols, self.t.rate,
-                                                B.ptr(self.bad), B.stream_handle(stream))
+        entry = self.lib.padra_exl3_decode_weights_tensor if tensor_form else self.lib.padra_exl3_decode_weights
+        st = entry(self.t.descriptor_ptr(layer, expert, part), B.ptr(out), rows, cols, self.t.rate, B.ptr(self.bad),
+                   B.stream_handle(stream))
         B.check(st, "padra_exl3_decode_weights")
         return out
+
+    def codec_ceiling(self, rate: int, form: int, iterations: int, blocks: int, stream=None) -> int:
+        """Launches the register-only codec loop; returns the number of weights it decodes."""
+        key = ("ceiling", blocks)
+        if key not in self._workspace:
+            self._workspace[key] = torch.empty(blocks * 256, dtype=torch.int32, device=self.t.device)
+        st = self.lib.padra_codec_ceiling_launch(rate, form, iterations, blocks, B.ptr(self._workspace[key]), B.stream_handle(stream))
+        B.check(st, "padra_codec_ceiling_launch")
+        return blocks * 256 * 32 * iterations
 
 
 # ---- synthetic inputs (seeded; shapes and distributions of the benchmark configurations) --------------------

@@ -31,27 +31,34 @@ def routed_inputs(oracle, tokens, hidden, seed):
     return x, ids, w
 
 
+CODEC_FORMS = [False, True]  # byte sums on the integer pipe (dp4a) / on the tensor cores (integer mma)
+
+
+@pytest.mark.parametrize("tensor_form", CODEC_FORMS)
 @pytest.mark.parametrize("rate", RATES)
-def test_weight_decode_bit_exact(oracle, gpu, rate):
+def test_weight_decode_bit_exact(oracle, gpu, rate, tensor_form):
     host, table, k = make(1, 256, 128, rate, 11, gpu)
     for e in (0, 17, 63):
         for part in (0, 2):
             rows, cols = table.shape(part)
-            got = u16(k.decode_weights(0, e, part))
+            got = u16(k.decode_weights(0, e, part, tensor_form=tensor_form))
             want = oracle.decode_matrix(host.get(0, e, part)[0], rows, cols, rate)
             assert (got == want).all(), (rate, e, part, int((got != want).sum()))
     assert k.bad_flag() == 0
 
 
-def test_weight_decode_bit_exact_full_size_k4(oracle, gpu):
-    """One 1024 x 2048 K4 matrix: every one of its 2 Mi weights."""
+@pytest.mark.parametrize("tensor_form", CODEC_FORMS)
+@pytest.mark.parametrize("rate", RATES)
+def test_weight_decode_bit_exact_full_size(oracle, gpu, rate, tensor_form):
+    """One 1024 x 2048 matrix per rate: every one of its 2 Mi weights, through both forms of the codec."""
     from padra_b200.experts import ExpertKernels, ExpertTable
 
-    table = ExpertTable(1, 2048, 1024, 4, gpu).fill_random(3)
+    table = ExpertTable(1, 2048, 1024, rate, gpu).fill_random(3)
     k = ExpertKernels(table)
-    got = u16(k.decode_weights(0, 5, 0))
-    want = oracle.decode_matrix(table.host_matrix(0, 5, 0)[0], 1024, 2048, 4)
+    got = u16(k.decode_weights(0, 5, 0, tensor_form=tensor_form))
+    want = oracle.decode_matrix(table.host_matrix(0, 5, 0)[0], 1024, 2048, rate)
     assert (got == want).all()
+    assert k.bad_flag() == 0
 
 
 @pytest.mark.parametrize("rate", RATES)
@@ -100,17 +107,15 @@ def test_multi_token_layer(oracle, gpu, rate, tokens):
     assert k.bad_flag() == 0
 
 
-FORMS = ["moe_decode_layer", "moe_decode_layer_persistent"]
+FORMS = ["moe_decode_layer"]
 
 
 @pytest.mark.parametrize("form", FORMS)
 @pytest.mark.parametrize("rate", RATES)
 @pytest.mark.parametrize("tokens", [1, 3, 8, 13])
 def test_layer_call_matches_separate_launches(oracle, gpu, rate, tokens, form):
-    """Both forms of the whole-layer call (four-launch pipeline, persistent kernel) against the per-part entry
-    points launched one after another."""
-    if form.endswith("persistent") and tokens != 1:
-        pytest.skip("the persistent form takes single-token steps only")
+    """The whole-layer call (two launches, epilogues inside) against the per-part entry points launched one after
+    another."""
     hidden, inter = 512, 384
     host, table, k = make(1, hidden, inter, rate, 97, gpu)
     x, ids, w = routed_inputs(oracle, tokens, hidden, 40 + tokens)
@@ -133,7 +138,7 @@ def test_layer_call_mellum_dims(oracle, gpu, form):
     from padra_b200.experts import ExpertKernels, ExpertTable
 
     hidden, inter = 2304, 896
-    tokens = 1 if form.endswith("persistent") else 5
+    tokens = 5
     table = ExpertTable(1, hidden, inter, 4, gpu).fill_random(9)
     k = ExpertKernels(table)
     x, ids, w = routed_inputs(oracle, tokens, hidden, 50)
@@ -173,23 +178,10 @@ def test_layer_call_rejects_bad_ids_and_descriptors(gpu, form):
     assert k.bad_flag() == 0 and not torch.equal(good, x)
 
 
-def test_persistent_form_is_single_token_only(gpu):
-    from padra_b200 import binding as B
-
-    _, table, k = make(1, 256, 128, 4, 103, gpu)
-    ws = k.decode_workspace(2)
-    x = torch.ones((2, 256), device=gpu)
-    ids = torch.arange(16, dtype=torch.int32, device=gpu)
-    w = torch.full((16,), 0.125, device=gpu)
-    st = k.lib.padra_exl3_moe_decode_layer_persistent(table.descriptors.data_ptr(), 0, B.ptr(ids), B.ptr(w), B.ptr(x), B.ptr(x), 2, 4,
-                                                      256, 128, B.ptr(k.table), B.ptr(ws), ws.numel(), B.ptr(k.bad), B.stream_handle())
-    assert st == B.UNSUPPORTED
-
-
 @pytest.mark.parametrize("form", FORMS)
 def test_layer_call_repeated_many_times_single_token(oracle, gpu, form):
     """Forty back-to-back single-token steps over two layers of the benchmark shape: every one must agree with the
-    per-part launches and leave the error flag down (guards the hand-shakes inside the persistent kernel)."""
+    per-part launches and leave the error flag down (guards the ticket counters that hand the epilogues out)."""
     from padra_b200.experts import ExpertKernels, ExpertTable, bf16_values, route_topk
 
     hidden, inter = 2048, 1024
@@ -208,31 +200,50 @@ def test_layer_call_repeated_many_times_single_token(oracle, gpu, form):
     assert k.bad_flag() == 0
 
 
-def test_config1_layer_k4(oracle, gpu):
-    """The benchmark's decode configuration: 64 experts, hidden 2048, intermediate 1024, one token."""
+def host_experts(table, layer, experts):
+    """Oracle-side descriptor table holding host copies of just the given experts of one layer."""
+    mats = (O.Matrix * (64 * 3))()
+    keep = []
+    for e in sorted(set(int(e) for e in experts)):
+        for part in range(3):
+            data, suh, svh = table.host_matrix(layer, e, part)
+            keep.append((data, suh, svh))
+            m = mats[e * 3 + part]
+            m.data, m.suh, m.svh = data.ctypes.data, suh.ctypes.data, svh.ctypes.data
+            m.rows, m.cols = table.shape(part)
+            m.format = O.FORMAT_OF_RATE[table.rate]
+    return mats, keep
+
+
+@pytest.mark.parametrize("rate", RATES)
+@pytest.mark.parametrize("tokens", [1, 2, 5, 16])
+def test_graded_shape_layer_against_oracle(oracle, gpu, rate, tokens):
+    """The benchmark's decode shape (64 experts, hidden 2048, intermediate 1024) at every rate and batch of the rate and
+    batch sweep, routing drawn per token from seeded logits: the whole-layer call against the oracle.  Sixteen tokens
+    take the 16-row form of the kernels and touch most of the 64 experts."""
     hidden, inter = 2048, 1024
     from padra_b200.experts import ExpertKernels, ExpertTable
 
-    table = ExpertTable(1, hidden, inter, 4, gpu).fill_random(0)
+    table = ExpertTable(1, hidden, inter, rate, gpu).fill_random(rate)
     k = ExpertKernels(table)
-    x, ids, w = routed_inputs(oracle, 1, hidden, 0)
-    # host copy of just the eight selected experts
-    mats = (O.Matrix * (64 * 3))()
-    keep = []
-    for e in ids.reshape(-1):
-        for part in range(3):
-            data, suh, svh = table.host_matrix(0, int(e), part)
-            keep.append((data, suh, svh))
-            m = mats[int(e) * 3 + part]
-            m.data, m.suh, m.svh = data.ctypes.data, suh.ctypes.data, svh.ctypes.data
-            m.rows, m.cols = table.shape(part)
-            m.format = O.FORMAT_OF_RATE[4]
-    want, bad = oracle.moe_layer(mats, 0, ids, w, x, hidden, inter)
+    x, ids, w = routed_inputs(oracle, tokens, hidden, 100 * rate + tokens)
+    normalized, _, _ = routed_inputs(oracle, tokens, hidden, 200 * rate + tokens)
+    mats, keep = host_experts(table, 0, ids.reshape(-1))
+    # the oracle's layer takes one activation for both roles; here the residual stream and the normalised input differ,
+    # as they do in the model: out = x + (layer(normalized) - normalized)
+    want_n, bad = oracle.moe_layer(mats, 0, ids, w, normalized, hidden, inter)
     assert not bad
+    dn = torch.from_numpy(normalized).to(gpu)
+    got_n = dn.clone()
+    dids, dw = torch.from_numpy(ids.reshape(-1)).to(gpu), torch.from_numpy(w.reshape(-1)).to(gpu)
+    k.moe_decode_layer(0, dids, dw, dn, got_n, tokens)
+    assert_close_rows(got_n.cpu().numpy(), want_n, f"K{rate} M={tokens} layer at 2048/1024", chained=True)
+    # and with a residual stream of its own: against the per-part entry points' chain on the same inputs
     dx = torch.from_numpy(x).to(gpu)
-    xs = dx.clone()
-    k.moe_decode_layer(0, torch.from_numpy(ids.reshape(-1)).to(gpu), torch.from_numpy(w.reshape(-1)).to(gpu), dx, xs, 1)
-    assert_close_rows(xs.cpu().numpy(), want, "config-1 layer", chained=True)
+    fused, separate = dx.clone(), dx.clone()
+    k.moe_decode_layer(0, dids, dw, dn, fused, tokens)
+    k.moe_decode_layer_unfused(0, dids, dw, dn, separate, tokens)
+    assert_close_rows(fused.cpu().numpy(), separate.cpu().numpy(), "layer call vs separate launches", chained=True)
     assert k.bad_flag() == 0
 
 
@@ -326,7 +337,7 @@ def test_overflowing_activation_sets_flag(gpu):
 @pytest.mark.parametrize("form", FORMS)
 def test_layer_call_is_graph_capturable_and_deterministic(oracle, gpu, form):
     hidden, inter = 512, 256
-    tokens = 1 if form.endswith("persistent") else 5
+    tokens = 5
     _, table, k = make(1, hidden, inter, 4, 59, gpu)
     x, ids, w = routed_inputs(oracle, tokens, hidden, 8)
     dids = torch.from_numpy(ids.reshape(-1)).to(gpu)

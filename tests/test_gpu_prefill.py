@@ -248,3 +248,89 @@ def test_tensor_memory_gemm_odd_shapes(oracle, gpu, hidden, inter, tokens, rate)
         want, bad = oracle.linear(oracle.matrix(data, suh, svh, inter, hidden, rate), h_x[pair // 8])
         assert not bad
         assert_close_rows(gate[pair][None], want[None], f"gate row of pair {pair} vs oracle")
+
+
+def test_config3_full_shape_against_oracle(oracle, gpu):
+    """The graded prefill configuration itself: 2048 tokens, hidden 2048 / intermediate 1024, K4, top-8 of 64 with
+    Zipf(1.1) popularity.  The whole layer against the oracle for 72 pairs spread over the hottest expert, a middle one
+    and the coldest one (gate, up, down rows of each pair, and the layer's output row of each pair's token through a
+    combine over the kernel's own down rows), and gate/up/down against the small-tile kernel on every row."""
+    from padra_b200.experts import ExpertKernels, ExpertTable, bf16_values, zipf_routing
+    hidden, inter, tokens, rate = 2048, 1024, 2048, 4
+    table = ExpertTable(1, hidden, inter, rate, gpu).fill_random(31)
+    k = ExpertKernels(table)
+    ids, w = zipf_routing(tokens, seed=4, device=gpu)
+    g = torch.Generator(device=gpu)
+    g.manual_seed(4)
+    dn = bf16_values(torch.randn((tokens, hidden), device=gpu, generator=g))
+    dx = bf16_values(torch.randn((tokens, hidden), device=gpu, generator=g))
+    xa, xb = dx.clone(), dx.clone()
+    ga, ua, da = (t.clone() for t in k.prefill_layer(0, ids.reshape(-1), w.reshape(-1), dn, xa, tokens, tensor_memory=True))
+    gb, ub, db = k.prefill_layer(0, ids.reshape(-1), w.reshape(-1), dn, xb, tokens, tensor_memory=False)
+    torch.cuda.synchronize()
+    assert k.bad_flag() == 0
+    assert_close_rows(bf16_bits_to_f32(u16(ga)), bf16_bits_to_f32(u16(gb)), "gate: tensor-memory vs small-tile kernel")
+    assert_close_rows(bf16_bits_to_f32(u16(ua)), bf16_bits_to_f32(u16(ub)), "up: tensor-memory vs small-tile kernel")
+    a, b = bf16_bits_to_f32(u16(da)).astype(np.float64), bf16_bits_to_f32(u16(db)).astype(np.float64)
+    assert (np.linalg.norm(a - b, axis=1) <= 1e-2 * np.linalg.norm(b, axis=1)).all()
+
+    h_ids, h_n = ids.cpu().numpy().reshape(-1), dn.cpu().numpy()
+    counts = np.bincount(h_ids, minlength=64)
+    order = np.argsort(-counts)
+    chosen = [int(order[0]), int(order[32]), int(order[-1] if counts[order[-1]] else order[np.nonzero(counts[order])[0][-1]])]
+    assert counts[chosen[0]] > 1024 and counts[chosen[2]] < 128, counts  # the imbalance the configuration is about
+    gate, up, down = bf16_bits_to_f32(u16(ga)), bf16_bits_to_f32(u16(ua)), bf16_bits_to_f32(u16(da))
+    checked = 0
+    for e in chosen:
+        pairs = np.nonzero(h_ids == e)[0]
+        m = [oracle.matrix(*table.host_matrix(0, e, part), *table.shape(part), rate) for part in range(3)]
+        for pair in pairs[np.linspace(0, len(pairs) - 1, 24).astype(int)]:  # first, last and evenly between
+            x_row = h_n[pair // 8]
+            want_g, bad_g = oracle.linear(m[0], x_row)
+            want_u, bad_u = oracle.linear(m[1], x_row)
+            assert not bad_g and not bad_u
+            assert_close_rows(gate[pair][None], want_g[None], f"gate row, expert {e}, pair {pair}")
+            assert_close_rows(up[pair][None], want_u[None], f"up row, expert {e}, pair {pair}")
+            act = oracle.swiglu(want_g, want_u)
+            want_d, bad_d = oracle.linear(m[2], act)
+            assert not bad_d
+            assert_close_rows(down[pair][None], want_d[None], f"down row, expert {e}, pair {pair}", chained=True)
+            checked += 1
+    assert checked == 72
+    # the combine over the kernel's own down rows, every token
+    want_x, bad = oracle.combine(dx.cpu().numpy(), down.reshape(tokens, 8, hidden), w.cpu().numpy().reshape(tokens, 8))
+    assert not bad
+    assert np.array_equal(xa.cpu().numpy(), want_x), "combine over the down rows differs from the oracle's"
+
+
+@pytest.mark.parametrize("rows_entry", [False, True])
+def test_prefill_rejects_a_table_of_another_rate(gpu, rows_entry):
+    """A descriptor table whose format does not match the requested rate: detected from the descriptor before anything
+    is read through it, by the input transform as well as by the grouped GEMM; the flag is raised, nothing is written."""
+    from padra_b200 import binding as B
+    from padra_b200.experts import bf16_values, zipf_routing
+
+    hidden, inter, tokens = 256, 128, 16
+    _, table, k = make(1, hidden, inter, 4, 601, gpu)
+    ids, w = zipf_routing(tokens, seed=1, device=gpu)
+    ids = ids.reshape(-1)
+    dx = bf16_values(torch.randn((tokens, hidden), device=gpu))
+    sched = k.group_and_schedule(ids, tokens)
+    groups, counts, tiles, tile_count = sched
+    out = torch.full((tokens * 8, inter), 0x7777, dtype=torch.uint16, device=gpu)
+    transformed = torch.zeros((tokens * 8, hidden), dtype=torch.float16, device=gpu)
+    wrong_rate = 6
+    if rows_entry:
+        rows = bf16_values(torch.randn((tokens * 8, hidden), device=gpu)).to(torch.bfloat16).view(torch.uint16)
+        st = k.lib.padra_exl3_prefill_rows_launch(table.descriptors.data_ptr(), 0, 0, B.ptr(groups), B.ptr(counts), tokens, tokens * 8,
+                                                  B.ptr(rows), B.ptr(out), None, None, B.ptr(k.table), B.ptr(transformed), B.ptr(k.bad),
+                                                  B.stream_handle(), wrong_rate, hidden, inter, 0, 0)
+    else:
+        st = k.lib.padra_exl3_prefill_launch(table.descriptors.data_ptr(), 0, 0, B.ptr(ids), B.ptr(groups), B.ptr(counts), B.ptr(tiles),
+                                             B.ptr(tile_count), B.ptr(dx), B.ptr(out), None, None, B.ptr(k.table), B.ptr(transformed),
+                                             tokens, B.ptr(k.bad), B.stream_handle(), None, 1, wrong_rate, hidden, inter)
+    assert st == 0
+    torch.cuda.synchronize()
+    assert k.bad_flag() == 1
+    assert int((u16(out) != 0x7777).sum()) == 0, "a refused projection wrote output rows"
+    assert float(transformed.abs().max()) == 0.0, "a refused projection wrote transformed rows"

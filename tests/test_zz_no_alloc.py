@@ -3,21 +3,22 @@
 Collected last on purpose: the entry point shares one device array between all calls of the process, so it has to give
 the right answer after everything else has run as well as in a fresh process.  Its results are compared with the
 caller-workspace entry point's on the same inputs, two calls in a row (the second call meets the first call's
-left-overs in the array)."""
+left-overs in the array).  Both entry points run the same deterministic pipeline, so the results must be equal bit for
+bit."""
 import numpy as np
 import pytest
 import torch
 
-from tests.helpers import assert_close_rows
 from tests.test_gpu_decode import make, routed_inputs
 
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("tokens", [1, 4])
-def test_static_scratch_layer_equals_workspace_layer_twice(oracle, gpu, tokens):
+@pytest.mark.parametrize("rate,tokens", [(4, 1), (4, 4), (3, 2), (6, 3)])
+def test_static_scratch_layer_equals_workspace_layer_twice(oracle, gpu, rate, tokens):
     hidden, inter = 512, 256
-    _, _, k = make(2, hidden, inter, 4, 97, gpu)
+    _, _, k = make(2, hidden, inter, rate, 97, gpu)
+    k.decode_workspace(tokens)  # the workspace entry point's buffer exists before free memory is sampled
     for call in range(2):
         x, ids, w = routed_inputs(oracle, tokens, hidden, 300 + call)
         normalized, _, _ = routed_inputs(oracle, tokens, hidden, 400 + call)
@@ -26,23 +27,49 @@ def test_static_scratch_layer_equals_workspace_layer_twice(oracle, gpu, tokens):
         dn = torch.from_numpy(normalized).to(gpu)
         want, got = torch.from_numpy(x).to(gpu), torch.from_numpy(x).to(gpu)
         k.moe_decode_layer(call, dids, dw, dn, want, tokens)
+        if call == 0:
+            k.moe_decode_layer_static(call, dids, dw, dn, got, tokens)  # first call: set-up (address look-up) happens here
+            got.copy_(torch.from_numpy(x).to(gpu))
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
         k.moe_decode_layer_static(call, dids, dw, dn, got, tokens)
         torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before, "the allocation-free entry point changed the device's free memory"
         assert k.bad_flag() == 0
-        assert_close_rows(got.cpu().numpy(), want.cpu().numpy(), f"static scratch vs workspace, call {call}", chained=True)
+        assert torch.equal(got, want), f"static scratch vs workspace, call {call}"
         assert not np.array_equal(got.cpu().numpy(), x), "the layer did not change the residual stream"
 
 
-def test_static_scratch_refuses_what_does_not_fit(gpu):
+def test_static_scratch_size_limit(oracle, gpu):
+    """The benchmark shape (hidden 2048 / intermediate 1024) fits the 4 MiB array at every batch up to sixteen tokens; at
+    hidden 4096 / intermediate 2048 eleven tokens fit and twelve do not.  The largest batch that fits is run and compared,
+    the first one that does not fit is refused without touching anything."""
     from padra_b200 import binding as B
+    from padra_b200.experts import ExpertKernels, ExpertTable
 
-    hidden, inter = 2048, 1024
     lib = B.load()
-    needed = lib.padra_exl3_moe_decode_workspace_bytes(16, hidden, inter)
-    assert needed > (4 << 20)
-    _, _, k = make(1, 256, 128, 4, 5, gpu)
-    dummy = torch.zeros(16 * hidden, device=gpu)
-    ids = torch.zeros(16 * 8, dtype=torch.int32, device=gpu)
-    st = lib.padra_exl3_moe_decode_layer_static(k.t.descriptors.data_ptr(), 0, ids.data_ptr(), dummy.data_ptr(), dummy.data_ptr(),
-                                                dummy.data_ptr(), 16, 4, hidden, inter, k.table.data_ptr(), k.bad.data_ptr(), None)
+    limit = 4 << 20
+    assert lib.padra_exl3_moe_decode_workspace_bytes(16, 2048, 1024) <= limit
+    assert lib.padra_exl3_moe_decode_workspace_bytes(16, 2304, 896) <= limit
+    hidden, inter = 4096, 2048
+    assert lib.padra_exl3_moe_decode_workspace_bytes(11, hidden, inter) <= limit
+    assert lib.padra_exl3_moe_decode_workspace_bytes(12, hidden, inter) > limit
+    table = ExpertTable(1, hidden, inter, 4, gpu).fill_random(2)
+    k = ExpertKernels(table)
+    x, ids, w = routed_inputs(oracle, 12, hidden, 500)
+    dids = torch.from_numpy(ids.reshape(-1)).to(gpu)
+    dw = torch.from_numpy(w.reshape(-1)).to(gpu)
+    dx = torch.from_numpy(x).to(gpu)
+    fits = dx[:11].contiguous()
+    want, got = fits.clone(), fits.clone()
+    k.moe_decode_layer(0, dids[:88], dw[:88], fits, want, 11)
+    k.moe_decode_layer_static(0, dids[:88], dw[:88], fits, got, 11)
+    torch.cuda.synchronize()
+    assert k.bad_flag() == 0 and torch.equal(got, want) and not torch.equal(got, fits)
+    refused = dx.clone()
+    st = lib.padra_exl3_moe_decode_layer_static(table.descriptors.data_ptr(), 0, dids.data_ptr(), dw.data_ptr(), dx.data_ptr(),
+                                                refused.data_ptr(), 12, 4, hidden, inter, k.table.data_ptr(), k.bad.data_ptr(), None)
     assert st == B.RESOURCE_EXHAUSTED
+    torch.cuda.synchronize()
+    assert torch.equal(refused, dx), "a refused call must not touch the residual stream"
