@@ -202,9 +202,36 @@ PADRA_API int padra_exl3_prefill_rows_launch(const padra_matrix *matrices, int l
 PADRA_API int padra_ep_combine(float *x, const unsigned short *down_rows, const int *position, const float *weights,
                                int tokens, int *bad, int residual, int hidden, padra_stream stream);
 
+/* ---- the callers either side of the experts: routing and norms -----------------------------------------------
+ * padra_route: RouteRankExact (src/cuda/router_rank_exact.cuh:3-81; launched <<<rows, 64>>> at src/cuda/inference.cu:2950
+ * and :3366): logits [tokens][64] FP32 -> ids [tokens][8] ascending, weights [tokens][8] BF16-valued.  Softmax with FP64
+ * exp rounded to FP32 and ascending compensated sums, rank by probability then index, renormalised over the selection.
+ * A raised *bad or a non-finite logit gives ids 0 and weights 0 for the token and raises *bad.
+ * padra_route_group_schedule: the same routing and, in the same launch, the chunk's expert-major pair lists and 32-pair
+ * tile list (what padra_expert_group and padra_exl3_schedule produce): one launch for the reference's three
+ * (src/cuda/inference.cu:3861, :3875, :3890).  tokens <= 2048.  ticket: one word of device memory, zero before the first
+ * call and left zero by every call (the CTA that finishes routing last does the scheduling). */
+PADRA_API int padra_route(const float *logits, int *ids, float *weights, int tokens, int *bad, padra_stream stream);
+PADRA_API int padra_route_group_schedule(const float *logits, int *ids, float *weights, int *groups, int *counts,
+                                         padra_tile *tiles, int *tile_count, int tokens, unsigned *ticket, int *bad,
+                                         padra_stream stream);
+/* padra_residual_norm: ResidualPostNormWideExact (src/cuda/residual_norm_wide_exact.cuh:84-131; call sites
+ * src/cuda/inference.cu:2913, :3358): per row x = B(x + residual), normalized = B(B(x * inv) * weight) with
+ * inv = 1 / sqrt(mean(x^2) + 1e-6) from the reference's compensated 128-thread sum.  weight: BF16 bits [hidden].
+ * residual may be NULL (x is normalised as it is).  statistics (may be NULL) receives [rows][2] = variance, inv.
+ * padra_combine_norm: combine_norm_exact::CombineNorm<false> (src/cuda/combine_norm_exact.cuh:7-68): the ordered BF16
+ * combine of the eight slots (down [rows][8][hidden], routing [rows][8]), the residual add into x and the same norm. */
+PADRA_API int padra_residual_norm(float *x, const float *residual, float *normalized, const unsigned short *weight,
+                                  int rows, int hidden, int *bad, float *statistics, padra_stream stream);
+PADRA_API int padra_combine_norm(float *x, const float *down, const float *routing, float *normalized,
+                                 const unsigned short *weight, int rows, int hidden, int *bad, float *statistics,
+                                 padra_stream stream);
+
 /* ---- small-batch projection (T < 4) -------------------------------------------------------------------
  * exl3_expert::Launch (src/cuda/expert_exl3.cuh:137-151): pairs = tokens*8, input row pair/8 (gate/up) or
- * pair (down), FP32-held BF16 in and out.  in_scratch / out_scratch are accepted and unused. */
+ * pair (down), FP32-held BF16 in and out.  in_scratch / out_scratch are accepted and unused.  The reference's two
+ * trailing parameters are not part of this signature: `bool fp32` (keep the transformed input unrounded, a diagnostic
+ * form) and `unsigned *ranges` (value statistics); the serving path passes neither (both default to off). */
 PADRA_API int padra_exl3_expert_launch(const padra_matrix *matrices, int layer, int part, const int *ids,
                                        const float *input, float *output, float *in_scratch, float *out_scratch,
                                        int tokens, int *bad, padra_stream stream, int rate, int hidden, int inter);

@@ -351,6 +351,108 @@ int exl3_combine(float *x, const float *down, const float *weights, int hidden) 
   return bad;
 }
 
+/* Merge of the 128 per-thread compensated sums: shuffle-down trees inside each of the four warps (every lane reads its
+ * partner's values from before the step), then over the four warp results.
+ * src/cuda/rms_wide_exact.cuh:3-33 (and AccurateReduce, src/cuda/inference.cu:110-134, which gives the same sum). */
+static float reduce_squares128(float *sum, float *err) {
+  float wsum[4], werr[4];
+  for (int w = 0; w < 4; ++w) {
+    float *s = sum + 32 * w, *e = err + 32 * w;
+    for (int d = 16; d; d /= 2) {
+      float os[32], oe[32];
+      for (int l = 0; l < 32; ++l) {
+        os[l] = l + d < 32 ? s[l + d] : s[l];
+        oe[l] = l + d < 32 ? e[l + d] : e[l];
+      }
+      for (int l = 0; l + d < 32; ++l) {
+        accumulate(os[l], &s[l], &e[l]);
+        accumulate(oe[l], &s[l], &e[l]);
+      }
+    }
+    wsum[w] = s[0];
+    werr[w] = e[0];
+  }
+  for (int d = 2; d; d /= 2) {
+    float os[4], oe[4];
+    for (int l = 0; l < 4; ++l) {
+      os[l] = l + d < 4 ? wsum[l + d] : wsum[l];
+      oe[l] = l + d < 4 ? werr[l + d] : werr[l];
+    }
+    for (int l = 0; l + d < 4; ++l) {
+      accumulate(os[l], &wsum[l], &werr[l]);
+      accumulate(oe[l], &wsum[l], &werr[l]);
+    }
+  }
+  return wsum[0] + werr[0];
+}
+
+static float bf16_bits_f32(uint16_t b) {
+  return bits_f32((uint32_t)b << 16);
+}
+
+/* x = B(x + residual) (residual may be NULL), normalized = B(B(x * inv) * weight), inv = 1 / sqrt(mean(x^2) + 1e-6) with
+ * thread t of 128 summing the squares of elements t, t+128, ... compensated.  One row of `hidden` elements.
+ * src/cuda/residual_norm_wide_exact.cuh:84-131.  stats (may be NULL) receives variance and inv. */
+int exl3_residual_norm(float *x, const float *residual, float *normalized, const uint16_t *weight, int hidden, float *stats) {
+  float sum[128], err[128];
+  int bad = 0;
+  for (int t = 0; t < 128; ++t) {
+    sum[t] = 0.f, err[t] = 0.f;
+    for (int i = t; i < hidden; i += 128) {
+      const float value = exl3_bf16_round(residual ? x[i] + residual[i] : x[i]);
+      x[i] = value;
+      if (!isfinite(value))
+        bad = 1;
+      accumulate(value * value, &sum[t], &err[t]);
+    }
+  }
+  const float total = reduce_squares128(sum, err);
+  if (!isfinite(total))
+    bad = 1;
+  const float variance = total / (float)hidden;
+  const float inv = 1.f / sqrtf(variance + 1e-6f);
+  if (stats)
+    stats[0] = variance, stats[1] = inv;
+  for (int i = 0; i < hidden; ++i) {
+    normalized[i] = exl3_bf16_round(exl3_bf16_round(x[i] * inv) * bf16_bits_f32(weight[i]));
+    if (!isfinite(normalized[i]))
+      bad = 1;
+  }
+  return bad;
+}
+
+/* The ordered BF16 combine of the eight slots, the residual add and the same norm in one pass, one row.
+ * down [8][hidden], routing [8].  src/cuda/combine_norm_exact.cuh:7-68 (EncodeFP8 = false). */
+int exl3_combine_norm(float *x, const float *down, const float *routing, float *normalized, const uint16_t *weight, int hidden,
+                      float *stats) {
+  float sum[128], err[128];
+  int bad = 0;
+  for (int t = 0; t < 128; ++t) {
+    sum[t] = 0.f, err[t] = 0.f;
+    for (int i = t; i < hidden; i += 128) {
+      float acc = 0.f;
+      for (int s = 0; s < 8; ++s)
+        acc = exl3_bf16_round(acc + exl3_bf16_round(down[(size_t)s * hidden + i] * routing[s]));
+      const float value = exl3_bf16_round(x[i] + acc);
+      x[i] = value;
+      if (!isfinite(value))
+        bad = 1;
+      accumulate(value * value, &sum[t], &err[t]);
+    }
+  }
+  const float total = reduce_squares128(sum, err);
+  const float variance = total / (float)hidden;
+  const float inv = 1.f / sqrtf(variance + 1e-6f);
+  if (stats)
+    stats[0] = variance, stats[1] = inv;
+  for (int i = 0; i < hidden; ++i) {
+    normalized[i] = exl3_bf16_round(exl3_bf16_round(x[i] * inv) * bf16_bits_f32(weight[i]));
+    if (!isfinite(normalized[i]))
+      bad = 1;
+  }
+  return bad;
+}
+
 /* Stable expert-major slot lists.  groups[e*tokens + n] = n-th (token*8+slot) that chose expert e.
  * src/cuda/expert_schedule.cuh:11-69 */
 int exl3_group(const int *ids, int *groups, int *counts, int tokens) {

@@ -65,6 +65,13 @@ int exl3_activate(float *gate, const float *up, int count);        /* inference.
 int exl3_route(const float *logits64, int *ids8, float *weights8); /* inference.cu:482-536 */
 int exl3_combine(float *x, const float *down, const float *weights, int hidden); /* inference.cu:580-594 */
 
+/* the norms either side of the experts: one row of `hidden` elements, weight = BF16 bits, stats (may be NULL) receives
+ * the variance and its inverse root */
+int exl3_residual_norm(float *x, const float *residual, float *normalized, const uint16_t *weight, int hidden,
+                       float *stats); /* residual_norm_wide_exact.cuh:84-131 */
+int exl3_combine_norm(float *x, const float *down, const float *routing, float *normalized, const uint16_t *weight,
+                      int hidden, float *stats); /* combine_norm_exact.cuh:7-68 */
+
 /* scheduling */
 int exl3_group(const int *ids, int *groups, int *counts, int tokens);          /* expert_schedule.cuh:11-69 */
 int exl3_schedule(const int *counts, int *tiles3, int *tile_count, int tokens);/* expert_exl3_prefill_masked.cuh:12-45 */

@@ -218,6 +218,12 @@ class COracle:
         L.exl3_moe_layer.argtypes = [C.POINTER(Matrix), C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_float),
                                      C.POINTER(C.c_float), C.c_int, C.c_int, C.c_int, C.c_int,
                                      C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.exl3_residual_norm.restype = C.c_int
+        L.exl3_residual_norm.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_void_p, C.c_int,
+                                         C.POINTER(C.c_float)]
+        L.exl3_combine_norm.restype = C.c_int
+        L.exl3_combine_norm.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float),
+                                        C.c_void_p, C.c_int, C.POINTER(C.c_float)]
         L.exl3_set_threads.argtypes = [C.c_int]
         L.exl3_get_threads.restype = C.c_int
 
@@ -279,6 +285,33 @@ class COracle:
         for t in range(tokens):
             bad |= self.lib.exl3_combine(_f32p(out[t]), _f32p(down[t]), _f32p(weights[t]), hidden)
         return out, bad
+
+    def residual_norm(self, x, residual, weight_bits):
+        """Rows of ResidualPostNormWideExact (src/cuda/residual_norm_wide_exact.cuh:84-131): returns (x, normalized,
+        stats[rows][2], bad); residual may be None; weight_bits are BF16 bit patterns [hidden]."""
+        out = np.array(x, dtype=np.float32, copy=True)
+        rows, hidden = out.shape
+        res = None if residual is None else np.ascontiguousarray(residual, dtype=np.float32).reshape(rows, hidden)
+        weight_bits = np.ascontiguousarray(weight_bits, dtype=np.uint16)
+        normalized, stats, bad = np.empty_like(out), np.empty((rows, 2), np.float32), 0
+        for r in range(rows):
+            bad |= self.lib.exl3_residual_norm(_f32p(out[r]), None if res is None else _f32p(res[r]), _f32p(normalized[r]),
+                                               weight_bits.ctypes.data, hidden, _f32p(stats[r]))
+        return out, normalized, stats, bad
+
+    def combine_norm(self, x, down, routing, weight_bits):
+        """Rows of combine_norm_exact::CombineNorm<false> (src/cuda/combine_norm_exact.cuh:7-68): x [rows][hidden],
+        down [rows][8][hidden], routing [rows][8]; returns (x, normalized, stats, bad)."""
+        out = np.array(x, dtype=np.float32, copy=True)
+        rows, hidden = out.shape
+        down = np.ascontiguousarray(down, dtype=np.float32).reshape(rows, 8, hidden)
+        routing = np.ascontiguousarray(routing, dtype=np.float32).reshape(rows, 8)
+        weight_bits = np.ascontiguousarray(weight_bits, dtype=np.uint16)
+        normalized, stats, bad = np.empty_like(out), np.empty((rows, 2), np.float32), 0
+        for r in range(rows):
+            bad |= self.lib.exl3_combine_norm(_f32p(out[r]), _f32p(down[r]), _f32p(routing[r]), _f32p(normalized[r]),
+                                              weight_bits.ctypes.data, hidden, _f32p(stats[r]))
+        return out, normalized, stats, bad
 
     def silu_table(self) -> np.ndarray:
         t = np.empty(65536, dtype=np.uint16)
@@ -365,6 +398,7 @@ class RefKernels:
             "ref_combine_packed": [p, p, p, i, p, i, p],
             "ref_route": [p, p, p, i, p, p],
             "ref_route_rank_exact": [p, p, p, i, p, p],
+            "ref_residual_post_norm": [p, p, p, p, p, p, i, p],
         }
         for name, args in sig.items():
             f = getattr(self.lib, name)

@@ -8,6 +8,7 @@
 #include "cuda/expert_exl3_decode_dual.cuh"
 #include "cuda/mtp_experts.cuh"
 #include "cuda/expert_schedule.cuh"
+#include "cuda/residual_norm_wide_exact.cuh"
 } // namespace
 } // namespace mellum16
 
@@ -190,5 +191,15 @@ REF_API int ref_route(const float *logits, int *ids, float *weights, int tokens,
 REF_API int ref_route_rank_exact(const float *logits, int *ids, float *weights, int tokens, int *bad,
                                  cudaStream_t stream) {
   RouteRankExact<<<tokens, 64, 0, stream>>>(logits, ids, weights, bad);
+  return Done();
+}
+
+// Residual add + post-attention RMS norm, src/cuda/residual_norm_wide_exact.cuh (the default profile's form), launched
+// as at src/cuda/inference.cu:2913 and :3358: rows 1..5 of 2304 elements, weight = 2304 BF16 values.
+REF_API int ref_residual_post_norm(float *x, const float *residual, float *normalized, const unsigned char *weight, int *bad,
+                                   float *statistics, int rows, cudaStream_t stream) {
+  DeviceMatrix w{};
+  w.data = weight, w.rows = 2304, w.cols = 1, w.format = 0;
+  ResidualPostNormWideExact<<<rows, 256, 0, stream>>>(x, residual, normalized, w, bad, statistics, rows);
   return Done();
 }

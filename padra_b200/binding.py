@@ -52,6 +52,10 @@ SIGNATURES = {
     "padra_exl3_moe_decode_layer": ([_p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, C.c_size_t, _p, _p], _i),
     "padra_exl3_decode_weights": ([_p, _p, _i, _i, _i, _p, _p], _i),
     "padra_exl3_decode_weights_tensor": ([_p, _p, _i, _i, _i, _p, _p], _i),
+    "padra_route": ([_p, _p, _p, _i, _p, _p], _i),
+    "padra_route_group_schedule": ([_p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p], _i),
+    "padra_residual_norm": ([_p, _p, _p, _p, _i, _i, _p, _p, _p], _i),
+    "padra_combine_norm": ([_p, _p, _p, _p, _p, _i, _i, _p, _p, _p], _i),
     "padra_codec_ceiling_launch": ([_i, _i, _i, _i, _p, _p], _i),
 }
 

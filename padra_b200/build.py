@@ -1,4 +1,5 @@
-"""Builds the CUDA library in-tree: padra_b200/libpadra_b200.so, sm_100a only.
+"""Builds the CUDA library in-tree (padra_b200/libpadra_b200.so, sm_100a only) and the C++ host tool above its C ABI
+(padra_b200/host/padra_host_tool, g++ -std=c++20).
 
 Run as `python -m padra_b200.build` (or call build()).  nvcc cross-compiles without a GPU."""
 from __future__ import annotations
@@ -11,7 +12,11 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libpadra_b200.so"
+HOST = HERE / "host"
+HOST_TOOL = HOST / "padra_host_tool"
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+CXX = os.environ.get("CXX", "g++")
+CUDA_HOME = Path(NVCC).resolve().parent.parent
 FLAGS = [
     "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
@@ -29,8 +34,21 @@ def stale() -> bool:
     return newest > LIB.stat().st_mtime
 
 
+def build_host_tool(force: bool = False) -> Path:
+    """The C++ host tool: artifact reader/writer/binder and one decode layer through the C ABI."""
+    sources_ = [HOST / "host_tool.cpp", HOST / "artifact.cpp"]
+    newest = max(p.stat().st_mtime for p in list(HOST.glob("*.?pp")) + [LIB, HERE.parent / "include" / "padra_b200.h"])
+    if not force and HOST_TOOL.exists() and HOST_TOOL.stat().st_mtime >= newest:
+        return HOST_TOOL
+    subprocess.check_call([CXX, "-std=c++20", "-O2", "-Wall", "-Wextra", f"-I{CUDA_HOME / 'include'}", *map(str, sources_), "-o",
+                           str(HOST_TOOL), f"-L{HERE}", "-lpadra_b200", f"-L{CUDA_HOME / 'lib64'}", "-lcudart",
+                           "-Wl,-rpath,$ORIGIN/..", f"-Wl,-rpath,{CUDA_HOME / 'lib64'}"])
+    return HOST_TOOL
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and not stale():
+        build_host_tool()
         return LIB
     objects = []
     build_dir = HERE / "build"
@@ -52,6 +70,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if failed:
         raise RuntimeError("nvcc failed")
     subprocess.check_call([NVCC, "-shared", "-o", str(LIB), *map(str, objects), "-lcudart"])
+    build_host_tool(force=True)
     return LIB
 
 

@@ -241,6 +241,25 @@ int padra_exl3_moe_decode_layer_launches(const padra_matrix *matrices, int layer
                            workspace_bytes, bad, S(stream), launches);
 }
 
+int padra_route(const float *logits, int *ids, float *weights, int tokens, int *bad, padra_stream stream) {
+  return LaunchRoute(logits, ids, weights, tokens, bad, S(stream));
+}
+
+int padra_route_group_schedule(const float *logits, int *ids, float *weights, int *groups, int *counts, padra_tile *tiles,
+                               int *tile_count, int tokens, unsigned *ticket, int *bad, padra_stream stream) {
+  return LaunchRouteGroupSchedule(logits, ids, weights, groups, counts, tiles, tile_count, tokens, ticket, bad, S(stream));
+}
+
+int padra_residual_norm(float *x, const float *residual, float *normalized, const unsigned short *weight, int rows, int hidden,
+                        int *bad, float *statistics, padra_stream stream) {
+  return LaunchResidualNorm(x, residual, normalized, weight, rows, hidden, bad, statistics, S(stream));
+}
+
+int padra_combine_norm(float *x, const float *down, const float *routing, float *normalized, const unsigned short *weight, int rows,
+                       int hidden, int *bad, float *statistics, padra_stream stream) {
+  return LaunchCombineNorm(x, down, routing, normalized, weight, rows, hidden, bad, statistics, S(stream));
+}
+
 int padra_codec_ceiling_launch(int rate, int form, int iterations, int blocks, unsigned *sink, padra_stream stream) {
   return LaunchCodecCeiling(rate, form, iterations, blocks, sink, S(stream));
 }

@@ -29,6 +29,13 @@ int InitDecodeLayerWorkspace(void *workspace, size_t bytes, cudaStream_t stream)
 int LaunchDecodeLayer(const Matrix *matrices, int layer, const int *ids, const float *routing, const float *normalized, float *x,
                       int tokens, int rate, int hidden, int inter, const unsigned short *table, void *workspace,
                       size_t workspace_bytes, int *bad, cudaStream_t stream, unsigned launches = 3u);
+int LaunchRoute(const float *logits, int *ids, float *weights, int tokens, int *bad, cudaStream_t stream);
+int LaunchRouteGroupSchedule(const float *logits, int *ids, float *weights, int *groups, int *counts, padra_tile *tiles, int *tile_count,
+                             int tokens, unsigned *ticket, int *bad, cudaStream_t stream);
+int LaunchResidualNorm(float *x, const float *residual, float *normalized, const unsigned short *weight, int rows, int hidden, int *bad,
+                       float *statistics, cudaStream_t stream);
+int LaunchCombineNorm(float *x, const float *down, const float *routing, float *normalized, const unsigned short *weight, int rows,
+                      int hidden, int *bad, float *statistics, cudaStream_t stream);
 int LaunchCodecCeiling(int rate, int form, int iterations, int blocks, unsigned *sink, cudaStream_t stream);
 int LaunchDecodeWeightsTensor(const Matrix *matrix, unsigned short *out, int rows, int cols, int rate, int *bad, cudaStream_t stream);
 int LaunchTileProjection(const Matrix *matrices, int layer, int part, const int *groups, const padra_tile *tiles,

@@ -51,12 +51,15 @@ class ExpertTable:
         self.total_bytes = layers * EXPERTS * self.expert_bytes
         self.arena = torch.empty(self.total_bytes, dtype=torch.uint8, device=self.device)
         self.descriptors = None  # device uint8 [layers*64*3*56]
+        self._bound = None  # (layer, expert, part) -> (packed, suh, svh) offsets when the arena is an artifact's payload
 
     def shape(self, part: int) -> tuple[int, int]:
         """(rows = outputs, cols = inputs) of part 0 gate, 1 up, 2 down."""
         return (self.hidden, self.inter) if part == 2 else (self.inter, self.hidden)
 
     def offsets(self, layer: int, expert: int, part: int) -> tuple[int, int, int]:
+        if self._bound is not None:
+            return self._bound[layer, expert, part]
         base = (layer * EXPERTS + expert) * self.expert_bytes
         p, s, v = self.region[part]
         return base + p, base + s, base + v
@@ -64,6 +67,51 @@ class ExpertTable:
     def algorithmic_bytes_per_expert(self) -> int:
         """Packed words of the three matrices plus their FP16 sidecars."""
         return 3 * self.packed_bytes + 2 * 2 * (self.hidden + self.inter) + 2 * (self.inter + self.hidden)
+
+    # ---- artifacts (manifest.json + weights.bin; src/model/compiled.cpp:91-216) --------------------------------
+    def save_artifact(self, directory) -> None:
+        """Writes the table's tensors as an artifact directory.  The arena already has the artifact's canonical layout
+        (per matrix packed | suh | svh, each region on a 256-byte boundary), so the payload is the arena's bytes."""
+        from . import artifact
+
+        def tensors():
+            for layer in range(self.layers):
+                for e in range(EXPERTS):
+                    for part in range(3):
+                        rows, cols = self.shape(part)
+                        yield (artifact.expert_tensor_name(layer, e, part), rows, cols, *self.host_matrix(layer, e, part))
+
+        artifact.write(directory, self.rate, tensors())
+
+    @classmethod
+    def from_artifact(cls, directory, device="cuda", verify_payload: bool = True) -> "ExpertTable":
+        """Uploads an artifact's payload as the arena and binds the descriptor table to its regions, wherever the
+        manifest puts them (the binder of src/cuda/device_matrix.cuh:14-66)."""
+        from . import artifact
+
+        art = artifact.load(directory, verify_payload=verify_payload)
+        gate = art.tensors[artifact.expert_tensor_name(0, 0, 0)]
+        table = cls.__new__(cls)
+        table.layers, table.hidden, table.inter, table.rate = art.layers, gate.cols, gate.rows, art.rate
+        table.device = torch.device(device)
+        table.packed_bytes = table.hidden * table.inter * table.rate // 8
+        table.region, table.expert_bytes, table.total_bytes = None, None, art.weights_bytes
+        table.arena = torch.from_numpy(art.payload()).to(table.device)
+        table._bound = {}
+        d = np.zeros(art.layers * EXPERTS * 3, dtype=DESCRIPTOR)
+        base = table.arena.data_ptr()
+        for layer in range(art.layers):
+            for e in range(EXPERTS):
+                for part in range(3):
+                    t = art.tensors[artifact.expert_tensor_name(layer, e, part)]
+                    assert (t.rows, t.cols) == table.shape(part), "artifact mixes expert shapes"
+                    table._bound[layer, e, part] = (t.packed[0], t.suh[0], t.svh[0])
+                    row = d[(layer * EXPERTS + e) * 3 + part]
+                    row["data"], row["suh"], row["svh"] = base + t.packed[0], base + t.suh[0], base + t.svh[0]
+                    row["rows"], row["cols"], row["format"] = t.rows, t.cols, B.FORMAT_OF_RATE[art.rate]
+        table.host_descriptors = d
+        table.descriptors = torch.from_numpy(d.view(np.uint8).copy()).to(table.device)
+        return table
 
     def finalize(self) -> "ExpertTable":
         """(Re)builds the device descriptor table from the arena address."""
@@ -219,6 +267,41 @@ class ExpertKernels:
         B.check(self.lib.padra_exl3_schedule(B.ptr(counts), B.ptr(tiles), B.ptr(tile_count), tokens, B.ptr(self.bad),
                                              B.stream_handle(stream)), "padra_exl3_schedule")
         return groups, counts, tiles, tile_count
+
+    # RouteRankExact, and the same fused with Group + Schedule
+    def route(self, logits, stream=None):
+        tokens = logits.shape[0]
+        ids = torch.empty((tokens, TOPK), dtype=torch.int32, device=self.t.device)
+        weights = torch.empty((tokens, TOPK), dtype=torch.float32, device=self.t.device)
+        B.check(self.lib.padra_route(B.ptr(logits), B.ptr(ids), B.ptr(weights), tokens, B.ptr(self.bad), B.stream_handle(stream)),
+                "padra_route")
+        return ids, weights
+
+    def route_group_schedule(self, logits, stream=None):
+        dev, tokens = self.t.device, logits.shape[0]
+        ids = torch.empty((tokens, TOPK), dtype=torch.int32, device=dev)
+        weights = torch.empty((tokens, TOPK), dtype=torch.float32, device=dev)
+        groups = torch.full((EXPERTS * tokens,), -1, dtype=torch.int32, device=dev)
+        counts = torch.zeros(EXPERTS, dtype=torch.int32, device=dev)
+        tiles = torch.zeros(((tokens * TOPK + 31) // 32 + EXPERTS, 3), dtype=torch.int32, device=dev)
+        tile_count = torch.zeros(1, dtype=torch.int32, device=dev)
+        if getattr(self, "_ticket", None) is None:
+            self._ticket = torch.zeros(1, dtype=torch.int32, device=dev)
+        B.check(self.lib.padra_route_group_schedule(B.ptr(logits), B.ptr(ids), B.ptr(weights), B.ptr(groups), B.ptr(counts), B.ptr(tiles),
+                                                    B.ptr(tile_count), tokens, B.ptr(self._ticket), B.ptr(self.bad),
+                                                    B.stream_handle(stream)), "padra_route_group_schedule")
+        return ids, weights, (groups, counts, tiles, tile_count)
+
+    # ResidualPostNormWideExact / combine_norm_exact::CombineNorm
+    def residual_norm(self, x, residual, normalized, weight_bits, statistics=None, stream=None):
+        rows, hidden = x.shape
+        B.check(self.lib.padra_residual_norm(B.ptr(x), B.ptr(residual), B.ptr(normalized), B.ptr(weight_bits), rows, hidden,
+                                             B.ptr(self.bad), B.ptr(statistics), B.stream_handle(stream)), "padra_residual_norm")
+
+    def combine_norm(self, x, down, routing, normalized, weight_bits, statistics=None, stream=None):
+        rows, hidden = x.shape
+        B.check(self.lib.padra_combine_norm(B.ptr(x), B.ptr(down), B.ptr(routing), B.ptr(normalized), B.ptr(weight_bits), rows, hidden,
+                                            B.ptr(self.bad), B.ptr(statistics), B.stream_handle(stream)), "padra_combine_norm")
 
     # exl3_transport_async64::Launch / exl3_packed_activations::Launch
     def prefill_launch(self, layer, part, ids, sched, x, output_bits, gate_bits, up_bits, transformed, tokens, stream=None,

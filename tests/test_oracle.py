@@ -170,3 +170,31 @@ def test_moe_layer_small(oracle):
     out16, bad16 = oracle.moe_layer(host.table, 0, ids, w, x, 256, 128, f16_form=True)
     assert not bad16
     assert np.abs(out - out16).max() <= 1e-2 * np.abs(out).max()
+
+
+def test_norm_restatements_against_float64(oracle):
+    """The compensated RMS norms of the oracle against a float64 evaluation of the same formulas: the variance and the
+    inverse root to FP32 rounding, x exactly, normalized within one BF16 step per rounding (two roundings)."""
+    rng = np.random.default_rng(5)
+    hidden, rows = 2304, 3
+    x = O.bf16_round((3.0 * rng.standard_normal((rows, hidden))).astype(np.float32))
+    residual = O.bf16_round(rng.standard_normal((rows, hidden)).astype(np.float32))
+    wb = (O.bf16_round((1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32)).view(np.uint32) >> 16).astype(np.uint16)
+    weight = (wb.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    got_x, got_n, stats, bad = oracle.residual_norm(x, residual, wb)
+    assert not bad
+    want_x = O.bf16_round((x.astype(np.float64) + residual).astype(np.float32))
+    assert np.array_equal(got_x, want_x)
+    variance = (want_x.astype(np.float64) ** 2).mean(axis=1)
+    inv = 1.0 / np.sqrt(variance + 1e-6)
+    assert np.allclose(stats[:, 0], variance, rtol=3e-7) and np.allclose(stats[:, 1], inv, rtol=3e-7)
+    want_n = want_x.astype(np.float64) * inv[:, None] * weight
+    assert np.allclose(got_n, want_n, rtol=2 ** -7, atol=1e-30)
+    # the fused combine + norm equals combine followed by the norm without a residual
+    down = O.bf16_round((4.0 * rng.standard_normal((rows, 8, hidden))).astype(np.float32))
+    routing = O.bf16_round(np.full((rows, 8), 0.125, dtype=np.float32))
+    fused_x, fused_n, fused_s, bad = oracle.combine_norm(x, down, routing, wb)
+    step_x, bad2 = oracle.combine(x, down, routing)
+    step_x, step_n, step_s, bad3 = oracle.residual_norm(step_x, None, wb)
+    assert not (bad or bad2 or bad3)
+    assert np.array_equal(fused_x, step_x) and np.array_equal(fused_n, step_n) and np.array_equal(fused_s, step_s)
