@@ -273,7 +273,7 @@ PADRA_API int padra_exl3_moe_decode_layer_launches(const padra_matrix *matrices,
  * other allocating routine.
  *   - Shapes whose workspace (padra_exl3_moe_decode_workspace_bytes) exceeds the array are refused with
  *     PADRA_RESOURCE_EXHAUSTED and nothing is enqueued.  Hidden 2048 / intermediate 1024 and 2304 / 896 fit at every
- *     batch (1..16 tokens); hidden 4096 / intermediate 2048 fits up to 11 tokens.
+ *     batch (1..16 tokens); hidden 4096 / intermediate 2048 fits up to 9 tokens.
  *   - There is one array per device (256-byte aligned) and every call shares it: calls that may overlap on the GPU
  *     race on it and then give wrong results without any error, so the caller orders them (one stream, or events).
  *     The array keeps the last call's contents.  Only the ticket counters at its start have to be zero; the module

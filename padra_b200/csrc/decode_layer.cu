@@ -27,41 +27,17 @@
 // clears the counter, so every call leaves them zero.  No CTA ever waits for another one.
 #include <cstdlib>
 
-#include "codec.cuh"
-#include "common.cuh"
-#include "kernels.cuh"
+#include "decode_common.cuh"
 
 namespace padra {
+#ifdef PADRA_DECODE_TRACE
+namespace decode {
+unsigned long long *g_trace = nullptr;
+int g_trace_launch = 0;
+} // namespace decode
+#endif
 namespace {
-
-constexpr int kThreads = 256;
-constexpr int kMaxSlices = 8;
-constexpr int kMaxBlocks = 64; // 128-wide blocks per dimension the ticket area provides for
-
-__device__ __forceinline__ void MmaF16(const uint32_t (&a)[4], uint32_t b0, uint32_t b1, float (&d)[4]) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void Unpack4(uint2 bits, float (&f)[4]) {
-  f[0] = HalfBitsToFloat(bits.x & 0xffffu);
-  f[1] = HalfBitsToFloat(bits.x >> 16);
-  f[2] = HalfBitsToFloat(bits.y & 0xffffu);
-  f[3] = HalfBitsToFloat(bits.y >> 16);
-}
-__device__ __forceinline__ void LetSuccessorLaunch() {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-}
-__device__ __forceinline__ void WaitForPredecessor() {
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-}
-// A hint: fetch `bytes` (a multiple of 16, from a 16-byte aligned address) into L2.  Nothing waits for it.
-__device__ __forceinline__ void PrefetchL2(const void *p, unsigned bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ int LoadFlag(const int *p) { // never from a stale L1 line
-  return __ldcg(p);
-}
+using namespace decode;
 
 struct LayerArgs {
   const Matrix *matrices;
@@ -78,30 +54,9 @@ struct LayerArgs {
   unsigned *tickets;           // gate+up: [unit][kMaxBlocks]; down: [token][kMaxBlocks]
   int *bad;
   int debug; // temporary switches
-#ifdef PADRA_DECODE_TRACE
-  unsigned long long *trace;
-#endif
+  unsigned long long *trace; // scratch builds only
 };
-#ifdef PADRA_DECODE_TRACE
-unsigned long long *g_trace = nullptr;
-int g_trace_launch = 0;
-#define TRACE(slot)                                                                                                        \
-  do {                                                                                                                     \
-    if (a.trace && threadIdx.x == 0) {                                                                                     \
-      unsigned long long now;                                                                                              \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));                                                              \
-      a.trace[((static_cast<size_t>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (slot)] = now; \
-    }                                                                                                                      \
-  } while (0)
-#else
-#define TRACE(slot)
-#endif
 
-// Place of element k of a row (k counted from the start of the row or slice) in the order the B fragments are read:
-// inside every K16 step, input i sits at codec::PermutedInput(i).
-__device__ __forceinline__ int PermutedPlace(int k) {
-  return (k & ~15) + codec::PermutedInput(k & 15);
-}
 
 // Unit `unit` of the launch.  One token: the unit is the slot, and it takes part (count = 1) even when its id is
 // invalid, because the token's combine counts on eight arrivals.  Several tokens: the unit-th active expert in ascending
@@ -285,16 +240,16 @@ __global__ void __launch_bounds__(kThreads, 4) LayerProjectionKernel(LayerArgs a
   __shared__ __align__(16) float s_down[Phase ? kTopK : 1][128];
   __shared__ unsigned s_done;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  TRACE(0);
+  PADRA_TRACE(a.trace, 0);
   // Gate+up: the ids, activations and the error flag are the work of whatever ran before this call, so it waits first,
   // and lets the down kernel start only then: the down kernel reads the ids before its own wait.
   if (Phase == 0)
     WaitForPredecessor();
   LetSuccessorLaunch();
-  TRACE(1);
+  PADRA_TRACE(a.trace, 1);
   int expert, count, rows[8 * NG];
   ResolveUnit<NG>(a.ids, a.tokens, blockIdx.y, expert, count, rows, a.bad);
-  TRACE(2);
+  PADRA_TRACE(a.trace, 2);
   if (count == 0)
     return; // the same in every CTA of the unit: nobody takes this unit's tickets
   const int part = Phase ? 2 : static_cast<int>(blockIdx.z) / a.slices;
@@ -313,7 +268,7 @@ __global__ void __launch_bounds__(kThreads, 4) LayerProjectionKernel(LayerArgs a
       work = false;
     }
   }
-  TRACE(3);
+  PADRA_TRACE(a.trace, 3);
   const int cols = Phase ? a.inter : a.hidden;
   const int span = cols / a.slices, k_begin = slice * span; // inputs of this slice, a multiple of 128
   const int stride = span + 8;
@@ -355,12 +310,12 @@ __global__ void __launch_bounds__(kThreads, 4) LayerProjectionKernel(LayerArgs a
       svh_bits = __ldg(reinterpret_cast<const uint2 *>(m.svh + base + lane * 4));
     }
   }
-  TRACE(4);
+  PADRA_TRACE(a.trace, 4);
   if (Phase == 1)
     WaitForPredecessor(); // from here on: what the gate+up kernel wrote, and this kernel's own stores
   if (__syncthreads_or(LoadFlag(a.bad)))
     work = false; // refused or failed earlier: no work, but the tickets are still taken (one verdict for the whole CTA)
-  TRACE(5);
+  PADRA_TRACE(a.trace, 5);
 
   if (work) { // uniform over the CTA
     // ---- activation rows of the slice, in the order the B fragments are read ----
@@ -392,12 +347,12 @@ __global__ void __launch_bounds__(kThreads, 4) LayerProjectionKernel(LayerArgs a
       }
     }
     __syncthreads();
-    TRACE(6);
+    PADRA_TRACE(a.trace, 6);
 #ifdef PADRA_DECODE_TRACE
     {
       unsigned probe = fetched[0][0] ^ 1u;
       asm volatile("mov.u32 %0, %0;" : "+r"(probe));
-      TRACE(7);
+      PADRA_TRACE(a.trace, 7);
     }
 #endif
 
@@ -448,7 +403,7 @@ __global__ void __launch_bounds__(kThreads, 4) LayerProjectionKernel(LayerArgs a
         }
       }
     }
-    TRACE(8);
+    PADRA_TRACE(a.trace, 8);
     // accumulator (row g | g+8, column 2t | 2t+1) -> this slice's sums of the warp's 16 outputs
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng)
@@ -472,7 +427,7 @@ __global__ void __launch_bounds__(kThreads, 4) LayerProjectionKernel(LayerArgs a
     s_done = 0;
   __threadfence();
   __syncthreads();
-  TRACE(9);
+  PADRA_TRACE(a.trace, 9);
   if (Phase == 0) {
     unsigned *ticket = a.tickets + static_cast<size_t>(blockIdx.y) * kMaxBlocks + nb;
     if (tid == 0 && atomicAdd(ticket, 1u) == 2u * a.slices - 1u) {
@@ -487,7 +442,7 @@ __global__ void __launch_bounds__(kThreads, 4) LayerProjectionKernel(LayerArgs a
     }
   }
   __syncthreads();
-  TRACE(10);
+  PADRA_TRACE(a.trace, 10);
   const unsigned done = s_done;
   if (!done)
     return;
@@ -510,58 +465,7 @@ __global__ void __launch_bounds__(kThreads, 4) LayerProjectionKernel(LayerArgs a
       if (done & (1u << n))
         DownEpilogue(a, rows[n] >> 3, nb, s_down);
   }
-  TRACE(11);
-}
-
-// K-slices: enough CTAs to fill the machine several deep, slices of whole 128-input blocks.
-int SliceOverride() {
-  static const int value = [] {
-    const char *text = std::getenv("PADRA_DECODE_SLICES");
-    return text ? std::atoi(text) : 0;
-  }();
-  return value;
-}
-int PickSlices(int cols, int base_ctas) {
-  int slices = SliceOverride() > 0 ? SliceOverride() : 4;
-  if (slices > kMaxSlices)
-    slices = kMaxSlices;
-  while (slices > 1 && ((cols / 128) % slices != 0 || base_ctas * slices > 1024))
-    slices /= 2;
-  return slices;
-}
-
-struct LayerWorkspace {
-  size_t tickets_gateup, tickets_down, gateup, xdown, down, svh, total;
-  int slices_gateup, slices_down;
-  LayerWorkspace(int tokens, int hidden, int inter) {
-    const size_t pairs = static_cast<size_t>(tokens) * kTopK;
-    const int units = pairs < kExperts ? static_cast<int>(pairs) : kExperts;
-    slices_gateup = PickSlices(hidden, (inter / 128) * units * 2);
-    slices_down = PickSlices(inter, (hidden / 128) * units);
-    auto align = [](size_t n) { return (n + 255) & ~static_cast<size_t>(255); };
-    size_t at = 0;
-    // the ticket area has one size for every shape, so that a workspace (or the built-in array) that serves calls of
-    // different shapes never has one shape's partial sums where another shape keeps its counters
-    tickets_gateup = at, at += align(static_cast<size_t>(kExperts) * kMaxBlocks * sizeof(unsigned));
-    tickets_down = at, at += align(static_cast<size_t>(kMaxDecodeRows) * kMaxBlocks * sizeof(unsigned));
-    gateup = at, at += align(pairs * 2 * slices_gateup * inter * sizeof(float));
-    xdown = at, at += align(pairs * inter * sizeof(__half));
-    down = at, at += align(pairs * slices_down * hidden * sizeof(float));
-    svh = at, at += align(pairs * hidden * sizeof(__half));
-    total = at;
-  }
-};
-
-template <typename... KernelArgs, typename... Args>
-int LaunchProgrammatic(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
-  static const int allowed = std::getenv("PADRA_DECODE_NO_OVERLAP") ? 0 : 1;
-  cudaLaunchAttribute attribute{};
-  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute.val.programmaticStreamSerializationAllowed = allowed;
-  cudaLaunchConfig_t config{};
-  config.gridDim = grid, config.blockDim = block, config.dynamicSmemBytes = smem, config.stream = stream;
-  config.attrs = &attribute, config.numAttrs = 1;
-  return CudaStatus(cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...));
+  PADRA_TRACE(a.trace, 11);
 }
 
 template <int Rate, int NG, int Phase> int LaunchLayerKernel(const LayerArgs &a, dim3 grid, size_t smem, cudaStream_t stream) {
@@ -604,6 +508,10 @@ int LaunchDecodeLayer(const Matrix *matrices, int layer, const int *ids, const f
   const LayerWorkspace w(tokens, hidden, inter);
   if (workspace_bytes < w.total)
     return PADRA_RESOURCE_EXHAUSTED;
+  static const bool general_only = std::getenv("PADRA_DECODE_GENERAL") != nullptr; // scratch switch: compare the two forms
+  if (tokens == 1 && !general_only)
+    return LaunchSingleTokenLayer(matrices, layer, ids, routing, normalized, x, rate, hidden, inter, table, workspace, bad, stream,
+                                  launches);
   auto *base = static_cast<unsigned char *>(workspace);
   const int pairs = tokens * kTopK, units = pairs < kExperts ? pairs : kExperts;
   const bool wide = tokens > 8;

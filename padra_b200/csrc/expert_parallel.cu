@@ -466,6 +466,14 @@ bool FillPeers(PeerBlocks &peers, const unsigned long long *bases, int world) {
 
 } // namespace
 
+// SMs of the current device (asked every time: a process may drive several devices).
+static int SmCount() {
+  int device = 0, sms = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 1)
+    return 132; // a floor that any part this library runs on exceeds
+  return sms;
+}
+
 size_t ExchangeBytes(int world, int cap, int hidden, size_t *offsets) {
   if (world < 1 || world > kMaxRanks || cap < 8 || cap > 2048 * kTopK || hidden < 128 || (hidden % 128))
     return 0;
@@ -484,7 +492,7 @@ int LaunchDispatch(const float *activations, const int *order, const int *send_i
       reinterpret_cast<uintptr_t>(activations) % 16)
     return PADRA_INVALID_ARGUMENT;
   const int blocks = (pairs + 7) / 8;
-  DispatchKernel<<<blocks < 148 * 4 ? blocks : 148 * 4, 256, 0, stream>>>(activations, order, send_ids, send_counts, peers,
+  DispatchKernel<<<blocks < SmCount() * 4 ? blocks : SmCount() * 4, 256, 0, stream>>>(activations, order, send_ids, send_counts, peers,
                                                                           MakeExchangeLayout(world, cap, hidden), rank, world, cap, pairs,
                                                                           hidden, epoch, bad);
   return CudaStatus(cudaGetLastError());
@@ -519,7 +527,7 @@ int LaunchReturn(const unsigned short *down, const unsigned long long *bases, in
       !FillPeers(peers, bases, world) || reinterpret_cast<uintptr_t>(down) % 16 || column_begin < 0 || column_count < 8 ||
       (column_begin % 8) || (column_count % 8) || column_begin + column_count > hidden)
     return PADRA_INVALID_ARGUMENT;
-  ReturnKernel<<<148 * 4, 256, 0, stream>>>(down, peers, MakeExchangeLayout(world, cap, hidden), rank, world, cap, hidden, epoch, bad,
+  ReturnKernel<<<SmCount() * 4, 256, 0, stream>>>(down, peers, MakeExchangeLayout(world, cap, hidden), rank, world, cap, hidden, epoch, bad,
                                             column_begin, column_count, announce);
   return CudaStatus(cudaGetLastError());
 }
@@ -546,7 +554,7 @@ int LaunchPackRows(const float *activations, const int *order, unsigned short *p
       reinterpret_cast<uintptr_t>(activations) % 16 || reinterpret_cast<uintptr_t>(packed) % 8)
     return PADRA_INVALID_ARGUMENT;
   const int blocks = (rows + 7) / 8;
-  PackRowsKernel<<<blocks < 148 * 16 ? blocks : 148 * 16, 256, 0, stream>>>(activations, order, packed, rows, hidden, bad);
+  PackRowsKernel<<<blocks < SmCount() * 16 ? blocks : SmCount() * 16, 256, 0, stream>>>(activations, order, packed, rows, hidden, bad);
   return CudaStatus(cudaGetLastError());
 }
 

@@ -118,7 +118,7 @@ def test_residual_norm_equals_oracle(oracle, gpu, hidden, rows, with_residual):
 
 @pytest.mark.parametrize("hidden,rows", [(2048, 1), (2304, 4)])
 def test_combine_norm_equals_oracle_and_the_two_step_form(oracle, gpu, hidden, rows):
-    _, _, k = make(1, 256, 128, 4, 811, gpu)
+    _, _, k = make(1, hidden, 128, 4, 811, gpu)  # the combine wrapper takes the row length from its table
     rng = np.random.default_rng(hidden)
     x = O.bf16_round(rng.standard_normal((rows, hidden)).astype(np.float32))
     down = O.bf16_round((4.0 * rng.standard_normal((rows, 8, hidden))).astype(np.float32))

@@ -43,7 +43,7 @@ def test_static_scratch_layer_equals_workspace_layer_twice(oracle, gpu, rate, to
 
 def test_static_scratch_size_limit(oracle, gpu):
     """The benchmark shape (hidden 2048 / intermediate 1024) fits the 4 MiB array at every batch up to sixteen tokens; at
-    hidden 4096 / intermediate 2048 eleven tokens fit and twelve do not.  The largest batch that fits is run and compared,
+    hidden 4096 / intermediate 2048 nine tokens fit and ten do not.  The largest batch that fits is run and compared,
     the first one that does not fit is refused without touching anything."""
     from padra_b200 import binding as B
     from padra_b200.experts import ExpertKernels, ExpertTable
@@ -53,23 +53,23 @@ def test_static_scratch_size_limit(oracle, gpu):
     assert lib.padra_exl3_moe_decode_workspace_bytes(16, 2048, 1024) <= limit
     assert lib.padra_exl3_moe_decode_workspace_bytes(16, 2304, 896) <= limit
     hidden, inter = 4096, 2048
-    assert lib.padra_exl3_moe_decode_workspace_bytes(11, hidden, inter) <= limit
-    assert lib.padra_exl3_moe_decode_workspace_bytes(12, hidden, inter) > limit
+    assert lib.padra_exl3_moe_decode_workspace_bytes(9, hidden, inter) <= limit
+    assert lib.padra_exl3_moe_decode_workspace_bytes(10, hidden, inter) > limit
     table = ExpertTable(1, hidden, inter, 4, gpu).fill_random(2)
     k = ExpertKernels(table)
-    x, ids, w = routed_inputs(oracle, 12, hidden, 500)
+    x, ids, w = routed_inputs(oracle, 10, hidden, 500)
     dids = torch.from_numpy(ids.reshape(-1)).to(gpu)
     dw = torch.from_numpy(w.reshape(-1)).to(gpu)
     dx = torch.from_numpy(x).to(gpu)
-    fits = dx[:11].contiguous()
+    fits = dx[:9].contiguous()
     want, got = fits.clone(), fits.clone()
-    k.moe_decode_layer(0, dids[:88], dw[:88], fits, want, 11)
-    k.moe_decode_layer_static(0, dids[:88], dw[:88], fits, got, 11)
+    k.moe_decode_layer(0, dids[:72], dw[:72], fits, want, 9)
+    k.moe_decode_layer_static(0, dids[:72], dw[:72], fits, got, 9)
     torch.cuda.synchronize()
     assert k.bad_flag() == 0 and torch.equal(got, want) and not torch.equal(got, fits)
     refused = dx.clone()
     st = lib.padra_exl3_moe_decode_layer_static(table.descriptors.data_ptr(), 0, dids.data_ptr(), dw.data_ptr(), dx.data_ptr(),
-                                                refused.data_ptr(), 12, 4, hidden, inter, k.table.data_ptr(), k.bad.data_ptr(), None)
+                                                refused.data_ptr(), 10, 4, hidden, inter, k.table.data_ptr(), k.bad.data_ptr(), None)
     assert st == B.RESOURCE_EXHAUSTED
     torch.cuda.synchronize()
     assert torch.equal(refused, dx), "a refused call must not touch the residual stream"
