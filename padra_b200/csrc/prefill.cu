@@ -13,7 +13,10 @@
 //     shared-memory layout: with the lane <-> (row pair, K-step) ownership of the codec the four 16-byte stores of a
 //     quarter-warp are 128 contiguous bytes.
 //   * the tokens are the M side: the expert's transformed activation rows (FP16, written in expert-grouped order by
-//     PrefillInputKernel), copied with cp.async into the same canonical layout, one tile of up to 128 rows.
+//     PrefillInputKernel).  One elected producer thread fetches a stage's 128 rows x 64 inputs with ONE tensor copy
+//     (cp.async.bulk.tensor, 128-byte swizzle, completion counted in bytes on the stage's barrier); the sixteen decoding
+//     warps never touch the activations.  (Gathering them with 16-byte cp.async from those warps cost them three times
+//     as many cycles per stage as the decode itself.)
 //   * one elected thread issues tcgen05.mma (M = 128 tokens, N = 256 outputs, K = 16), four per stage, and commits each
 //     stage back to the producers; a 4-stage ring of (32 KB weights + 16 KB activations) that runs on across items.
 //   * a thread of the four epilogue warps owns one TOKEN row of the accumulator, so the 128-point output Hadamard of
@@ -24,6 +27,8 @@
 //     producers and the MMA thread already work on item i+1.
 // Every wait on an mbarrier is bounded in time: on expiry the CTA raises the sticky error flag, skips the rest of
 // its work, frees its tensor memory and leaves.
+#include <cuda.h>
+
 #include "codec.cuh"
 #include "common.cuh"
 #include "exchange.cuh"
@@ -38,14 +43,14 @@ constexpr int kTileM = 128;    // outputs per item (the MMA's N), and token rows
 constexpr int kMaxTileN = 128; // tokens per item (one MMA token tile)
 constexpr int kItemBlocks = 2; // 128-output blocks per item: 256 accumulator columns
 constexpr int kStageABytes = kItemBlocks * kTileM * kStageK * 2; // 32 KB of decoded weights
-// B stage: eight 16-byte K pieces per row; consecutive pieces are (tile_n*16 + 16) bytes apart -- the extra 16 bytes
-// put the eight pieces of one row on eight different bank groups, so the coalesced copy (eight lanes per row) is
-// free of bank conflicts.
-constexpr int kStageBBytes = 8 * (kMaxTileN * 16 + 16) + 896; // 32 KB + padding, kept a multiple of 1 KB
+// Activation stage: 128 token rows of 128 bytes (64 inputs), 128-byte swizzle: what one tensor copy delivers and what
+// the MMA's operand descriptor (layout SWIZZLE_128B, 1024 bytes per eight-row group) reads.
+constexpr int kStageBBytes = kMaxTileN * kStageK * 2; // 16 KB
 constexpr int kEpilogueWarps = 4, kProducerSets = 2, kWarpsPerSet = 8; // set b decodes output block b of the item
 constexpr int kMmaWarp = kEpilogueWarps;
 constexpr int kFirstProducerWarp = kMmaWarp + 1;
-constexpr int kPrefillThreads = (kEpilogueWarps + 1 + kProducerSets * kWarpsPerSet) * 32; // 672
+constexpr int kCopyWarp = kFirstProducerWarp + kProducerSets * kWarpsPerSet; // one thread of it fetches the activation tiles
+constexpr int kPrefillThreads = (kCopyWarp + 1) * 32; // 704
 constexpr int kTmemColumns = 512;                   // two accumulators of 256 columns (128 tokens x 256 outputs)
 constexpr int kBufferColumns = 256;
 constexpr int kMaxPairs = 4096 * kTopK;              // grouped pairs (rows) one call works on
@@ -55,13 +60,28 @@ constexpr int kAhead = 3;                           // own stages of packed word
 constexpr unsigned long long kWaitLimitNs = 1000000000ull; // a wait that lasts a second has failed
 constexpr int kMaxTokensPrefill = 2048;
 
+#ifdef PADRA_PREFILL_TRACE
+__device__ unsigned long long *g_prefill_trace = nullptr; // [stage record][8], CTA 0 only
+#define PF_TRACE(record, slot)                                                     \
+  do {                                                                             \
+    if (g_prefill_trace && blockIdx.x == 0 && (record) < 8192) {                   \
+      g_prefill_trace[static_cast<size_t>(record) * 8 + (slot)] = clock64();       \
+    }                                                                              \
+  } while (0)
+__device__ int g_prefill_variant = 0; // timing experiments: 1 no decode, 2 no weight stores, 4 no activation copies, 8 no MMAs
+#define PF_VARIANT(bit) (g_prefill_variant & (bit))
+#else
+#define PF_TRACE(record, slot)
+#define PF_VARIANT(bit) 0
+#endif
+
 struct TileInfo {
   int expert, valid, row_base, begin; // begin = index of the tile's first pair inside the expert's group
 };
 
 struct PrefillSmem {
-  alignas(128) unsigned char a[kStages][kStageABytes];
-  alignas(128) unsigned char b[kStages][kStageBBytes];
+  alignas(1024) unsigned char b[kStages][kStageBBytes]; // swizzled tiles want 1024-byte alignment
+  alignas(1024) unsigned char a[kStages][kStageABytes];
   alignas(16) float scale[2][kItemBlocks * kTileM]; // svh of the item being drained / the next one
   alignas(8) unsigned long long full[kStages], empty[kStages], accumulator_ready[2], accumulator_free[2];
   TileInfo tile[kMaxTiles], unsorted[kMaxTiles];
@@ -136,6 +156,23 @@ __device__ __forceinline__ unsigned long long OperandDescriptor(unsigned smem_ad
   // [32,46) stride>>4, [46,48) descriptor version 1 (sm_100), [61,64) layout 0 = no swizzle.
   return static_cast<unsigned long long>((smem_address & 0x3ffffu) >> 4) | (static_cast<unsigned long long>(leading_bytes >> 4) << 16) |
          (static_cast<unsigned long long>(stride_bytes >> 4) << 32) | (1ull << 46);
+}
+// K-major with 128-byte swizzle: rows of 128 bytes, eight-row groups 1024 bytes apart; a K16 step inside the 64-input row
+// is selected by moving the start address 32 bytes on.  Bits as above; layout 2 = SWIZZLE_128B, leading offset unused.
+__device__ __forceinline__ unsigned long long SwizzledOperandDescriptor(unsigned smem_address) {
+  return static_cast<unsigned long long>((smem_address & 0x3ffffu) >> 4) | (1ull << 16) | (static_cast<unsigned long long>(1024 >> 4) << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+// One tile of the 2-D tensor behind `map` (inner coordinate x in elements, a multiple of 8; outer coordinate y) into
+// shared memory; its bytes are counted on `bar`.  The CTA is the only reader of the tile.
+__device__ __forceinline__ void TensorTileLoad(void *smem, const CUtensorMap *map, int x, int y, unsigned long long *bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                   SmemAddress(smem)),
+               "l"(map), "r"(x), "r"(y), "r"(SmemAddress(bar))
+               : "memory");
+}
+__device__ __forceinline__ void BarrierExpect(unsigned long long *bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(SmemAddress(bar)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ unsigned InstructionDescriptor(int n) {
   // kind::f16: FP32 accumulate (bits 4-5 = 1), A and B FP16 (0), both K-major (0), N>>3 at [17,23), M>>4 at [24,29)
@@ -222,10 +259,11 @@ __device__ __forceinline__ int ItemIndex(int sequence) {
 }
 
 template <int Rate>
-__global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillArgs a) {
+__global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillArgs a, const __grid_constant__ CUtensorMap activations) {
   using L = codec::Lane<Rate>;
-  extern __shared__ __align__(128) unsigned char raw_smem[];
-  PrefillSmem &sm = *reinterpret_cast<PrefillSmem *>(raw_smem); // no-swizzle operands need 16-byte alignment only
+  extern __shared__ __align__(16) unsigned char raw_smem[];
+  // swizzled tiles want 1024-byte alignment: the launch provides 1024 spare bytes and the struct starts at the next boundary
+  PrefillSmem &sm = *reinterpret_cast<PrefillSmem *>(raw_smem + ((1024u - (SmemAddress(raw_smem) & 1023u)) & 1023u));
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rows = a.part == 2 ? a.hidden : a.inter, cols = a.part == 2 ? a.inter : a.hidden;
   const int pairs_total = a.pairs_total;
@@ -236,6 +274,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
   if (tid == 0) {
     sm.abort = *a.bad != 0;
     sm.tiles = 0;
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&activations) : "memory");
   }
   if (a.return_to_peers && tid < a.world) {
     const int4 meta = reinterpret_cast<const int4 *>(a.peers.base[a.rank] + a.layout.meta)[tid];
@@ -305,7 +344,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
   }
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
-      BarrierInit(&sm.full[s], kProducerSets * kWarpsPerSet * 33); // every producer thread's copies + one arrival per warp
+      BarrierInit(&sm.full[s], kProducerSets * kWarpsPerSet + 1); // one arrival per producer warp + the activation copy's
       BarrierInit(&sm.empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -331,7 +370,36 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
   const unsigned tmem = sm.tmem_base;
   const volatile int *abort = &sm.abort;
 
-  if (warp >= kFirstProducerWarp) {
+  if (warp == kCopyWarp) {
+    // =============================== activation copies ===============================
+    // One thread runs ahead of everybody by as many stages as the ring has: as soon as a stage's buffers are free it
+    // asks for the stage's 128 rows x 64 inputs with one tensor copy, whose bytes complete the stage's `full` barrier.
+    if (lane == 0) {
+      bool alive = true;
+      unsigned q = 0;
+      for (int sequence = 0; alive; ++sequence, q += stages) {
+        const int index = ItemIndex(sequence);
+        if (index >= items)
+          break;
+        const int row_base = sm.tile[index / row_blocks].row_base;
+        for (int i = 0; i < stages && alive; ++i) {
+          const int s = (q + i) % kStages;
+          alive = BarrierWait(&sm.empty[s], (((q + i) / kStages) & 1) ^ 1, abort, 64);
+          if (!alive)
+            break;
+          if (PF_VARIANT(4)) {
+            BarrierArrive(&sm.full[s]);
+            continue;
+          }
+          BarrierExpect(&sm.full[s], kStageBBytes);
+          // rows past the expert's group are the next group's, or zero past the end of the tensor: they only reach
+          // accumulator rows nobody reads
+          TensorTileLoad(sm.b[s], &activations, i * kStageK, row_base, &sm.full[s]);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp >= kFirstProducerWarp) {
     // =============================== producers ===============================
     const int set = (warp - kFirstProducerWarp) / kWarpsPerSet;   // output block of the item this warp decodes
     const int column = (warp - kFirstProducerWarp) % kWarpsPerSet; // 16-output tile column inside the 128-output block
@@ -339,7 +407,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
     const int g = lane & 7, kstep = lane >> 3; // row pair, K16 step inside the stage
     const size_t tiles_per_kstep = rows / 16;
     const size_t stage_bytes = static_cast<size_t>(4) * tiles_per_kstep * L::kTileBytes;
-    const int piece = ptid & 7; // this thread copies K piece `piece` of rows (ptid >> 3) + 64*j
     // address of this lane's packed words for stage 0 of an item
     auto lane_base_of = [&](int index) -> const unsigned char * {
       const TileInfo t = sm.tile[index / row_blocks];
@@ -376,17 +443,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
       const int index = ItemIndex(sequence);
       if (index >= items)
         break;
-      const TileInfo t = sm.tile[index / row_blocks];
-      const int valid = t.valid, tile_n = (valid + 15) & ~15;
-      const __half *b_rows = a.transformed + static_cast<size_t>(t.row_base) * cols;
       const bool decodes = (index % row_blocks) * kItemBlocks + set < a.block_count; // false: single-block last item
-      int b_source[kMaxTileN / 64];
-#pragma unroll
-      for (int j = 0; j < kMaxTileN / 64; ++j) {
-        const int n = (ptid >> 3) + 64 * j;
-        b_source[j] = (n < valid ? n : valid - 1) * cols + piece * 8;
-      }
-      const int b_piece_bytes = tile_n * 16 + 16;
       for (int i = 0; i < stages; ++i) {
         const int s = (q + i) % kStages;
         uint32_t words[Rate];
@@ -398,30 +455,40 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
             ahead[d][w] = ahead[d + 1][w];
         }
         fetch(ahead[kAhead - 1]);
-        const uint32_t previous = __shfl_sync(0xffffffffu, words[Rate - 1], (lane & 24) | ((lane + 7) & 7));
-        uint32_t frag[4][4];
-        codec::Decode32<Rate>(words, previous, frag);
-        // the stage's buffers are free once the MMAs that read them four stages ago have completed
-        alive = BarrierWait(&sm.empty[s], (((q + i) / kStages) & 1) ^ 1, abort, 32);
+        // the stage's buffers are free once the MMAs that read them four stages ago have completed: normally long ago.
+        // ONE lane asks (thirty-two lanes polling one barrier word are served one after the other, and that was a third of
+        // the stage's time); the warp-wide exchange of its answer also orders the other lanes' stores behind the wait.
+        if (lane == 0)
+          alive = BarrierWait(&sm.empty[s], (((q + i) / kStages) & 1) ^ 1, abort, 32);
+        alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
         if (!alive)
           break;
-        // B: tile_n rows x 64 inputs as 16-byte pieces: canonical layout [K piece][row]
-        const unsigned b_target = SmemAddress(sm.b[s]) + piece * b_piece_bytes + (ptid >> 3) * 16;
-        const __half *b_stage_rows = b_rows + i * kStageK;
+        if (ptid == 0)
+          PF_TRACE(q + i, 0);
+        const uint32_t previous = __shfl_sync(0xffffffffu, words[Rate - 1], (lane & 24) | ((lane + 7) & 7));
+        uint32_t frag[4][4];
+        if (PF_VARIANT(1)) {
 #pragma unroll
-        for (int j = 0; j < kMaxTileN / 64; ++j)
-          if ((ptid >> 3) + 64 * j < tile_n)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_target + j * 1024), "l"(b_stage_rows + b_source[j]) : "memory");
-        // the stage's barrier counts this thread's copies as one arrival of their own, once they have landed
-        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(SmemAddress(&sm.full[s])) : "memory");
-        // weights: this lane's four 16-byte core-matrix rows (fragment f: K half f>>1, output group f&1)
-        // (K piece 2*kstep + f>>1 holds 256 rows = 4096 bytes; output block `set` starts 2048 bytes into it)
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int f = 0; f < 4; ++f)
+              frag[c][f] = ((words[(c + f) % Rate] ^ previous) & 0x03ff03ffu) | 0x30003000u; // small finite halves
+        } else {
+          codec::Decode32<Rate>(words, previous, frag);
+        }
+        if (ptid == 0)
+          PF_TRACE(q + i, 1);
+        // weights: this lane's four 16-byte pieces (fragment f: K half f>>1, output row g + 8*(f&1) of the warp's tile
+        // column), into the same layout the tensor copies produce: one 128-byte row of 64 inputs per output, eight-row
+        // groups of 1024 bytes, the 16-byte piece index XORed with the row's low three bits.  The eight lanes of a quarter
+        // warp (g = 0..7, one K16 step) hit eight different pieces: no bank conflicts, for these stores or for the MMA.
         unsigned char *a_stage = sm.a[s];
-        if (decodes) {
+        if (decodes && !PF_VARIANT(2)) {
 #pragma unroll
           for (int f = 0; f < 4; ++f) {
             const uint4 row = make_uint4(frag[0][f], frag[1][f], frag[2][f], frag[3][f]);
-            *reinterpret_cast<uint4 *>(a_stage + (2 * kstep + (f >> 1)) * 4096 + set * 2048 + (2 * column + (f & 1)) * 128 + g * 16) = row;
+            const int n = set * 128 + column * 16 + (f & 1) * 8 + g; // output row inside the stage's 256
+            *reinterpret_cast<uint4 *>(a_stage + n * 128 + (((2 * kstep + (f >> 1)) ^ g) << 4)) = row;
           }
         }
         // publish at once (release); the MMA thread orders these generic-proxy writes before its tensor-core reads
@@ -429,9 +496,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
         __syncwarp();
         if (lane == 0)
           BarrierArrive(&sm.full[s]);
+        if (ptid == 0)
+          PF_TRACE(q + i, 2);
       }
     }
-    asm volatile("cp.async.wait_all;" ::: "memory");
   } else if (warp == kMmaWarp) {
     // =============================== MMA issue ===============================
     if (lane == 0) {
@@ -441,30 +509,32 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
         const int index = ItemIndex(sequence);
         if (index >= items)
           break;
-        const int valid = sm.tile[index / row_blocks].valid, tile_n = (valid + 15) & ~15;
         const int left = a.block_count - (index % row_blocks) * kItemBlocks;
         const unsigned idesc = InstructionDescriptor((left < kItemBlocks ? left : kItemBlocks) * kTileM);
-        const unsigned piece_bytes = tile_n * 16 + 16;
         const int buffer = sequence & 1;
         // the accumulator must have been drained by the epilogue of the item two before
         alive = BarrierWait(&sm.accumulator_free[buffer], ((sequence >> 1) & 1) ^ 1, abort, 0);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         for (int i = 0; i < stages && alive; ++i) {
           const int s = (q + i) % kStages;
+          PF_TRACE(q + i, 3);
           alive = BarrierWait(&sm.full[s], ((q + i) / kStages) & 1, abort, 0);
           if (!alive)
             break;
+          PF_TRACE(q + i, 4);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // producers' stores and copies -> tensor-core reads
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const unsigned w_base = SmemAddress(sm.a[s]), x_base = SmemAddress(sm.b[s]);
-          // token rows past tile_n hold whatever the ring held before: they only reach accumulator rows nobody reads
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
-            const unsigned long long x_desc = OperandDescriptor(x_base + ks * 2 * piece_bytes, piece_bytes, 128);
-            const unsigned long long w_desc = OperandDescriptor(w_base + ks * 8192, 4096, 128);
+            if (PF_VARIANT(8) && (i > 0 || ks > 0))
+              continue;
+            const unsigned long long x_desc = SwizzledOperandDescriptor(x_base + ks * 32);
+            const unsigned long long w_desc = SwizzledOperandDescriptor(w_base + ks * 32);
             MmaSS(tmem + buffer * kBufferColumns, x_desc, w_desc, idesc, i > 0 || ks > 0);
           }
           MmaCommit(&sm.empty[s]); // arrives when the MMAs above have finished reading the stage
+          PF_TRACE(q + i, 5);
         }
         if (alive)
           MmaCommit(&sm.accumulator_ready[buffer]);
@@ -692,12 +762,31 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
   }
 }
 
-template <int Rate> int LaunchGemm(const PrefillArgs &a, dim3 grid, cudaStream_t stream) {
-  const size_t smem = sizeof(PrefillSmem);
+// The tensor map of the transformed activation rows [rows][cols] FP16: tiles of 128 rows x 64 inputs, 128-byte swizzle,
+// zeros past the end.  The encoder is a driver entry point, looked up through the runtime (no link against the driver).
+int MakeActivationMap(CUtensorMap *map, const void *transformed, int rows, int cols) {
+  using Encode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                              const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  void *entry = nullptr;
+  cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &found) != cudaSuccess || found != cudaDriverEntryPointSuccess ||
+      !entry)
+    return PADRA_INTERNAL;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * sizeof(__half)};
+  const cuuint32_t box[2] = {kStageK, kMaxTileN}, element_strides[2] = {1, 1};
+  const CUresult status = reinterpret_cast<Encode>(entry)(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(transformed), dims, strides, box,
+                                                          element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return status == CUDA_SUCCESS ? PADRA_OK : PADRA_INTERNAL;
+}
+
+template <int Rate> int LaunchGemm(const PrefillArgs &a, const CUtensorMap &map, dim3 grid, cudaStream_t stream) {
+  const size_t smem = sizeof(PrefillSmem) + 1024; // room to start the struct on a 1024-byte boundary
   // set on every launch: the attribute belongs to the current device, and the call is cheap
   if (cudaFuncSetAttribute(PrefillGemmKernel<Rate>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return PADRA_RESOURCE_EXHAUSTED;
-  PrefillGemmKernel<Rate><<<grid, kPrefillThreads, smem, stream>>>(a);
+  PrefillGemmKernel<Rate><<<grid, kPrefillThreads, smem, stream>>>(a, map);
   return CudaStatus(cudaGetLastError());
 }
 
@@ -755,13 +844,17 @@ static int LaunchPrefillGemm(const Matrix *matrices, int layer, int part, const 
   if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 1)
     return PADRA_INTERNAL;
   const dim3 grid(sms); // persistent: one CTA per SM
+  CUtensorMap map;
+  const int cols = part == 2 ? inter : hidden;
+  if (const int status = MakeActivationMap(&map, transformed, pairs < kMaxPairs ? pairs : kMaxPairs, cols); status != PADRA_OK)
+    return status;
   switch (rate) {
   case 3:
-    return LaunchGemm<3>(a, grid, stream);
+    return LaunchGemm<3>(a, map, grid, stream);
   case 4:
-    return LaunchGemm<4>(a, grid, stream);
+    return LaunchGemm<4>(a, map, grid, stream);
   case 6:
-    return LaunchGemm<6>(a, grid, stream);
+    return LaunchGemm<6>(a, map, grid, stream);
   default:
     return PADRA_UNSUPPORTED;
   }
@@ -800,3 +893,12 @@ int LaunchPrefillDownReturn(const Matrix *matrices, int layer, const int *groups
 }
 
 } // namespace padra
+
+#ifdef PADRA_PREFILL_TRACE
+extern "C" __attribute__((visibility("default"))) int padra_debug_set_prefill_variant(int variant) {
+  return static_cast<int>(cudaMemcpyToSymbol(padra::g_prefill_variant, &variant, sizeof(variant)));
+}
+extern "C" __attribute__((visibility("default"))) int padra_debug_set_prefill_trace(unsigned long long *buffer) {
+  return static_cast<int>(cudaMemcpyToSymbol(padra::g_prefill_trace, &buffer, sizeof(buffer)));
+}
+#endif
