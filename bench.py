@@ -393,8 +393,8 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
     from padra_b200.experts import bf16_values, zipf_routing
 
     local = batch // world
-    if world > 1 and exchange == "nccl" and local <= chunk:
-        chunk = local // 2  # at least two chunks per rank, so that exchange and expert work overlap
+    if world > 1 and local <= chunk:
+        chunk = local // 2  # at least two chunks per rank, so that one chunk's exchange overlaps the other's expert work
     chunks = [(c, min(chunk, local - c)) for c in range(0, local, chunk)]
     g = torch.Generator(device=dev)
     g.manual_seed(500 + rank)
@@ -416,8 +416,8 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
     elif world > 1:
         # symmetric memory may be unavailable on a host (no peer access, no handle exchange): every rank then takes the
         # NCCL exchange, and the JSON line says which exchange ran
-        try:
-            peer = EP.PeerExchangePrefill.over_group(k, owners[0], cap=chunk * TOPK)
+        try:  # two engines with an exchange block each: the chunks of a layer alternate between them, on a stream each
+            peer = [EP.PeerExchangePrefill.over_group(k, owners[0], cap=chunk * TOPK) for _ in range(2)]
             failed = 0
         except Exception as error:  # noqa: BLE001 - any failure of the rendezvous means "not available here"
             print(f"rank {rank}: peer exchange unavailable ({type(error).__name__}: {error}); using NCCL all-to-all", file=sys.stderr)
@@ -430,23 +430,26 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
             engines = [EP.ExpertParallelPrefill(backend, group_exchange, owners[layer]) for layer in range(layers)]
         else:
             device_owners = [torch.from_numpy(o.astype(np.int32)).to(dev) for o in owners]
-    normalized = torch.empty((chunk, HIDDEN), dtype=torch.float32, device=dev)
+    lanes = 2 if peer is not None else 1
+    normalized = [torch.empty((chunk, HIDDEN), dtype=torch.float32, device=dev) for _ in range(lanes)]
+    streams = [torch.cuda.Stream(device=dev) for _ in range(lanes)] if peer is not None else None
 
-    def normalise(rows):  # the post-attention norm's place: this library's kernel, weight of ones
-        out = normalized[:rows.shape[0]]
+    def normalise(rows, lane=0):  # the post-attention norm's place: this library's kernel, weight of ones
+        out = normalized[lane][:rows.shape[0]]
         k.residual_norm(rows, None, out, norm_weight)
         return out
 
-    def one_layer(layer, c, n, x):
+    def one_layer(layer, c, n, x, lane=0):
         rows = x[c:c + n]
         if peer is not None:  # rows stored straight into the owners' memory over NVLink, nothing returns to the host
-            peer.layer(layer, *routing[layer, c], normalise(rows), rows, owner=device_owners[layer])
+            peer[lane].layer(layer, *routing[layer, c], normalise(rows, lane), rows, owner=device_owners[layer])
         elif engines is None:
             k.prefill_layer(layer, *routing[layer, c], normalise(rows), rows, n)
         else:
             engines[layer].layer(layer, *routing[layer, c], normalise(rows), rows)
 
     def stack(x):
+        main = torch.cuda.current_stream()
         for layer in range(layers):
             if engines is not None:  # NCCL all-to-all, all of the layer's chunks in one pipelined call
                 pieces = []
@@ -454,6 +457,19 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
                     rows = x[c:c + n]
                     pieces.append((*routing[layer, c], normalise(rows).clone(), rows))
                 engines[layer].layer_chunks(layer, pieces)
+            elif peer is not None:
+                # the layer's chunks alternate between the two engines; the layer ends when both streams have finished
+                # (every token of layer l+1 waits for layer l of the whole rank, as it would behind an attention block)
+                start = torch.cuda.Event()
+                start.record(main)
+                for lane, stream in enumerate(streams):
+                    stream.wait_event(start)
+                    with torch.cuda.stream(stream):
+                        for c, n in chunks[lane::lanes]:
+                            one_layer(layer, c, n, x, lane)
+                    done = torch.cuda.Event()
+                    done.record(stream)
+                    main.wait_event(done)
             else:
                 for c, n in chunks:
                     one_layer(layer, c, n, x)

@@ -176,6 +176,9 @@ PADRA_API int padra_ep_dispatch(const float *activations, const int *order, cons
                                 int cap, int pairs, int hidden, unsigned epoch, int *bad, padra_stream stream);
 PADRA_API int padra_ep_wait(const void *block, int which, int world, int cap, int hidden, unsigned epoch, int *bad,
                             padra_stream stream);
+/* How long padra_ep_wait's kernel polls before it gives up, raises *bad and returns (1..60000 ms, default 2000; a
+ * process-wide host setting read at launch).  A wait that expires leaves the stream and the context usable. */
+PADRA_API int padra_ep_set_wait_limit_ms(int milliseconds);
 PADRA_API int padra_ep_group_received(const void *block, int world, int cap, int hidden, int *groups, int *counts,
                                       int group_stride, int *bad, padra_stream stream);
 PADRA_API int padra_ep_return(const unsigned short *down_rows, const unsigned long long *peer_blocks, int rank, int world,

@@ -399,6 +399,7 @@ class RefKernels:
             "ref_route": [p, p, p, i, p, p],
             "ref_route_rank_exact": [p, p, p, i, p, p],
             "ref_residual_post_norm": [p, p, p, p, p, p, i, p],
+            "ref_activate": [p, p, i, p],
         }
         for name, args in sig.items():
             f = getattr(self.lib, name)

@@ -203,3 +203,9 @@ REF_API int ref_residual_post_norm(float *x, const float *residual, float *norma
   ResidualPostNormWideExact<<<rows, 256, 0, stream>>>(x, residual, normalized, w, bad, statistics, rows);
   return Done();
 }
+
+// SwiGLU without the table, src/cuda/inference.cu:575-579, as the MTP draft layer launches it (src/cuda/mtp.cuh:383).
+REF_API int ref_activate(float *gate, const float *up, int tokens, cudaStream_t stream) {
+  Activate<<<tokens * 56, 128, 0, stream>>>(gate, up, tokens);
+  return Done();
+}

@@ -135,6 +135,10 @@ int padra_ep_wait(const void *block, int which, int world, int cap, int hidden, 
   return LaunchWaitFlags(block, which, world, cap, hidden, epoch, bad, S(stream));
 }
 
+int padra_ep_set_wait_limit_ms(int milliseconds) {
+  return SetExchangeWaitLimit(milliseconds);
+}
+
 int padra_ep_group_received(const void *block, int world, int cap, int hidden, int *groups, int *counts, int group_stride, int *bad,
                             padra_stream stream) {
   return LaunchGroupRegions(block, world, cap, hidden, groups, counts, group_stride, bad, S(stream));

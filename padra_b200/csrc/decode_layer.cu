@@ -53,7 +53,6 @@ struct LayerArgs {
   __half *svh_rows;            // [pair][hidden]: the down matrices' svh, copied beside the partial sums
   unsigned *tickets;           // gate+up: [unit][kMaxBlocks]; down: [token][kMaxBlocks]
   int *bad;
-  int debug; // temporary switches
   unsigned long long *trace; // scratch builds only
 };
 
@@ -292,7 +291,7 @@ __global__ void __launch_bounds__(kThreads, 4) LayerProjectionKernel(LayerArgs a
       // hints for what comes later: the sidecars the block's epilogue reads, this CTA's share of the expert's down matrix
       if (slice == 0 && warp == 1 && lane < 2 && (reinterpret_cast<uintptr_t>(m.svh) & 15) == 0)
         PrefetchL2(reinterpret_cast<const unsigned char *>(m.svh + base) + lane * 128, 128);
-      if (warp == 2 && lane == 0 && !(a.debug & 1)) {
+      if (warp == 2 && lane == 0) {
         const Matrix &down = unit_matrices[2];
         const unsigned ctas = gridDim.x * gridDim.z, index = blockIdx.z * gridDim.x + blockIdx.x;
         const size_t bytes = static_cast<size_t>(a.hidden) * a.inter * Rate / 8;
@@ -508,8 +507,7 @@ int LaunchDecodeLayer(const Matrix *matrices, int layer, const int *ids, const f
   const LayerWorkspace w(tokens, hidden, inter);
   if (workspace_bytes < w.total)
     return PADRA_RESOURCE_EXHAUSTED;
-  static const bool general_only = std::getenv("PADRA_DECODE_GENERAL") != nullptr; // scratch switch: compare the two forms
-  if (tokens == 1 && !general_only)
+  if (tokens == 1)
     return LaunchSingleTokenLayer(matrices, layer, ids, routing, normalized, x, rate, hidden, inter, table, workspace, bad, stream,
                                   launches);
   auto *base = static_cast<unsigned char *>(workspace);
@@ -520,8 +518,6 @@ int LaunchDecodeLayer(const Matrix *matrices, int layer, const int *ids, const f
   LayerArgs a{};
   a.matrices = matrices, a.layer = layer, a.ids = ids, a.routing = routing, a.tokens = tokens, a.hidden = hidden, a.inter = inter;
   a.normalized = normalized, a.x = x, a.table = table, a.bad = bad;
-  static const int debug = std::getenv("PADRA_DECODE_DEBUG") ? std::atoi(std::getenv("PADRA_DECODE_DEBUG")) : 0;
-  a.debug = debug;
 #ifdef PADRA_DECODE_TRACE
   a.trace = g_trace ? g_trace + static_cast<size_t>(g_trace_launch++) * 2 * 1024 * 16 : nullptr;
 #endif

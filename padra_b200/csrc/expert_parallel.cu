@@ -15,6 +15,8 @@
 // (source, destination) that carries the call's epoch, written after a system-scope fence by the last CTA of the
 // sending kernel; a one-CTA wait kernel on the receiving side polls its own flags, bounded in time.  Nothing in this
 // form touches the host: row counts stay on the device, next to the flags.
+#include <atomic>
+
 #include "common.cuh"
 #include "exchange.cuh"
 #include "kernels.cuh"
@@ -24,40 +26,47 @@ namespace {
 
 constexpr int kMaxRows = 4096 * kTopK; // rows one grouped-projection call takes (received rows may exceed a rank's own)
 
-// One CTA per expert walks the rows in order and appends those routed to it (stable, like GroupKernel).  `ids` are
-// expert ids 0..63 per row; experts this rank does not own simply get no rows.
+// Expert-major row lists for rows that carry their expert id (received rows): one CTA per expert; thread t owns the
+// consecutive rows [t*per, (t+1)*per), counts its matches, one scan over the CTA gives every thread its first position,
+// then it writes -- lists are stable in row order.  `ids` are expert ids 0..63 per row; experts this rank does not own
+// simply get no rows.  (The same form as GroupKernel in schedule.cu and GroupRegionsKernel below.)
 __global__ void __launch_bounds__(256) GroupRowsKernel(const int *ids, int *groups, int *counts, int rows, int stride, int *bad) {
   const int expert = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   __shared__ int warp_counts[8], warp_offsets[8], total;
-  if (!threadIdx.x)
-    total = 0;
-  __syncthreads();
-  for (int base = 0; base < rows; base += 256) {
-    const int row = base + threadIdx.x;
-    const int id = row < rows ? ids[row] : -1;
-    if (row < rows && (id < 0 || id >= kExperts) && expert == 0)
+  const int per = (rows + 255) / 256, first = threadIdx.x * per, last = first + per < rows ? first + per : rows;
+  int mine = 0;
+  for (int row = first; row < last; ++row) {
+    const int id = ids[row];
+    if ((id < 0 || id >= kExperts) && expert == 0)
       Raise(bad);
-    const bool mine = id == expert;
-    const unsigned votes = __ballot_sync(0xffffffffu, mine);
-    if (!lane)
-      warp_counts[warp] = __popc(votes);
-    __syncthreads();
-    if (!threadIdx.x) {
-      int n = total;
-      for (int w = 0; w < 8; ++w) {
-        warp_offsets[w] = n;
-        n += warp_counts[w];
-      }
-      total = n;
+    mine += id == expert;
+  }
+  int inclusive = mine;
+#pragma unroll
+  for (int d = 1; d < 32; d *= 2) {
+    const int other = __shfl_up_sync(0xffffffffu, inclusive, d);
+    if (lane >= d)
+      inclusive += other;
+  }
+  if (lane == 31)
+    warp_counts[warp] = inclusive;
+  __syncthreads();
+  if (!threadIdx.x) {
+    int n = 0;
+    for (int w = 0; w < 8; ++w) {
+      warp_offsets[w] = n;
+      n += warp_counts[w];
     }
-    __syncthreads();
-    if (mine) {
-      const int at = warp_offsets[warp] + __popc(votes & ((1u << lane) - 1u));
+    total = n;
+  }
+  __syncthreads();
+  int at = warp_offsets[warp] + inclusive - mine;
+  for (int row = first; row < last && mine; ++row)
+    if (ids[row] == expert) {
       if (at < stride)
         groups[static_cast<size_t>(expert) * stride + at] = row;
+      ++at;
     }
-    __syncthreads();
-  }
   if (!threadIdx.x) {
     if (total > stride)
       Raise(bad);
@@ -308,8 +317,9 @@ __global__ void __launch_bounds__(256) DispatchKernel(const float *activations, 
   }
 }
 
-// Poll `world` flags of this rank's own block until each carries `epoch`; give up after kFlagWaitNs.
-__global__ void WaitFlagsKernel(const unsigned *flags, int world, unsigned epoch, int *bad) {
+// Poll `world` flags of this rank's own block until each carries `epoch`; give up after limit_ns (the kernel then raises the
+// error flag and returns: the stream goes on, the context stays usable).
+__global__ void WaitFlagsKernel(const unsigned *flags, int world, unsigned epoch, int *bad, unsigned long long limit_ns) {
   if (threadIdx.x >= world)
     return;
   unsigned long long started;
@@ -317,7 +327,7 @@ __global__ void WaitFlagsKernel(const unsigned *flags, int world, unsigned epoch
   while (LoadFlagSystem(flags + threadIdx.x) != epoch) {
     unsigned long long now;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-    if (now - started > kFlagWaitNs) {
+    if (now - started > limit_ns) {
       Raise(bad);
       break;
     }
@@ -466,6 +476,15 @@ bool FillPeers(PeerBlocks &peers, const unsigned long long *bases, int world) {
 
 } // namespace
 
+// How long padra_ep_wait's kernel polls before it gives up (host setting, default kFlagWaitNs).
+static std::atomic<unsigned long long> g_flag_wait_ns{kFlagWaitNs};
+int SetExchangeWaitLimit(int milliseconds) {
+  if (milliseconds < 1 || milliseconds > 60000)
+    return PADRA_INVALID_ARGUMENT;
+  g_flag_wait_ns.store(static_cast<unsigned long long>(milliseconds) * 1000000ull);
+  return PADRA_OK;
+}
+
 // SMs of the current device (asked every time: a process may drive several devices).
 static int SmCount() {
   int device = 0, sms = 0;
@@ -503,7 +522,8 @@ int LaunchWaitFlags(const void *block, int which, int world, int cap, int hidden
     return PADRA_INVALID_ARGUMENT;
   const ExchangeLayout l = MakeExchangeLayout(world, cap, hidden);
   WaitFlagsKernel<<<1, 32, 0, stream>>>(
-      reinterpret_cast<const unsigned *>(static_cast<const unsigned char *>(block) + (which ? l.came_back : l.arrived)), world, epoch, bad);
+      reinterpret_cast<const unsigned *>(static_cast<const unsigned char *>(block) + (which ? l.came_back : l.arrived)), world, epoch, bad,
+      g_flag_wait_ns.load());
   return CudaStatus(cudaGetLastError());
 }
 

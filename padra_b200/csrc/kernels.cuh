@@ -50,6 +50,7 @@ size_t ExchangeBytes(int world, int cap, int hidden, size_t *offsets);
 int LaunchDispatch(const float *activations, const int *order, const int *send_ids, const long long *send_counts,
                    const unsigned long long *bases, int rank, int world, int cap, int pairs, int hidden, unsigned epoch, int *bad,
                    cudaStream_t stream);
+int SetExchangeWaitLimit(int milliseconds);
 int LaunchWaitFlags(const void *block, int which, int world, int cap, int hidden, unsigned epoch, int *bad, cudaStream_t stream);
 int LaunchGroupRegions(const void *block, int world, int cap, int hidden, int *groups, int *counts, int group_stride, int *bad,
                        cudaStream_t stream);

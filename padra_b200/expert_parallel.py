@@ -252,6 +252,12 @@ class PeerExchangePrefill:
         self.transformed_up = torch.empty((self.MAX_GROUPED, self.hidden), dtype=torch.float16, device=dev)
         self.backend = KernelBackend(kernels)
         self.epoch = 0
+        self._side = None  # this engine's second stream (two engines may run side by side, each on its own pair of streams)
+
+    def side_stream(self):
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        return self._side
 
     @staticmethod
     def exchange_bytes(lib, world: int, cap: int, hidden: int) -> int:
@@ -304,7 +310,7 @@ class PeerExchangePrefill:
                 on, k.t.rate, self.hidden, self.inter, *blocks), "padra_exl3_prefill_rows_launch")
 
         # the up projection runs on a second stream beside the gate projection; both join before the down projection
-        main, side = torch.cuda.current_stream(), k.side_stream()
+        main, side = torch.cuda.current_stream(), self.side_stream()
         fork, join = torch.cuda.Event(), torch.cuda.Event()
         fork.record(main)
         side.wait_event(fork)

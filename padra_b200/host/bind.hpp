@@ -118,4 +118,40 @@ inline void DecodeLayer(const mellum16::DeviceMatrix *m, int layer, const int *i
                                     workspace_bytes, bad, s));
 }
 
+// The expert layer of the MTP draft model (src/cuda/mtp.cuh:370-387): one K4 layer with a descriptor table of its own
+// (layer 0), one token.  Replaces Projection<4><<<dim3(7, 8, 2)>>> (gate+up), Activate<<<56, 128>>>,
+// Projection<4><<<dim3(18, 8)>>> (down) and Combine<<<18, 128>>> with one call; ids and routing weights come from the
+// draft's own Route kernel as before.
+inline void DraftExpertLayer(const mellum16::DeviceMatrix *draft_descriptors, const int *ids, const float *routing_weights,
+                             const float *normalized, float *x, const unsigned short *table, void *workspace,
+                             std::size_t workspace_bytes, int *bad, cudaStream_t s) {
+  DecodeLayer(draft_descriptors, 0, ids, routing_weights, normalized, x, 1, 4, table, workspace, workspace_bytes, bad, s);
+}
+
+// RouteRankExact<<<rows, 64>>> (src/cuda/router_rank_exact.cuh:3-81; inference.cu:2950, :3366).
+inline void RouteRankExact(const float *logits, int *ids, float *weights, int rows, int *bad, cudaStream_t s) {
+  Check(padra_route(logits, ids, weights, rows, bad, s));
+}
+// Route + fast_expert::Group + exl3_masked::Schedule of one prefill chunk (inference.cu:3861, :3875, :3890) as one
+// launch.  `ticket` is one zeroed word of device memory that every call leaves zero.
+inline void RouteGroupSchedule(const float *logits, int *ids, float *weights, int *groups, int *counts,
+                               mellum16::exl3_masked_schedule::Tile *tiles, int *tile_count, int tokens, unsigned *ticket,
+                               int *bad, cudaStream_t s) {
+  Check(padra_route_group_schedule(logits, ids, weights, groups, counts, reinterpret_cast<padra_tile *>(tiles), tile_count,
+                                   tokens, ticket, bad, s));
+}
+// ResidualPostNormWideExact<<<rows, 256>>> (src/cuda/residual_norm_wide_exact.cuh:82-131; inference.cu:2913, :3358).
+// The norm weight is a BF16 vector descriptor: its data pointer is passed on.
+inline void ResidualPostNorm(float *x, const float *residual, float *normalized, const mellum16::DeviceMatrix &weight, int *bad,
+                             float *statistics, int rows, cudaStream_t s) {
+  Check(padra_residual_norm(x, residual, normalized, reinterpret_cast<const unsigned short *>(weight.data), rows, kHidden, bad,
+                            statistics, s));
+}
+// combine_norm_exact::CombineNorm<false><<<1, 128>>> (src/cuda/combine_norm_exact.cuh:7-68), extended to `rows` rows.
+inline void CombineNorm(float *x, const float *down, const float *routing, float *normalized, const mellum16::DeviceMatrix &weight,
+                        int *bad, float *statistics, int rows, cudaStream_t s) {
+  Check(padra_combine_norm(x, down, routing, normalized, reinterpret_cast<const unsigned short *>(weight.data), rows, kHidden, bad,
+                           statistics, s));
+}
+
 } // namespace padra_b200_bind

@@ -172,6 +172,7 @@ void all(const mellum16::DeviceMatrix *m, mellum16::exl3_masked_schedule::Tile *
   CombinePacked(f, h, f, 4, i, true, s);
   ExpertLaunch(m, 0, 0, i, f, f, f, f, 1, i, s, false, u, 4);
   DecodeLayer(m, 0, i, f, f, f, 1, 4, h, ws, 0, i, s);
+  DraftExpertLayer(m, i, f, f, f, h, ws, 0, i, s);
 }}
 ''')
     cuda_include = "/usr/local/cuda/include"

@@ -273,3 +273,48 @@ def test_exchange_block_layout_is_consistent():
     assert lib.padra_ep_exchange_bytes(9, cap, hidden, None) == 0             # at most eight ranks
     assert lib.padra_ep_exchange_bytes(world, cap, 100, None) == 0            # hidden must be a multiple of 128
     assert lib.padra_ep_exchange_bytes(world, 4, hidden, None) == 0           # at least one token's pairs
+
+
+@pytest.mark.gpu
+def test_exchange_wait_gives_up_and_leaves_the_stream_usable():
+    """padra_ep_wait on a block that nobody will ever announce into: after the (shortened) time limit the kernel raises
+    the error flag and returns; the next launch on the stream runs as usual.  This is the path a rank takes when a peer
+    never sends -- made here without any peer, so nothing on the GPU hangs or faults."""
+    import ctypes as C
+    import time
+
+    from padra_b200 import binding as B
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    lib = B.load()
+    dev = torch.device("cuda:0")
+    world, cap, hidden = 2, 64, 256
+    total = lib.padra_ep_exchange_bytes(world, cap, hidden, None)
+    block = torch.zeros(total, dtype=torch.uint8, device=dev)  # no flag ever carries epoch 1
+    bad = torch.zeros(1, dtype=torch.int32, device=dev)
+    assert lib.padra_ep_set_wait_limit_ms(0) == B.INVALID_ARGUMENT
+    assert lib.padra_ep_set_wait_limit_ms(50) == B.OK
+    try:
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        assert lib.padra_ep_wait(block.data_ptr(), 0, world, cap, hidden, 1, bad.data_ptr(), B.stream_handle()) == B.OK
+        torch.cuda.synchronize()
+        waited = time.perf_counter() - t0
+        assert int(bad.item()) == 1, "an expired wait must raise the error flag"
+        assert 0.04 <= waited < 1.0, f"the wait took {waited:.3f} s against a 50 ms limit"
+        # the stream goes on: an ordinary launch of the library and a torch kernel both complete
+        table = torch.empty(65536, dtype=torch.uint16, device=dev)
+        assert lib.padra_exl3_silu_build(table.data_ptr(), B.stream_handle()) == B.OK
+        torch.cuda.synchronize()
+        assert int(table.view(torch.int16)[0x3F80].item()) != 0  # silu(1.0) is not zero
+        # a flag that is there is seen at once
+        offsets = (C.c_size_t * 6)()
+        lib.padra_ep_exchange_bytes(world, cap, hidden, offsets)
+        block[offsets[4]:offsets[4] + 4 * world].view(torch.int32).fill_(7)
+        bad.zero_()
+        assert lib.padra_ep_wait(block.data_ptr(), 0, world, cap, hidden, 7, bad.data_ptr(), B.stream_handle()) == B.OK
+        torch.cuda.synchronize()
+        assert int(bad.item()) == 0
+    finally:
+        assert lib.padra_ep_set_wait_limit_ms(2000) == B.OK

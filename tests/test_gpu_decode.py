@@ -477,3 +477,41 @@ def test_reference_row_union_kernel_agrees(oracle, gpu):
     assert_close_rows(gate.cpu().numpy(), rg.cpu().numpy(), "union gate vs reference")
     assert_close_rows(up.cpu().numpy(), ru.cpu().numpy(), "union up vs reference")
     assert int(bad.item()) == 0 and k.bad_flag() == 0
+
+
+@needs_ref
+def test_mtp_draft_expert_layer_against_reference_sequence(oracle, gpu):
+    """The expert layer of the MTP draft model (src/cuda/mtp.cuh:364-387): the reference's own sequence -- Route, the
+    gate+up projection kernel, the table-free Activate, the down projection kernel, Combine -- on a one-layer K4 table of
+    its own at the reference's dimensions, against one call of the whole-layer entry point (what the DraftExpertLayer
+    forwarder issues).  Routing must be equal bit for bit, the layer within the chained tolerance."""
+    from padra_b200 import binding as B
+    from padra_b200.experts import ExpertKernels, ExpertTable
+
+    hidden, inter, rate = 2304, 896, 4
+    table = ExpertTable(1, hidden, inter, rate, gpu).fill_random(321)  # the draft model's own table: layer 0 only
+    k = ExpertKernels(table)
+    ref = O.RefKernels()
+    rng = np.random.default_rng(17)
+    logits = torch.from_numpy(O.bf16_round(rng.standard_normal((1, 64)).astype(np.float32))).to(gpu)
+    normalized = torch.from_numpy(O.bf16_round(rng.standard_normal((1, hidden)).astype(np.float32))).to(gpu)
+    x = torch.from_numpy(O.bf16_round(rng.standard_normal((1, hidden)).astype(np.float32))).to(gpu)
+    s, D = B.stream_handle(), table.descriptors.data_ptr()
+    bad = torch.zeros(1, dtype=torch.int32, device=gpu)
+    ids = torch.zeros(8, dtype=torch.int32, device=gpu)
+    weights = torch.zeros(8, device=gpu)
+    ref.ref_route(B.ptr(logits), B.ptr(ids), B.ptr(weights), 1, B.ptr(bad), s)
+    ours_ids, ours_w = k.route(logits)
+    assert torch.equal(ours_ids.reshape(-1), ids) and torch.equal(ours_w.reshape(-1).view(torch.int32), weights.view(torch.int32))
+    gate, up = torch.zeros((8, inter), device=gpu), torch.zeros((8, inter), device=gpu)
+    down = torch.zeros((8, hidden), device=gpu)
+    want = x.clone()
+    ref.ref_decode_dual_launch(D, 0, 0, B.ptr(ids), B.ptr(normalized), B.ptr(gate), B.ptr(up), 8, B.ptr(bad), s, rate)
+    ref.ref_activate(B.ptr(gate), B.ptr(up), 1, s)
+    ref.ref_decode_dual_launch(D, 0, 2, B.ptr(ids), B.ptr(gate), B.ptr(down), None, 8, B.ptr(bad), s, rate)
+    ref.ref_combine(B.ptr(want), B.ptr(down), B.ptr(weights), 1, B.ptr(bad), s)
+    got = x.clone()
+    k.moe_decode_layer(0, ids, weights, normalized, got, 1)
+    torch.cuda.synchronize()
+    assert int(bad.item()) == 0 and k.bad_flag() == 0
+    assert_close_rows(got.cpu().numpy(), want.cpu().numpy(), "draft expert layer vs the reference's sequence", chained=True)
