@@ -131,6 +131,16 @@ PADRA_API int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer,
                                         padra_stream stream, unsigned *stats, int wide_input, int rate,
                                         int hidden, int inter);
 
+/* Gate and up of a chunk in ONE launch of the tensor-memory grouped GEMM (the reference launches the two parts one
+ * after the other, src/cuda/inference.cu:3896-3907): the work items of both parts form one list, so the persistent CTAs
+ * are loaded evenly (1248 equal items on 148 SMs instead of two times 624).  Arguments as padra_exl3_prefill_launch
+ * with wide_input = 1; gate_output / up_output are the two parts' [pairs][inter] BF16-bit outputs; transformed is
+ * workspace of 2*pairs*hidden halves (both parts' transformed rows).  Results equal those of the two separate calls. */
+PADRA_API int padra_exl3_prefill_gate_up_launch(const padra_matrix *matrices, int layer, const int *groups,
+                                                const int *counts, const float *input, unsigned short *gate_output,
+                                                unsigned short *up_output, void *transformed, int tokens, int *bad,
+                                                padra_stream stream, int rate, int hidden, int inter);
+
 /* ---- expert-parallel prefill -----------------------------------------------------------------------------
  * The reference runs on one GPU; these four entry points are what a host needs around an all-to-all exchange when the
  * 64 experts of a layer are spread over several GPUs (the exchange itself is the host's: NCCL).  Arithmetic is that
@@ -146,6 +156,8 @@ PADRA_API int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer,
  *     (parts 0, 1: input_rows [rows][hidden]; part 2: gate/up [rows][inter]); output [rows][out] BF16 bits in row
  *     order (row indices may be sparse, up to 2^20; at most 32768 rows may be grouped); transformed is workspace of
  *     32768*max(hidden, inter) halves at most.
+ *   padra_exl3_prefill_rows_gate_up_launch: parts 0 and 1 of the same in one launch (see
+ *     padra_exl3_prefill_gate_up_launch); transformed holds 2*min(rows, 32768)*hidden halves.
  *   padra_ep_combine: padra_combine_packed with the down row of pair p at down_rows[position[p]]. */
 /* The exchange done by the GPUs themselves over NVLink peer memory (no host in the loop, no NCCL on the data path).
  * Every rank owns one exchange block of padra_ep_exchange_bytes(world, cap, hidden, offsets) bytes, zero-filled once,
@@ -202,6 +214,11 @@ PADRA_API int padra_exl3_prefill_rows_launch(const padra_matrix *matrices, int l
                                              const unsigned short *table, void *transformed, int *bad,
                                              padra_stream stream, int rate, int hidden, int inter, int block_begin,
                                              int block_count);
+PADRA_API int padra_exl3_prefill_rows_gate_up_launch(const padra_matrix *matrices, int layer, const int *groups,
+                                                     const int *counts, int group_stride, int rows,
+                                                     const unsigned short *input_rows, unsigned short *gate_output,
+                                                     unsigned short *up_output, void *transformed, int *bad,
+                                                     padra_stream stream, int rate, int hidden, int inter);
 PADRA_API int padra_ep_combine(float *x, const unsigned short *down_rows, const int *position, const float *weights,
                                int tokens, int *bad, int residual, int hidden, padra_stream stream);
 

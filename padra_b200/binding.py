@@ -47,6 +47,8 @@ SIGNATURES = {
     "padra_ep_pack_rows": ([_p, _p, _p, _i, _i, _p, _p], _i),
     "padra_ep_group_rows": ([_p, _p, _p, _i, _i, _p, _p], _i),
     "padra_exl3_prefill_rows_launch": ([_p, _i, _i, _p, _p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i], _i),
+    "padra_exl3_prefill_gate_up_launch": ([_p, _i, _p, _p, _p, _p, _p, _p, _i, _p, _p, _i, _i, _i], _i),
+    "padra_exl3_prefill_rows_gate_up_launch": ([_p, _i, _p, _p, _i, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i], _i),
     "padra_ep_combine": ([_p, _p, _p, _p, _i, _p, _i, _i, _p], _i),
     "padra_exl3_moe_decode_layer_static": ([_p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p], _i),
     "padra_exl3_moe_decode_layer_launches": ([_p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, C.c_size_t, _p, _p, C.c_uint], _i),

@@ -121,6 +121,33 @@ int padra_exl3_prefill_launch(const padra_matrix *matrices, int layer, int part,
                               bad, S(stream), rate, hidden, inter);
 }
 
+int padra_exl3_prefill_gate_up_launch(const padra_matrix *matrices, int layer, const int *groups, const int *counts,
+                                      const float *input, unsigned short *gate_output, unsigned short *up_output, void *transformed,
+                                      int tokens, int *bad, padra_stream stream, int rate, int hidden, int inter) {
+  if (!RateOk(rate))
+    return PADRA_UNSUPPORTED;
+  if (tokens < 4 || tokens > 2048)
+    return PADRA_INVALID_ARGUMENT;
+  if (!matrices || !groups || !counts || !input || !gate_output || !up_output || !transformed || !bad || layer < 0 || hidden < 128 ||
+      inter < 128 || (hidden % 128) || (inter % 128))
+    return PADRA_INVALID_ARGUMENT;
+  return LaunchPrefillGateUp(matrices, layer, groups, counts, input, gate_output, up_output, transformed, tokens, bad, S(stream), rate,
+                             hidden, inter);
+}
+
+int padra_exl3_prefill_rows_gate_up_launch(const padra_matrix *matrices, int layer, const int *groups, const int *counts,
+                                           int group_stride, int rows, const unsigned short *input_rows, unsigned short *gate_output,
+                                           unsigned short *up_output, void *transformed, int *bad, padra_stream stream, int rate,
+                                           int hidden, int inter) {
+  if (!RateOk(rate))
+    return PADRA_UNSUPPORTED;
+  if (!matrices || !groups || !counts || !input_rows || !gate_output || !up_output || !transformed || !bad || layer < 0 || hidden < 128 ||
+      inter < 128 || (hidden % 128) || (inter % 128))
+    return PADRA_INVALID_ARGUMENT;
+  return LaunchPrefillRowsGateUp(matrices, layer, groups, counts, group_stride, rows, input_rows, gate_output, up_output, transformed, bad,
+                                 S(stream), rate, hidden, inter);
+}
+
 size_t padra_ep_exchange_bytes(int world, int cap, int hidden, size_t *offsets) {
   return ExchangeBytes(world, cap, hidden, offsets);
 }

@@ -71,6 +71,12 @@ int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const
                               unsigned short *output, const unsigned short *gate, const unsigned short *up,
                               const unsigned short *table, void *transformed, int tokens, int *bad, cudaStream_t stream, int rate,
                               int hidden, int inter);
+int LaunchPrefillGateUp(const Matrix *matrices, int layer, const int *groups, const int *counts, const float *input,
+                        unsigned short *gate_output, unsigned short *up_output, void *transformed, int tokens, int *bad, cudaStream_t stream,
+                        int rate, int hidden, int inter);
+int LaunchPrefillRowsGateUp(const Matrix *matrices, int layer, const int *groups, const int *counts, int group_stride, int rows,
+                            const unsigned short *input_rows, unsigned short *gate_output, unsigned short *up_output, void *transformed,
+                            int *bad, cudaStream_t stream, int rate, int hidden, int inter);
 int LaunchGroup(const int *ids, int *groups, int *counts, int tokens, int *bad, cudaStream_t stream);
 int LaunchSchedule(const int *counts, padra_tile *tiles, int *tile_count, int tokens, int *bad, cudaStream_t stream);
 int LaunchPrefill(const Matrix *matrices, int layer, int part, const int *ids, const int *groups, const int *counts,

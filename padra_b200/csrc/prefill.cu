@@ -95,9 +95,11 @@ struct PrefillSmem {
 struct PrefillArgs {
   const Matrix *matrices;
   int layer, part;
+  int parts; // 1, or 2: the launch computes parts `part` and `part + 1` (gate and up) as one list of items
   const int *groups, *counts;
   const __half *transformed; // [pairs][cols] in expert-grouped order
   unsigned short *output;    // [pairs][rows] BF16 bits, pair order
+  unsigned short *output_second; // parts == 2: the rows of the second part
   int group_stride; // rows of `groups` per expert = the most pairs one expert can hold
   int pairs_total;  // pairs (rows of `output`) in the call
   int hidden, inter;
@@ -259,7 +261,8 @@ __device__ __forceinline__ int ItemIndex(int sequence) {
 }
 
 template <int Rate>
-__global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillArgs a, const __grid_constant__ CUtensorMap activations) {
+__global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillArgs a, const __grid_constant__ CUtensorMap activations,
+                                                                        const __grid_constant__ CUtensorMap activations_second) {
   using L = codec::Lane<Rate>;
   extern __shared__ __align__(16) unsigned char raw_smem[];
   // swizzled tiles want 1024-byte alignment: the launch provides 1024 spare bytes and the struct starts at the next boundary
@@ -275,6 +278,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
     sm.abort = *a.bad != 0;
     sm.tiles = 0;
     asm volatile("prefetch.tensormap [%0];" ::"l"(&activations) : "memory");
+    if (a.parts == 2)
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&activations_second) : "memory");
   }
   if (a.return_to_peers && tid < a.world) {
     const int4 meta = reinterpret_cast<const int4 *>(a.peers.base[a.rank] + a.layout.meta)[tid];
@@ -295,10 +300,12 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
     }
     my_tiles = (my_count + kMaxTileN - 1) / kMaxTileN;
     if (my_count) {
-      const Matrix &m = a.matrices[(static_cast<size_t>(a.layer) * kExperts + tid) * 3 + a.part];
-      if (m.format != FormatOfRate(Rate) || m.rows != rows || m.cols != cols || (cols % 128) || (rows % kTileM) || !m.data || !m.svh || !m.suh) {
-        Raise(a.bad);
-        sm.abort = 1;
+      for (int p = 0; p < a.parts; ++p) {
+        const Matrix &m = a.matrices[(static_cast<size_t>(a.layer) * kExperts + tid) * 3 + a.part + p];
+        if (m.format != FormatOfRate(Rate) || m.rows != rows || m.cols != cols || (cols % 128) || (rows % kTileM) || !m.data || !m.svh || !m.suh) {
+          Raise(a.bad);
+          sm.abort = 1;
+        }
       }
     }
     tile_prefix = my_tiles, pair_prefix = my_count; // inclusive scans inside the warp
@@ -354,7 +361,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  const int items = tiles * row_blocks;
+  // item index -> (second part?, token tile, pair of output blocks): the parts' item lists follow one another
+  const int items_per_part = tiles * row_blocks, items = items_per_part * a.parts;
+  auto second_part = [&](int index) { return index >= items_per_part; };
+  auto tile_of = [&](int index) { return (index >= items_per_part ? index - items_per_part : index) / row_blocks; };
+  auto block_item_of = [&](int index) { return (index >= items_per_part ? index - items_per_part : index) % row_blocks; };
   if (sm.abort || ItemIndex(0) >= items) { // nothing allocated yet
     AnnounceReturn(a, &sm.last);
     return;
@@ -381,7 +392,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
         const int index = ItemIndex(sequence);
         if (index >= items)
           break;
-        const int row_base = sm.tile[index / row_blocks].row_base;
+        const int row_base = sm.tile[tile_of(index)].row_base;
+        const CUtensorMap *map = second_part(index) ? &activations_second : &activations;
         for (int i = 0; i < stages && alive; ++i) {
           const int s = (q + i) % kStages;
           alive = BarrierWait(&sm.empty[s], (((q + i) / kStages) & 1) ^ 1, abort, 64);
@@ -394,7 +406,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
           BarrierExpect(&sm.full[s], kStageBBytes);
           // rows past the expert's group are the next group's, or zero past the end of the tensor: they only reach
           // accumulator rows nobody reads
-          TensorTileLoad(sm.b[s], &activations, i * kStageK, row_base, &sm.full[s]);
+          TensorTileLoad(sm.b[s], map, i * kStageK, row_base, &sm.full[s]);
         }
       }
     }
@@ -409,9 +421,9 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
     const size_t stage_bytes = static_cast<size_t>(4) * tiles_per_kstep * L::kTileBytes;
     // address of this lane's packed words for stage 0 of an item
     auto lane_base_of = [&](int index) -> const unsigned char * {
-      const TileInfo t = sm.tile[index / row_blocks];
-      const unsigned char *data = a.matrices[(static_cast<size_t>(a.layer) * kExperts + t.expert) * 3 + a.part].data;
-      int block = a.block_begin + (index % row_blocks) * kItemBlocks + set;
+      const TileInfo t = sm.tile[tile_of(index)];
+      const unsigned char *data = a.matrices[(static_cast<size_t>(a.layer) * kExperts + t.expert) * 3 + a.part + second_part(index)].data;
+      int block = a.block_begin + block_item_of(index) * kItemBlocks + set;
       if (block >= a.block_begin + a.block_count)
         block = a.block_begin + a.block_count - 1; // odd block count: the last item has one block, this set idles there
       return data + (static_cast<size_t>(kstep) * tiles_per_kstep + block * 8 + column) * L::kTileBytes + g * L::kBytes;
@@ -443,7 +455,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
       const int index = ItemIndex(sequence);
       if (index >= items)
         break;
-      const bool decodes = (index % row_blocks) * kItemBlocks + set < a.block_count; // false: single-block last item
+      const bool decodes = block_item_of(index) * kItemBlocks + set < a.block_count; // false: single-block last item
       for (int i = 0; i < stages; ++i) {
         const int s = (q + i) % kStages;
         uint32_t words[Rate];
@@ -509,7 +521,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
         const int index = ItemIndex(sequence);
         if (index >= items)
           break;
-        const int left = a.block_count - (index % row_blocks) * kItemBlocks;
+        const int left = a.block_count - block_item_of(index) * kItemBlocks;
         const unsigned idesc = InstructionDescriptor((left < kItemBlocks ? left : kItemBlocks) * kTileM);
         const int buffer = sequence & 1;
         // the accumulator must have been drained by the epilogue of the item two before
@@ -552,10 +564,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
       const int index = ItemIndex(sequence);
       if (index >= items)
         break;
-      const TileInfo t = sm.tile[index / row_blocks];
-      const int first_block = a.block_begin + (index % row_blocks) * kItemBlocks, valid = t.valid, buffer = sequence & 1;
+      const TileInfo t = sm.tile[tile_of(index)];
+      const int first_block = a.block_begin + block_item_of(index) * kItemBlocks, valid = t.valid, buffer = sequence & 1;
       const int left = a.block_begin + a.block_count - first_block, item_blocks = left < kItemBlocks ? left : kItemBlocks;
-      const Matrix &m = a.matrices[(static_cast<size_t>(a.layer) * kExperts + t.expert) * 3 + a.part];
+      const Matrix &m = a.matrices[(static_cast<size_t>(a.layer) * kExperts + t.expert) * 3 + a.part + second_part(index)];
+      unsigned short *const item_output = second_part(index) ? a.output_second : a.output;
       for (int b = 0; b < item_blocks; ++b)
         sm.scale[buffer][b * kTileM + o] = HalfBitsToFloat(m.svh[(first_block + b) * kTileM + o]);
       int *pairs = sm.pairs[buffer];
@@ -611,7 +624,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
           out = reinterpret_cast<unsigned short *>(a.peers.base[source] + a.layout.returned) +
                 static_cast<size_t>(sm.from[source] + (pair - source * a.cap)) * rows + block * kTileM;
         } else {
-          out = a.output + (n < valid ? static_cast<size_t>(pairs[n]) : 0) * rows + block * kTileM;
+          out = item_output + (n < valid ? static_cast<size_t>(pairs[n]) : 0) * rows + block * kTileM;
         }
 #pragma unroll 1
         for (int c0 = 0; c0 < 32; c0 += 8) {
@@ -781,12 +794,12 @@ int MakeActivationMap(CUtensorMap *map, const void *transformed, int rows, int c
   return status == CUDA_SUCCESS ? PADRA_OK : PADRA_INTERNAL;
 }
 
-template <int Rate> int LaunchGemm(const PrefillArgs &a, const CUtensorMap &map, dim3 grid, cudaStream_t stream) {
+template <int Rate> int LaunchGemm(const PrefillArgs &a, const CUtensorMap &map, const CUtensorMap &map_second, dim3 grid, cudaStream_t stream) {
   const size_t smem = sizeof(PrefillSmem) + 1024; // room to start the struct on a 1024-byte boundary
   // set on every launch: the attribute belongs to the current device, and the call is cheap
   if (cudaFuncSetAttribute(PrefillGemmKernel<Rate>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return PADRA_RESOURCE_EXHAUSTED;
-  PrefillGemmKernel<Rate><<<grid, kPrefillThreads, smem, stream>>>(a, map);
+  PrefillGemmKernel<Rate><<<grid, kPrefillThreads, smem, stream>>>(a, map, map_second);
   return CudaStatus(cudaGetLastError());
 }
 
@@ -805,7 +818,11 @@ static int LaunchPrefillGemm(const Matrix *matrices, int layer, int part, const 
                              const unsigned short *pair_rows, unsigned short *output, const unsigned short *gate,
                              const unsigned short *up, const unsigned short *table, void *transformed, int group_stride, int pairs,
                              int *bad, cudaStream_t stream, int rate, int hidden, int inter, const ReturnSpec *ret = nullptr,
-                             int block_begin = 0, int block_count = 0) {
+                             int block_begin = 0, int block_count = 0, unsigned short *output_second = nullptr) {
+  // output_second: gate (part 0) and up (part 1) as ONE list of work items: `transformed` then holds both parts'
+  // rows, the second part's behind the first's
+  if (output_second && (part != 0 || ret || reinterpret_cast<uintptr_t>(output_second) % 16))
+    return PADRA_INVALID_ARGUMENT;
   if (pairs < 1 || pairs > kMaxPairIndex || group_stride < 1 || group_stride > kMaxPairs || !transformed)
     return PADRA_INVALID_ARGUMENT;
   if ((!ret && (!output || reinterpret_cast<uintptr_t>(output) % 16)) || reinterpret_cast<uintptr_t>(transformed) % 16)
@@ -816,18 +833,23 @@ static int LaunchPrefillGemm(const Matrix *matrices, int layer, int part, const 
   if (block_begin < 0 || block_count < 1 || block_begin + block_count > all_blocks)
     return PADRA_INVALID_ARGUMENT;
   // a launch that starts at a later block continues a call whose first launch has filled `transformed` already
+  const int cols = part == 2 ? inter : hidden, map_rows = pairs < kMaxPairs ? pairs : kMaxPairs;
+  __half *const transformed_second = static_cast<__half *>(transformed) + static_cast<size_t>(map_rows) * cols;
   if (block_begin == 0) {
-    PrefillInputKernel<<<((pairs < kMaxPairs ? pairs : kMaxPairs) + 7) / 8, 256, 0, stream>>>(
-        matrices, layer, part, groups, counts, input, gate, up, pair_rows, table, static_cast<__half *>(transformed), group_stride, pairs,
-        hidden, inter, FormatOfRate(rate), bad);
-    if (cudaGetLastError() != cudaSuccess)
-      return PADRA_INTERNAL;
+    for (int p = 0; p < (output_second ? 2 : 1); ++p) {
+      PrefillInputKernel<<<(map_rows + 7) / 8, 256, 0, stream>>>(matrices, layer, part + p, groups, counts, input, gate, up, pair_rows, table,
+                                                                 p ? transformed_second : static_cast<__half *>(transformed), group_stride,
+                                                                 pairs, hidden, inter, FormatOfRate(rate), bad);
+      if (cudaGetLastError() != cudaSuccess)
+        return PADRA_INTERNAL;
+    }
   }
   PrefillArgs a{};
   a.matrices = matrices, a.layer = layer, a.part = part, a.groups = groups, a.counts = counts;
   a.transformed = static_cast<const __half *>(transformed), a.output = output, a.group_stride = group_stride;
   a.pairs_total = pairs, a.hidden = hidden, a.inter = inter, a.bad = bad;
   a.block_begin = block_begin, a.block_count = block_count;
+  a.parts = output_second ? 2 : 1, a.output_second = output_second;
   if (ret) {
     if (part != 2 || ret->world < 1 || ret->world > kMaxRanks || ret->rank < 0 || ret->rank >= ret->world || ret->cap < 1 ||
         static_cast<long long>(ret->world) * ret->cap != pairs || !ret->bases)
@@ -844,17 +866,18 @@ static int LaunchPrefillGemm(const Matrix *matrices, int layer, int part, const 
   if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 1)
     return PADRA_INTERNAL;
   const dim3 grid(sms); // persistent: one CTA per SM
-  CUtensorMap map;
-  const int cols = part == 2 ? inter : hidden;
-  if (const int status = MakeActivationMap(&map, transformed, pairs < kMaxPairs ? pairs : kMaxPairs, cols); status != PADRA_OK)
+  CUtensorMap map, map_second;
+  if (const int status = MakeActivationMap(&map, transformed, map_rows, cols); status != PADRA_OK)
+    return status;
+  if (const int status = MakeActivationMap(&map_second, output_second ? transformed_second : transformed, map_rows, cols); status != PADRA_OK)
     return status;
   switch (rate) {
   case 3:
-    return LaunchGemm<3>(a, map, grid, stream);
+    return LaunchGemm<3>(a, map, map_second, grid, stream);
   case 4:
-    return LaunchGemm<4>(a, map, grid, stream);
+    return LaunchGemm<4>(a, map, map_second, grid, stream);
   case 6:
-    return LaunchGemm<6>(a, map, grid, stream);
+    return LaunchGemm<6>(a, map, map_second, grid, stream);
   default:
     return PADRA_UNSUPPORTED;
   }
@@ -868,6 +891,24 @@ int LaunchPrefillTensorMemory(const Matrix *matrices, int layer, int part, const
     return PADRA_INVALID_ARGUMENT;
   return LaunchPrefillGemm(matrices, layer, part, groups, counts, input, nullptr, output, gate, up, table, transformed, tokens,
                            tokens * kTopK, bad, stream, rate, hidden, inter);
+}
+
+int LaunchPrefillGateUp(const Matrix *matrices, int layer, const int *groups, const int *counts, const float *input,
+                        unsigned short *gate_output, unsigned short *up_output, void *transformed, int tokens, int *bad, cudaStream_t stream,
+                        int rate, int hidden, int inter) {
+  if (tokens < 1 || tokens > kMaxTokensPrefill || !up_output)
+    return PADRA_INVALID_ARGUMENT;
+  return LaunchPrefillGemm(matrices, layer, 0, groups, counts, input, nullptr, gate_output, nullptr, nullptr, nullptr, transformed, tokens,
+                           tokens * kTopK, bad, stream, rate, hidden, inter, nullptr, 0, 0, up_output);
+}
+
+int LaunchPrefillRowsGateUp(const Matrix *matrices, int layer, const int *groups, const int *counts, int group_stride, int rows,
+                            const unsigned short *input_rows, unsigned short *gate_output, unsigned short *up_output, void *transformed,
+                            int *bad, cudaStream_t stream, int rate, int hidden, int inter) {
+  if (!input_rows || !up_output)
+    return PADRA_INVALID_ARGUMENT;
+  return LaunchPrefillGemm(matrices, layer, 0, groups, counts, nullptr, input_rows, gate_output, nullptr, nullptr, nullptr, transformed,
+                           group_stride, rows, bad, stream, rate, hidden, inter, nullptr, 0, 0, up_output);
 }
 
 int LaunchPrefillRows(const Matrix *matrices, int layer, int part, const int *groups, const int *counts, int group_stride, int rows,

@@ -168,7 +168,7 @@ class KernelBackend:
                               counts=torch.empty(EXPERTS, dtype=torch.int32, device=dev),
                               gate=torch.empty((MAX_ROWS, i), dtype=torch.uint16, device=dev),
                               up=torch.empty((MAX_ROWS, i), dtype=torch.uint16, device=dev),
-                              transformed=torch.empty((MAX_ROWS, max(h, i)), dtype=torch.float16, device=dev))
+                              transformed=torch.empty((2 * MAX_ROWS, max(h, i)), dtype=torch.float16, device=dev))
         return self._work
 
     def plan(self, ids: torch.Tensor, owner: torch.Tensor, world: int) -> Plan:
@@ -196,12 +196,16 @@ class KernelBackend:
             n = min(MAX_ROWS, total - begin)
             B.check(self.lib.padra_ep_group_rows(B.ptr(ids[begin:begin + n]), B.ptr(w["groups"]), B.ptr(w["counts"]), n, n,
                                                  B.ptr(k.bad), stream), "padra_ep_group_rows")
-            for part, target in ((0, w["gate"]), (1, w["up"]), (2, down[begin:begin + n])):
-                B.check(self.lib.padra_exl3_prefill_rows_launch(
-                    k.t.descriptors.data_ptr(), layer, part, B.ptr(w["groups"]), B.ptr(w["counts"]), n, n,
-                    B.ptr(rows[begin:begin + n]), B.ptr(target), B.ptr(w["gate"]), B.ptr(w["up"]), B.ptr(k.table),
-                    B.ptr(w["transformed"]), B.ptr(k.bad), stream, k.t.rate, self.hidden, self.inter, 0, 0),
-                    "padra_exl3_prefill_rows_launch")
+            # gate and up as one launch (one list of work items), then down
+            B.check(self.lib.padra_exl3_prefill_rows_gate_up_launch(
+                k.t.descriptors.data_ptr(), layer, B.ptr(w["groups"]), B.ptr(w["counts"]), n, n, B.ptr(rows[begin:begin + n]),
+                B.ptr(w["gate"]), B.ptr(w["up"]), B.ptr(w["transformed"]), B.ptr(k.bad), stream, k.t.rate, self.hidden, self.inter),
+                "padra_exl3_prefill_rows_gate_up_launch")
+            B.check(self.lib.padra_exl3_prefill_rows_launch(
+                k.t.descriptors.data_ptr(), layer, 2, B.ptr(w["groups"]), B.ptr(w["counts"]), n, n,
+                B.ptr(rows[begin:begin + n]), B.ptr(down[begin:begin + n]), B.ptr(w["gate"]), B.ptr(w["up"]), B.ptr(k.table),
+                B.ptr(w["transformed"]), B.ptr(k.bad), stream, k.t.rate, self.hidden, self.inter, 0, 0),
+                "padra_exl3_prefill_rows_launch")
         return down
 
     def combine(self, plan: Plan, returned: torch.Tensor, routing: torch.Tensor, x: torch.Tensor) -> None:

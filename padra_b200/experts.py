@@ -314,10 +314,19 @@ class ExpertKernels:
                                                 self.t.rate, *self.dims)
         B.check(st, "padra_exl3_prefill_launch")
 
-    def prefill_layer(self, layer, ids, routing, normalized, x, tokens, stream=None, tensor_memory=True, overlap=True):
+    def prefill_gate_up(self, layer, sched, x, gate_bits, up_bits, transformed_both, tokens, stream=None):
+        """Gate and up of a chunk as one launch of the tensor-memory grouped GEMM (one list of work items)."""
+        groups, counts, _, _ = sched
+        st = self.lib.padra_exl3_prefill_gate_up_launch(self.t.descriptors.data_ptr(), layer, B.ptr(groups), B.ptr(counts), B.ptr(x),
+                                                        B.ptr(gate_bits), B.ptr(up_bits), B.ptr(transformed_both), tokens,
+                                                        B.ptr(self.bad), B.stream_handle(stream), self.t.rate, *self.dims)
+        B.check(st, "padra_exl3_prefill_gate_up_launch")
+
+    def prefill_layer(self, layer, ids, routing, normalized, x, tokens, stream=None, tensor_memory=True, overlap=True, merged=True):
         """gate, up, down (SwiGLU inside) and combine with residual for a prefill chunk; x updated in place.
-        overlap: the up projection runs on a second stream beside the gate projection (its input transform under the
-        gate GEMM, its first CTAs in the gate GEMM's tail); both join before the down projection."""
+        merged: gate and up are one launch (their work items form one list, which loads the SMs evenly).
+        Otherwise, overlap: the up projection runs on a second stream beside the gate projection (its input transform
+        under the gate GEMM, its first CTAs in the gate GEMM's tail); both join before the down projection."""
         dev, (hidden, inter) = self.t.device, self.dims
         pairs = tokens * TOPK
         key = ("prefill", tokens)
@@ -326,10 +335,13 @@ class ExpertKernels:
                                     torch.empty((pairs, inter), dtype=torch.uint16, device=dev),
                                     torch.empty((pairs, hidden), dtype=torch.uint16, device=dev),
                                     torch.empty((pairs, max(hidden, inter)), dtype=torch.float16, device=dev),
-                                    torch.empty((pairs, hidden), dtype=torch.float16, device=dev))
+                                    torch.empty((2 * pairs, hidden), dtype=torch.float16, device=dev))
         gate, up, down, transformed, transformed_up = self._workspace[key]
         sched = self.group_and_schedule(ids, tokens, stream)
-        if overlap and tensor_memory:
+        if merged and tensor_memory and tokens >= 4:
+            self.prefill_gate_up(layer, sched, normalized, gate, up, transformed_up, tokens, stream)
+            self.prefill_launch(layer, 2, ids, sched, normalized, down, gate, up, transformed, tokens, stream, tensor_memory)
+        elif overlap and tensor_memory:
             main = stream or torch.cuda.current_stream()
             side = self.side_stream()
             fork, join = torch.cuda.Event(), torch.cuda.Event()

@@ -91,6 +91,25 @@ def test_tensor_memory_gemm_large_imbalanced_chunk(oracle, gpu):
         assert_close_rows(gate[pair][None], want[None], f"gate row of pair {pair} vs oracle")
 
 
+@pytest.mark.parametrize("rate,hidden,inter,tokens", [(4, 512, 384, 600), (3, 256, 128, 37), (6, 384, 896, 200)])
+def test_gate_and_up_in_one_launch_equal_the_two_launches(gpu, rate, hidden, inter, tokens):
+    """The merged launch only reorders work items: every row of gate, up, down and x is bit-equal to the rows of the
+    part-by-part call sequence (inter 896 = seven output blocks: an item with a single block in each part)."""
+    from padra_b200.experts import bf16_values, zipf_routing
+
+    host, table, k = make(1, hidden, inter, rate, 77, gpu)
+    ids, w = zipf_routing(tokens, seed=5, device=gpu)
+    g = torch.Generator(device=gpu)
+    g.manual_seed(9)
+    dx = bf16_values(torch.randn((tokens, hidden), device=gpu, generator=g))
+    xa, xb = dx.clone(), dx.clone()
+    ga, ua, da = (t.clone() for t in k.prefill_layer(0, ids.reshape(-1), w.reshape(-1), dx, xa, tokens, merged=True))
+    gb, ub, db = k.prefill_layer(0, ids.reshape(-1), w.reshape(-1), dx, xb, tokens, merged=False)
+    torch.cuda.synchronize()
+    assert k.bad_flag() == 0
+    assert torch.equal(ga, gb) and torch.equal(ua, ub) and torch.equal(da, db) and torch.equal(xa, xb)
+
+
 def test_prefill_matches_decode_path(oracle, gpu):
     """The same tokens through the prefill entry points and through the decode layer call."""
     hidden, inter, tokens = 512, 256, 16
