@@ -8,15 +8,17 @@
 // things that bound the kernel: an SM pulls 16 KB of activations per 64-input stage for 256 output columns (half the L2
 // traffic per MAC of a 256-token x 128-output item), and every producer warp sees all four ring slots.
 //   * the weights are the MMA's N side.  Two sets of eight producer warps, one set per output block of the item and one
-//     warp per 16-output tile column, read packed words several stages ahead, decode 32 weights per lane in registers
-//     (codec.cuh) and store them as 16-byte rows of 8x8 FP16 core matrices into the canonical K-major, no-swizzle
-//     shared-memory layout: with the lane <-> (row pair, K-step) ownership of the codec the four 16-byte stores of a
-//     quarter-warp are 128 contiguous bytes.
+//     warp per 16-output tile column, read packed words three stages ahead, decode 32 weights per lane in registers
+//     (codec.cuh) and store them as 16-byte pieces of 128-byte rows (one row of 64 inputs per output) in the
+//     128-byte-swizzled K-major layout: with the lane <-> (row pair, K-step) ownership of the codec the eight lanes of a
+//     quarter-warp hit eight different pieces, so neither these stores nor the tensor cores' reads meet bank conflicts.
 //   * the tokens are the M side: the expert's transformed activation rows (FP16, written in expert-grouped order by
-//     PrefillInputKernel).  One elected producer thread fetches a stage's 128 rows x 64 inputs with ONE tensor copy
+//     PrefillInputKernel).  One thread of a copy warp fetches a stage's 128 rows x 64 inputs with ONE tensor copy
 //     (cp.async.bulk.tensor, 128-byte swizzle, completion counted in bytes on the stage's barrier); the sixteen decoding
 //     warps never touch the activations.  (Gathering them with 16-byte cp.async from those warps cost them three times
 //     as many cycles per stage as the decode itself.)
+//   * a launch may cover two parts (gate and up): their items then form one list and every item picks its part's
+//     matrices, tensor map and output.
 //   * one elected thread issues tcgen05.mma (M = 128 tokens, N = 256 outputs, K = 16), four per stage, and commits each
 //     stage back to the producers; a 4-stage ring of (32 KB weights + 16 KB activations) that runs on across items.
 //   * a thread of the four epilogue warps owns one TOKEN row of the accumulator, so the 128-point output Hadamard of
@@ -56,7 +58,7 @@ constexpr int kBufferColumns = 256;
 constexpr int kMaxPairs = 4096 * kTopK;              // grouped pairs (rows) one call works on
 constexpr int kMaxPairIndex = 1 << 20;              // pair indices may be sparse (received rows in per-source regions)
 constexpr int kMaxTiles = kExperts + kMaxPairs / kMaxTileN; // sum over experts of ceil(n_e / 256)
-constexpr int kAhead = 3;                           // own stages of packed words in flight per producer lane
+constexpr int kAhead = 2;                           // own stages of packed words in flight per producer lane
 constexpr unsigned long long kWaitLimitNs = 1000000000ull; // a wait that lasts a second has failed
 constexpr int kMaxTokensPrefill = 2048;
 
@@ -68,11 +70,8 @@ __device__ unsigned long long *g_prefill_trace = nullptr; // [stage record][8], 
       g_prefill_trace[static_cast<size_t>(record) * 8 + (slot)] = clock64();       \
     }                                                                              \
   } while (0)
-__device__ int g_prefill_variant = 0; // timing experiments: 1 no decode, 2 no weight stores, 4 no activation copies, 8 no MMAs
-#define PF_VARIANT(bit) (g_prefill_variant & (bit))
 #else
 #define PF_TRACE(record, slot)
-#define PF_VARIANT(bit) 0
 #endif
 
 struct TileInfo {
@@ -152,15 +151,10 @@ __device__ __forceinline__ bool BarrierWait(unsigned long long *bar, unsigned pa
       __nanosleep(backoff);
   }
 }
-__device__ __forceinline__ unsigned long long OperandDescriptor(unsigned smem_address, unsigned leading_bytes, unsigned stride_bytes) {
-  // K-major, no swizzle: 8x8 core matrices of 128 contiguous bytes; `leading` = distance between the two 16-byte
-  // K halves of a K16 step, `stride` = distance between 8-row groups.  Bits: [0,14) address>>4, [16,30) leading>>4,
-  // [32,46) stride>>4, [46,48) descriptor version 1 (sm_100), [61,64) layout 0 = no swizzle.
-  return static_cast<unsigned long long>((smem_address & 0x3ffffu) >> 4) | (static_cast<unsigned long long>(leading_bytes >> 4) << 16) |
-         (static_cast<unsigned long long>(stride_bytes >> 4) << 32) | (1ull << 46);
-}
 // K-major with 128-byte swizzle: rows of 128 bytes, eight-row groups 1024 bytes apart; a K16 step inside the 64-input row
-// is selected by moving the start address 32 bytes on.  Bits as above; layout 2 = SWIZZLE_128B, leading offset unused.
+// is selected by moving the start address 32 bytes on.  Bits: [0,14) address>>4, [16,30) leading offset>>4 (unused
+// here), [32,46) distance between eight-row groups>>4, [46,48) descriptor version 1 (sm_100), [61,64) layout 2 =
+// SWIZZLE_128B.
 __device__ __forceinline__ unsigned long long SwizzledOperandDescriptor(unsigned smem_address) {
   return static_cast<unsigned long long>((smem_address & 0x3ffffu) >> 4) | (1ull << 16) | (static_cast<unsigned long long>(1024 >> 4) << 32) |
          (1ull << 46) | (2ull << 61);
@@ -399,10 +393,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
           alive = BarrierWait(&sm.empty[s], (((q + i) / kStages) & 1) ^ 1, abort, 64);
           if (!alive)
             break;
-          if (PF_VARIANT(4)) {
-            BarrierArrive(&sm.full[s]);
-            continue;
-          }
           BarrierExpect(&sm.full[s], kStageBBytes);
           // rows past the expert's group are the next group's, or zero past the end of the tensor: they only reach
           // accumulator rows nobody reads
@@ -449,6 +439,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
 #pragma unroll
     for (int d = 0; d < kAhead; ++d)
       fetch(ahead[d]);
+    // where this lane's four 16-byte pieces go inside a weight stage (see the stores below): the same for every stage
+    unsigned store_offset[4];
+#pragma unroll
+    for (int f = 0; f < 4; ++f)
+      store_offset[f] = (set * 128 + column * 16 + (f & 1) * 8 + g) * 128 + (((2 * kstep + (f >> 1)) ^ g) << 4);
     bool alive = true;
     unsigned q = 0;        // stages this CTA has been through before the current item
     for (int sequence = 0; alive; ++sequence, q += stages) {
@@ -479,15 +474,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
           PF_TRACE(q + i, 0);
         const uint32_t previous = __shfl_sync(0xffffffffu, words[Rate - 1], (lane & 24) | ((lane + 7) & 7));
         uint32_t frag[4][4];
-        if (PF_VARIANT(1)) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-#pragma unroll
-            for (int f = 0; f < 4; ++f)
-              frag[c][f] = ((words[(c + f) % Rate] ^ previous) & 0x03ff03ffu) | 0x30003000u; // small finite halves
-        } else {
-          codec::Decode32<Rate>(words, previous, frag);
-        }
+        codec::Decode32<Rate>(words, previous, frag);
         if (ptid == 0)
           PF_TRACE(q + i, 1);
         // weights: this lane's four 16-byte pieces (fragment f: K half f>>1, output row g + 8*(f&1) of the warp's tile
@@ -495,13 +482,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
         // groups of 1024 bytes, the 16-byte piece index XORed with the row's low three bits.  The eight lanes of a quarter
         // warp (g = 0..7, one K16 step) hit eight different pieces: no bank conflicts, for these stores or for the MMA.
         unsigned char *a_stage = sm.a[s];
-        if (decodes && !PF_VARIANT(2)) {
+        if (decodes) {
 #pragma unroll
-          for (int f = 0; f < 4; ++f) {
-            const uint4 row = make_uint4(frag[0][f], frag[1][f], frag[2][f], frag[3][f]);
-            const int n = set * 128 + column * 16 + (f & 1) * 8 + g; // output row inside the stage's 256
-            *reinterpret_cast<uint4 *>(a_stage + n * 128 + (((2 * kstep + (f >> 1)) ^ g) << 4)) = row;
-          }
+          for (int f = 0; f < 4; ++f) // output row set*128 + column*16 + (f&1)*8 + g of the stage's 256
+            *reinterpret_cast<uint4 *>(a_stage + store_offset[f]) = make_uint4(frag[0][f], frag[1][f], frag[2][f], frag[3][f]);
         }
         // publish at once (release); the MMA thread orders these generic-proxy writes before its tensor-core reads
         // with a proxy fence after its wait, so nobody waits here for the copies
@@ -539,8 +523,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
           const unsigned w_base = SmemAddress(sm.a[s]), x_base = SmemAddress(sm.b[s]);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
-            if (PF_VARIANT(8) && (i > 0 || ks > 0))
-              continue;
             const unsigned long long x_desc = SwizzledOperandDescriptor(x_base + ks * 32);
             const unsigned long long w_desc = SwizzledOperandDescriptor(w_base + ks * 32);
             MmaSS(tmem + buffer * kBufferColumns, x_desc, w_desc, idesc, i > 0 || ks > 0);
@@ -936,9 +918,6 @@ int LaunchPrefillDownReturn(const Matrix *matrices, int layer, const int *groups
 } // namespace padra
 
 #ifdef PADRA_PREFILL_TRACE
-extern "C" __attribute__((visibility("default"))) int padra_debug_set_prefill_variant(int variant) {
-  return static_cast<int>(cudaMemcpyToSymbol(padra::g_prefill_variant, &variant, sizeof(variant)));
-}
 extern "C" __attribute__((visibility("default"))) int padra_debug_set_prefill_trace(unsigned long long *buffer) {
   return static_cast<int>(cudaMemcpyToSymbol(padra::g_prefill_trace, &buffer, sizeof(buffer)));
 }
