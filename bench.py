@@ -266,26 +266,25 @@ def decode_sweep_leg(dev, layers: int) -> list:
 
 
 def prefill_leg(k, dev, layers: int, tokens: int = 2048, passes: int = 3) -> dict:
-    """configs[3]: one prefill chunk per layer (grouping, three grouped projections with the decode fused in, SwiGLU, combine) over
-    `layers` layers of distinct weights, Zipf(1.1) routing; device time per chunk from CUDA events."""
+    """configs[3]: one prefill chunk per layer (routing from Zipf(1.1)-skewed logits, grouping, the grouped projections with the
+    decode fused in, SwiGLU, combine) over `layers` layers of distinct weights; device time per chunk from CUDA events."""
     import torch
-    from padra_b200.experts import bf16_values, zipf_routing
+    from padra_b200.experts import bf16_values, zipf_logits
 
     g = torch.Generator(device=dev)
     g.manual_seed(77)
     chunks = []
     for layer in range(layers):
-        ids, w = zipf_routing(tokens, seed=layer, device=dev)
-        chunks.append((layer, ids.reshape(-1), w.reshape(-1), bf16_values(torch.randn((tokens, HIDDEN), device=dev, generator=g)),
+        chunks.append((layer, zipf_logits(tokens, seed=layer, device=dev), bf16_values(torch.randn((tokens, HIDDEN), device=dev, generator=g)),
                        bf16_values(torch.randn((tokens, HIDDEN), device=dev, generator=g))))
     for c in chunks[:3]:
-        k.prefill_layer(*c, tokens)
+        k.prefill_chunk(*c, tokens)
     torch.cuda.synchronize(dev)
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(passes):
         for c in chunks:
-            k.prefill_layer(*c, tokens)
+            k.prefill_chunk(*c, tokens)
     b.record()
     torch.cuda.synchronize(dev)
     seconds = a.elapsed_time(b) / 1e3 / (passes * layers)
@@ -298,6 +297,9 @@ def prefill_leg(k, dev, layers: int, tokens: int = 2048, passes: int = 3) -> dic
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": burst, "unit": "TFLOP/s", "frac": achieved / burst,
                          "frac_of_sustained": achieved / sustained,
                          "peak_source": "measured (cuBLAS bf16 burst; the chunk is well under a second)" if data else "fallback"},
+            "launches_per_chunk": 6,
+            "chunk": "router logits -> residual stream: routing + grouping + schedule, gate+up input transform, gate+up grouped GEMM, "
+                     "down input transform (SwiGLU), down grouped GEMM, combine",
             "layers_rotated": layers, "passes": passes}
 
 

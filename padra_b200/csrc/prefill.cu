@@ -655,11 +655,15 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
 // x~ rows in expert-grouped order: row (offset of expert e) + i holds the transform of the i-th pair routed to e.
 // Parts 0/1: x~ = fp16(B(H128(x[token] * suh)))  (reference: src/cuda/expert_exl3_prefill_warp.cuh:14-57);
 // part 2: x = SwiGLU(gate[pair], up[pair]) first (expert_exl3_prefill_packed_activations.cuh:17-73).
-__global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices, int layer, int part, const int *groups, const int *counts,
-                                                          const float *input, const unsigned short *gate, const unsigned short *up,
-                                                          const unsigned short *pair_rows, const unsigned short *table,
-                                                          __half *transformed, int group_stride, int pairs, int hidden,
-                                                          int inter, int format, int *bad) {
+// A launch with gridDim.y == 2 transforms the rows for parts `first_part` and `first_part + 1` (gate and up: same input,
+// each part's own signs), the second part's rows `second_offset` halves behind the first's.
+__global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices, int layer, int first_part, const int *groups,
+                                                          const int *counts, const float *input, const unsigned short *gate,
+                                                          const unsigned short *up, const unsigned short *pair_rows,
+                                                          const unsigned short *table, __half *transformed, size_t second_offset,
+                                                          int group_stride, int pairs, int hidden, int inter, int format, int *bad) {
+  const int part = first_part + static_cast<int>(blockIdx.y);
+  transformed += blockIdx.y * second_offset;
   __shared__ int s_offset[kExperts + 1], s_half;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int cols = part == 2 ? inter : hidden, blocks = cols / 128;
@@ -818,13 +822,11 @@ static int LaunchPrefillGemm(const Matrix *matrices, int layer, int part, const 
   const int cols = part == 2 ? inter : hidden, map_rows = pairs < kMaxPairs ? pairs : kMaxPairs;
   __half *const transformed_second = static_cast<__half *>(transformed) + static_cast<size_t>(map_rows) * cols;
   if (block_begin == 0) {
-    for (int p = 0; p < (output_second ? 2 : 1); ++p) {
-      PrefillInputKernel<<<(map_rows + 7) / 8, 256, 0, stream>>>(matrices, layer, part + p, groups, counts, input, gate, up, pair_rows, table,
-                                                                 p ? transformed_second : static_cast<__half *>(transformed), group_stride,
-                                                                 pairs, hidden, inter, FormatOfRate(rate), bad);
-      if (cudaGetLastError() != cudaSuccess)
-        return PADRA_INTERNAL;
-    }
+    PrefillInputKernel<<<dim3((map_rows + 7) / 8, output_second ? 2 : 1), 256, 0, stream>>>(
+        matrices, layer, part, groups, counts, input, gate, up, pair_rows, table, static_cast<__half *>(transformed),
+        static_cast<size_t>(map_rows) * cols, group_stride, pairs, hidden, inter, FormatOfRate(rate), bad);
+    if (cudaGetLastError() != cudaSuccess)
+      return PADRA_INTERNAL;
   }
   PrefillArgs a{};
   a.matrices = matrices, a.layer = layer, a.part = part, a.groups = groups, a.counts = counts;

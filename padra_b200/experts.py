@@ -322,6 +322,34 @@ class ExpertKernels:
                                                         B.ptr(self.bad), B.stream_handle(stream), self.t.rate, *self.dims)
         B.check(st, "padra_exl3_prefill_gate_up_launch")
 
+    def prefill_chunk(self, layer, logits, normalized, x, tokens, stream=None):
+        """A prefill chunk from the router's logits to the updated residual stream in six launches: routing + grouping +
+        schedule, the gate and up input transforms, the gate+up grouped GEMM, the down input transform (SwiGLU inside), the
+        down grouped GEMM, the combine.  Buffers are reused from call to call (nothing is filled in between: the
+        scheduling kernel writes every count and every list entry that is read).  Returns ids and routing weights."""
+        dev, (hidden, inter) = self.t.device, self.dims
+        pairs = tokens * TOPK
+        key = ("chunk", tokens)
+        if key not in self._workspace:
+            self._workspace[key] = dict(
+                ids=torch.empty((tokens, TOPK), dtype=torch.int32, device=dev), weights=torch.empty((tokens, TOPK), dtype=torch.float32, device=dev),
+                groups=torch.full((EXPERTS * tokens,), -1, dtype=torch.int32, device=dev), counts=torch.zeros(EXPERTS, dtype=torch.int32, device=dev),
+                tiles=torch.zeros(((pairs + 31) // 32 + EXPERTS, 3), dtype=torch.int32, device=dev),
+                tile_count=torch.zeros(1, dtype=torch.int32, device=dev), ticket=torch.zeros(1, dtype=torch.int32, device=dev),
+                gate=torch.empty((pairs, inter), dtype=torch.uint16, device=dev), up=torch.empty((pairs, inter), dtype=torch.uint16, device=dev),
+                down=torch.empty((pairs, hidden), dtype=torch.uint16, device=dev),
+                transformed=torch.empty((2 * pairs, max(hidden, inter)), dtype=torch.float16, device=dev))
+        w = self._workspace[key]
+        st = B.stream_handle(stream)
+        B.check(self.lib.padra_route_group_schedule(B.ptr(logits), B.ptr(w["ids"]), B.ptr(w["weights"]), B.ptr(w["groups"]), B.ptr(w["counts"]),
+                                                    B.ptr(w["tiles"]), B.ptr(w["tile_count"]), tokens, B.ptr(w["ticket"]), B.ptr(self.bad), st),
+                "padra_route_group_schedule")
+        sched = (w["groups"], w["counts"], w["tiles"], w["tile_count"])
+        self.prefill_gate_up(layer, sched, normalized, w["gate"], w["up"], w["transformed"], tokens, stream)
+        self.prefill_launch(layer, 2, w["ids"], sched, normalized, w["down"], w["gate"], w["up"], w["transformed"], tokens, stream, True)
+        self.combine_packed(x, w["down"], w["weights"], tokens, True, stream)
+        return w["ids"], w["weights"]
+
     def prefill_layer(self, layer, ids, routing, normalized, x, tokens, stream=None, tensor_memory=True, overlap=True, merged=True):
         """gate, up, down (SwiGLU inside) and combine with residual for a prefill chunk; x updated in place.
         merged: gate and up are one launch (their work items form one list, which loads the SMs evenly).
@@ -453,6 +481,21 @@ def route_topk(logits: torch.Tensor):
     ids, order = torch.sort(ids, dim=-1)
     w = torch.gather(w, -1, order)
     return ids.to(torch.int32).contiguous(), bf16_values(w).contiguous()
+
+
+def zipf_logits(tokens: int, seed: int, s: float = 1.1, device="cuda", popularity_seed=None) -> torch.Tensor:
+    """Router logits [tokens][64] (FP32) whose top-8 are distributed like zipf_routing's ids: log of the Zipf(s)
+    popularity plus Gumbel noise (the eight largest of such sums are a sample without replacement with probability
+    proportional to the popularity)."""
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed if popularity_seed is None else popularity_seed)
+    rank = torch.randperm(EXPERTS, generator=g)
+    if popularity_seed is not None:
+        g.manual_seed(seed)
+    popularity = torch.empty(EXPERTS)
+    popularity[rank] = torch.arange(1, EXPERTS + 1, dtype=torch.float32) ** (-s)
+    u = torch.rand((tokens, EXPERTS), generator=g).clamp_(1e-9, 1 - 1e-9)
+    return (popularity.log() - torch.log(-torch.log(u))).to(torch.float32).to(device).contiguous()
 
 
 def zipf_routing(tokens: int, seed: int, s: float = 1.1, device="cuda", popularity_seed=None):

@@ -110,6 +110,29 @@ def test_gate_and_up_in_one_launch_equal_the_two_launches(gpu, rate, hidden, int
     assert torch.equal(ga, gb) and torch.equal(ua, ub) and torch.equal(da, db) and torch.equal(xa, xb)
 
 
+def test_routed_chunk_in_six_launches_equals_the_step_by_step_path(gpu):
+    """prefill_chunk (routing + grouping + schedule in one launch, merged gate+up, reused buffers) against route() followed
+    by prefill_layer's separate grouping and scheduling launches; twice, so that the second call meets used buffers."""
+    from padra_b200.experts import bf16_values, zipf_logits
+
+    hidden, inter, tokens = 512, 384, 600
+    host, table, k = make(1, hidden, inter, 4, 19, gpu)
+    g = torch.Generator(device=gpu)
+    g.manual_seed(4)
+    for seed in (1, 2):
+        logits = zipf_logits(tokens, seed=seed, device=gpu)
+        dx = bf16_values(torch.randn((tokens, hidden), device=gpu, generator=g))
+        xa, xb = dx.clone(), dx.clone()
+        ids, w = k.route(logits)
+        k.prefill_layer(0, ids.reshape(-1), w.reshape(-1), dx, xa, tokens, merged=False)
+        ids2, w2 = k.prefill_chunk(0, logits, dx, xb, tokens)
+        torch.cuda.synchronize()
+        assert k.bad_flag() == 0
+        assert torch.equal(ids, ids2) and torch.equal(w, w2) and torch.equal(xa, xb)
+    counts = torch.bincount(ids.reshape(-1).long(), minlength=64)
+    assert counts.max() > 4 * counts.min()  # the logits are skewed as asked
+
+
 def test_prefill_matches_decode_path(oracle, gpu):
     """The same tokens through the prefill entry points and through the decode layer call."""
     hidden, inter, tokens = 512, 256, 16
