@@ -394,7 +394,7 @@ def reference_kernels_leg(dev) -> dict | None:
 
 
 def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: str, passes: int, batch: int = 16384,
-                        chunk: int = 2048) -> dict:
+                        chunk: int = 2048, replicas: int = 1) -> dict:
     """configs[4]: a batch of 16384 tokens through `layers` MoE layers, experts sharded 64/world per rank by measured
     popularity, tokens split evenly over the ranks (strong scaling), dispatch and combine per layer and chunk.  Between
     layers the next input is the RMS-normalised residual stream (this library's norm kernel), so layer l+1 depends on
@@ -415,12 +415,14 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
     g.manual_seed(500 + rank)
     x0 = bf16_values(torch.randn((local, HIDDEN), device=dev, generator=g))
     norm_weight = torch.full((HIDDEN,), 0x3F80, dtype=torch.int16, device=dev)  # BF16 ones
-    routing, owners = {}, []
+    routing, owners, loads = {}, [], []
     for layer in range(layers):
         # popularity as a server would have measured it over earlier traffic: a long sample of the layer's routing
         sample, _ = zipf_routing(16384, seed=layer, device="cpu", popularity_seed=layer)
         popularity = np.bincount(sample.reshape(-1).numpy(), minlength=EXPERTS)
-        owners.append(EP.balanced_placement(popularity, world))
+        owners.append(EP.balanced_placement(popularity, world, replicas=replicas))
+        loads.append((EP.placement_load(popularity, EP.balanced_placement(popularity, world), world),
+                      EP.placement_load(popularity, owners[-1], world)))
         for c, n in chunks:
             ids, w = zipf_routing(n, seed=10007 * layer + (rank * local + c) // chunk + 1, device=dev, popularity_seed=layer)
             routing[layer, c] = (ids.reshape(-1), w.reshape(-1))
@@ -519,7 +521,10 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
         torch.cuda.synchronize(dev)
         times.append(a.elapsed_time(b) / 1e3)
         assert k.bad_flag() == 0 and bool(torch.isfinite(x).all()), "expert-parallel prefill raised the error flag"
-    return {"times": times, "batch": batch, "layers": layers, "chunk": chunk, "exchange": exchange, "parity_rows": parity_rows}
+    return {"times": times, "batch": batch, "layers": layers, "chunk": chunk, "exchange": exchange, "parity_rows": parity_rows,
+            "placement": {"second_copy_of_hottest_expert": bool(replicas and world > 1),
+                          "busiest_rank_over_mean_64_per_rank_exact": round(float(np.mean([a for a, _ in loads])), 4),
+                          "busiest_rank_over_mean_as_run": round(float(np.mean([b for _, b in loads])), 4)}}
 
 
 # ---- GPU arm ------------------------------------------------------------------------------------------------
@@ -640,7 +645,7 @@ def run_ours(args):
 
     ep = None
     if EXPERTS % world == 0 and not args.no_ep:
-        ep = expert_parallel_leg(k, dev, world, rank, layers, args.ep_exchange, passes=args.ep_passes)
+        ep = expert_parallel_leg(k, dev, world, rank, layers, args.ep_exchange, passes=args.ep_passes, replicas=args.ep_replicas)
     if world > 1:
         t = torch.tensor([seconds, e2e_seconds] + (ep["times"] if ep else []), device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -669,6 +674,7 @@ def run_ours(args):
             "n_gpus": world, "scaling": "strong", "exchange": ep["exchange"] if world > 1 else "none", "ms_per_batch": best * 1e3,
             "ms_per_batch_min": min(ep["times"]) * 1e3, "passes": len(ep["times"]), "tokens_per_s": ep["batch"] / best,
             "tflops_all_gpus": flops / best / 1e12, "parity_checked": world > 1, "parity_rows": ep["parity_rows"],
+            "placement": ep["placement"],
             "timing": "CUDA events per rank, max over ranks, median of passes"}
     line.update({
         "config": dict(base_config(layers), weight_bytes_resident=table.total_bytes,
@@ -736,6 +742,8 @@ def main():
     ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
                     help="expert-parallel exchange: kernels over NVLink peer memory (default) or NCCL all-to-all")
     ap.add_argument("--ep-passes", type=int, default=5, help="timed passes of the expert-parallel batch (median reported)")
+    ap.add_argument("--ep-replicas", type=int, default=1, choices=[0, 1],
+                    help="1: the most popular expert of a layer is held by two ranks where that lowers the busiest rank's load")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers of distinct weights to rotate over (profiling: fewer)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

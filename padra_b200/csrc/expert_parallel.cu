@@ -75,6 +75,8 @@ __global__ void __launch_bounds__(256) GroupRowsKernel(const int *ids, int *grou
 }
 
 // The send plan of one rank, one CTA: a stable counting sort of the pairs by destination rank owner[ids[pair]].
+// An owner entry may name two ranks (rank | (1 + second rank) << 8) for an expert whose weights two ranks hold: the
+// pairs of even tokens go to the first, those of odd tokens to the second, which halves the load of a very popular expert.
 //   order[j]      pair that travels as row j          position[pair]  row at which the pair's result comes back
 //   send_ids[j]   expert id of row j                  send_counts[r]  rows for rank r (64-bit, as the host API wants)
 // Thread t owns the 16 consecutive pairs from 16*t on; a scan over (destination, thread) keeps the order stable.
@@ -101,6 +103,10 @@ __global__ void __launch_bounds__(1024) PlanKernel(const int *ids, const int *ow
   for (int i = 0; i < kPer; ++i) {
     const int e = expert[i];
     int r = (e >= 0 && e < kExperts) ? s_owner[e] : -1;
+    if (r >= 0) { // low byte: the expert's rank; next byte: 1 + the rank of a second copy, which takes the odd tokens' pairs
+      const int second = (r >> 8) & 0xff;
+      r = (second && (((first + i) >> 3) & 1)) ? second - 1 : (r & 0xff);
+    }
     if ((i < per && first + i < pairs) && (r < 0 || r >= world)) {
       Raise(bad);
       r = -1;

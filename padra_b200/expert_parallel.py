@@ -27,20 +27,65 @@ EXPERTS, TOPK = 64, 8
 MAX_ROWS = 4096 * TOPK  # rows one grouped-projection call takes (a rank may receive more rows than it sends)
 
 
-def balanced_placement(popularity, world: int) -> np.ndarray:
+def balanced_placement(popularity, world: int, replicas: int = 0) -> np.ndarray:
     """owner[expert] for `world` ranks holding 64/world experts each: experts in order of falling popularity go to the
     rank with the least expected load that still has room (longest-processing-time-first).  Ties break towards the
-    lower rank, so every rank computes the same table from the same popularity."""
+    lower rank, so every rank computes the same table from the same popularity.
+
+    replicas = 1: the most popular expert is held by a second rank as well (one extra expert's weights on that rank,
+    3 MB at K4 2048/1024) and its pairs are split between the two by token parity; its entry is
+    rank | (1 + second rank) << 8 (see owner_ranks).  With Zipf(1.1) routing on eight ranks the busiest rank's load
+    drops from 1.155 to about 1.03 times the mean."""
     popularity = np.asarray(popularity, dtype=np.float64)
-    assert popularity.shape == (EXPERTS,) and EXPERTS % world == 0
-    room = np.full(world, EXPERTS // world)
+    assert popularity.shape == (EXPERTS,) and EXPERTS % world == 0 and replicas in (0, 1)
+
+    def place(split: int) -> np.ndarray:
+        # items in order of falling share; the split expert is two items of half its popularity, the second of which
+        # takes its rank's extra slot (no room needed) and must not meet the first
+        items = [(popularity[e] / 2 if e == split else popularity[e], int(e), 0) for e in range(EXPERTS)]
+        if split >= 0:
+            items.append((popularity[split] / 2, split, 1))
+        items.sort(key=lambda item: (-item[0], item[1], item[2]))
+        room, load = np.full(world, EXPERTS // world), np.zeros(world)
+        owner = np.empty(EXPERTS, dtype=np.int32)
+        for share, e, second in items:
+            if second:
+                candidates = np.array([r for r in range(world) if r != (owner[e] & 0xff)])
+            else:
+                candidates = np.where(room > 0)[0]
+            r = int(candidates[np.argmin(load[candidates])])
+            load[r] += share
+            if second:
+                owner[e] |= (r + 1) << 8
+            else:
+                owner[e], room[r] = r, room[r] - 1
+        return owner
+
+    exact = place(-1)
+    if not replicas or world < 2:
+        return exact
+    doubled = place(int(np.argmax(popularity)))
+    return doubled if placement_load(popularity, doubled, world) < placement_load(popularity, exact, world) else exact
+
+
+def owner_ranks(owner: np.ndarray):
+    """(first rank, second rank or -1) per expert of an owner table."""
+    owner = np.asarray(owner, dtype=np.int64)
+    return owner & 0xff, ((owner >> 8) & 0xff) - 1
+
+
+def placement_load(popularity, owner, world: int) -> float:
+    """Expected load of the busiest rank over the mean, for pairs drawn with the given popularity."""
+    popularity = np.asarray(popularity, dtype=np.float64)
+    first, second = owner_ranks(owner)
     load = np.zeros(world)
-    owner = np.empty(EXPERTS, dtype=np.int32)
-    for e in np.argsort(-popularity, kind="stable"):
-        candidates = np.where(room > 0)[0]
-        r = candidates[np.argmin(load[candidates])]
-        owner[e], load[r], room[r] = r, load[r] + popularity[e], room[r] - 1
-    return owner
+    for e in range(EXPERTS):
+        if second[e] >= 0:
+            load[first[e]] += popularity[e] / 2
+            load[second[e]] += popularity[e] / 2
+        else:
+            load[first[e]] += popularity[e]
+    return float(load.max() / load.mean())
 
 
 def contiguous_placement(world: int) -> np.ndarray:
@@ -58,7 +103,10 @@ class Plan:
 def make_plan(ids: torch.Tensor, owner: torch.Tensor, world: int) -> Plan:
     """ids [pairs] int32 expert ids in (token, slot) order; owner [64] on the same device."""
     flat = ids.reshape(-1).long()
-    dest = owner[flat]
+    entry = owner[flat].long()
+    second = (entry >> 8) & 0xff  # an expert held by two ranks: odd tokens' pairs go to the second
+    odd_token = (torch.arange(flat.numel(), device=flat.device) >> 3) & 1
+    dest = torch.where((second > 0) & (odd_token == 1), second - 1, entry & 0xff)
     order = torch.sort(dest, stable=True).indices
     position = torch.empty_like(order)
     position[order] = torch.arange(order.numel(), device=order.device)

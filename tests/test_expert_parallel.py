@@ -29,6 +29,34 @@ def test_balanced_placement_fills_every_rank_and_balances():
     assert (EP.balanced_placement(popularity, 8) == EP.balanced_placement(popularity, 8)).all()
 
 
+def test_a_second_copy_of_the_hottest_expert_lowers_the_busiest_rank():
+    from padra_b200.experts import zipf_routing
+
+    ids, _ = zipf_routing(16384, seed=3, device="cpu")
+    popularity = np.bincount(ids.reshape(-1).numpy(), minlength=64).astype(np.float64)
+    for world in (2, 4, 8):
+        exact = EP.balanced_placement(popularity, world)
+        doubled = EP.balanced_placement(popularity, world, replicas=1)
+        first, second = EP.owner_ranks(doubled)
+        hottest = int(np.argmax(popularity))
+        assert np.bincount(first, minlength=world).tolist() == [64 // world] * world
+        assert EP.placement_load(popularity, doubled, world) <= EP.placement_load(popularity, exact, world) + 1e-12
+        if world == 8:  # the copy is only made where it helps
+            assert (second >= 0).sum() == 1 and second[hottest] >= 0 and second[hottest] != first[hottest]
+    assert EP.placement_load(popularity, EP.balanced_placement(popularity, 8), 8) > 1.12
+    assert EP.placement_load(popularity, EP.balanced_placement(popularity, 8, replicas=1), 8) < 1.06
+    # the plan sends the even tokens' pairs of that expert to the first rank and the odd tokens' to the second
+    owner = EP.balanced_placement(popularity, 8, replicas=1)
+    first, second = EP.owner_ranks(owner)
+    chunk = ids[:256].reshape(-1)
+    plan = EP.make_plan(chunk, torch.from_numpy(owner.astype(np.int64)), 8)
+    dest = np.repeat(np.arange(8), plan.send_counts.numpy())
+    for row, pair in enumerate(plan.order.numpy()):
+        e = int(chunk[pair])
+        want = second[e] if second[e] >= 0 and (pair >> 3) & 1 else first[e]
+        assert dest[row] == want
+
+
 def test_plan_is_a_stable_sort_by_destination():
     g = torch.Generator().manual_seed(5)
     ids = torch.stack([torch.randperm(64, generator=g)[:8] for _ in range(40)]).to(torch.int32)
@@ -140,7 +168,7 @@ def test_ranks_on_one_gpu_equal_the_single_gpu_prefill(oracle, gpu, world, chunk
     table = ExpertTable(1, hidden, inter, rate, gpu).fill_from_host(host)
     hub = EP.LoopbackHub(world)
     popularity = np.arange(1, 65, dtype=np.float64) ** -1.1
-    owner = EP.balanced_placement(popularity, world)
+    owner = EP.balanced_placement(popularity, world, replicas=1 if world > 2 else 0)  # a second copy of expert 0 on 4 and 8 ranks
     kernels = [ExpertKernels(table) for _ in range(world)]
     tokens *= chunks
     inputs = [_inputs(oracle, r, tokens, hidden) for r in range(world)]
@@ -198,7 +226,7 @@ def test_peer_memory_exchange_on_one_gpu_equals_the_single_gpu_prefill(oracle, g
     total = EP.PeerExchangePrefill.exchange_bytes(lib, world, cap, hidden)
     blocks = [torch.zeros(total, dtype=torch.uint8, device=gpu) for _ in range(world)]
     popularity = np.arange(1, 65, dtype=np.float64) ** -1.1
-    owner = EP.balanced_placement(popularity, world)
+    owner = EP.balanced_placement(popularity, world, replicas=1 if split_return else 0)  # with and without a second copy
     kernels = [ExpertKernels(table) for _ in range(world)]
     inputs = [_inputs(oracle, r, tokens, hidden) for r in range(world)]
     barrier = threading.Barrier(world)
@@ -239,15 +267,15 @@ def test_peer_memory_exchange_on_one_gpu_equals_the_single_gpu_prefill(oracle, g
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("world,tokens", [(1, 8), (2, 333), (8, 2048)])
-def test_plan_kernel_equals_the_host_plan(gpu, world, tokens):
+@pytest.mark.parametrize("world,tokens,replicas", [(1, 8, 0), (2, 333, 1), (8, 2048, 0), (8, 2048, 1)])
+def test_plan_kernel_equals_the_host_plan(gpu, world, tokens, replicas):
     from padra_b200.experts import ExpertKernels, ExpertTable, zipf_routing
 
     table = ExpertTable(1, 256, 128, 4, gpu).fill_random(1)
     backend = EP.KernelBackend(ExpertKernels(table))
     ids, _ = zipf_routing(tokens, seed=world, device=gpu)
     popularity = np.bincount(ids.reshape(-1).cpu().numpy(), minlength=64)
-    owner = EP.balanced_placement(popularity, world)
+    owner = EP.balanced_placement(popularity, world, replicas=replicas)
     want = EP.make_plan(ids.reshape(-1), torch.from_numpy(owner.astype(np.int64)).to(gpu), world)
     got = backend.plan(ids.reshape(-1), torch.from_numpy(owner).to(gpu), world)
     torch.cuda.synchronize()
