@@ -94,6 +94,14 @@ inline void PrefillLaunch(const mellum16::DeviceMatrix *m, int layer, int part, 
   Check(padra_exl3_prefill_launch(M(m), layer, part, ids, groups, counts, reinterpret_cast<const padra_tile *>(tiles), tile_count, in,
                                   out, gate, up, table, workspace, tokens, bad, s, stats, wide ? 1 : 0, rate, kHidden, kInter));
 }
+// The gate and up launches of a prefill chunk (parts 0 and 1 of the call above, src/cuda/inference.cu:3896-3907) as one:
+// both parts' work items form one list.  `workspace` holds 2 * tokens * 8 * 2304 halves.
+inline void PrefillGateUpLaunch(const mellum16::DeviceMatrix *m, int layer, const int *groups, const int *counts, const float *in,
+                                unsigned short *gate_out, unsigned short *up_out, __half *workspace, int tokens, int *bad,
+                                cudaStream_t s, int rate) {
+  Check(padra_exl3_prefill_gate_up_launch(M(m), layer, groups, counts, in, gate_out, up_out, workspace, tokens, bad, s, rate, kHidden,
+                                          kInter));
+}
 // exl3_packed_activations::Combine, src/cuda/expert_exl3_prefill_packed_activations.cuh:86-103
 inline void CombinePacked(float *x, const unsigned short *down, const float *w, int tokens, int *bad, bool residual, cudaStream_t s) {
   Check(padra_combine_packed(x, down, w, tokens, bad, residual ? 1 : 0, kHidden, s));
