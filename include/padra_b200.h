@@ -263,12 +263,17 @@ PADRA_API int padra_exl3_expert_launch(const padra_matrix *matrices, int layer, 
  * x [tokens][hidden] the residual stream updated in place.  workspace must hold
  * padra_exl3_moe_decode_workspace_bytes() bytes; one workspace serves one stream at a time.
  *
- * padra_exl3_moe_decode_layer enqueues two launches: the split-K projection of gate+up, whose CTA that delivers the
- * last K-slice of an (expert, 128-output block) runs the block's epilogue (SwiGLU and the down input transform), and the
- * split-K projection of down with the combine done the same way.  The ticket counters at the start of the workspace must
- * be zero before the first call on it: call padra_exl3_moe_decode_workspace_init once after allocating it (it zero-fills
- * the workspace; stream-ordered, not graph-captured work of every step).  Every call leaves the counters zero again, also
- * when it raised *bad. */
+ * padra_exl3_moe_decode_layer enqueues two launches that overlap on the GPU: the split-K projection of gate+up, and the
+ * split-K projection of down, whose CTAs wait (bounded) for the gate/up blocks they need, apply SwiGLU and the down input
+ * transform to them, and whose last-arriving CTA per 128-output block combines.  (Several tokens: the gate/up CTA that
+ * delivers a block's last K-slice runs that epilogue instead.)  The counters at the start of the workspace must be zero
+ * before the first call on it: call padra_exl3_moe_decode_workspace_init once after allocating it (it zero-fills the
+ * workspace; stream-ordered, not graph-captured work of every step).  Every call leaves the counters zero again, also
+ * when it raised *bad.
+ * Stream order: ids, routing, normalized, x and *bad are read and written in stream order like any kernel's arguments.
+ * `matrices` (the descriptor table) and the packed weights and sidecars it points to are model state: the launches
+ * are programmatic dependents of what precedes them on the stream and read that state BEFORE the preceding work has
+ * finished, so it must not be written by work that is still in flight on the stream when the call is made. */
 PADRA_API size_t padra_exl3_moe_decode_workspace_bytes(int tokens, int hidden, int inter);
 PADRA_API int padra_exl3_moe_decode_workspace_init(void *workspace, size_t workspace_bytes, padra_stream stream);
 PADRA_API int padra_exl3_moe_decode_layer(const padra_matrix *matrices, int layer, const int *ids,
