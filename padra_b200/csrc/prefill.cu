@@ -622,15 +622,17 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
           if (n < valid) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              unsigned packed[4];
+              unsigned packed[4], exponents = 0;
 #pragma unroll
               for (int j = 0; j < 8; j += 2) {
-                const float y0 = RoundBF16(__fmul_rn(__fmul_rn(v[q][j], kHadamardScale), scale[32 * q + c0 + j]));
-                const float y1 = RoundBF16(__fmul_rn(__fmul_rn(v[q][j + 1], kHadamardScale), scale[32 * q + c0 + j + 1]));
-                if (!isfinite(y0) || !isfinite(y1))
-                  Raise(a.bad);
-                packed[j >> 1] = static_cast<unsigned>(BF16Bits(y0)) | (static_cast<unsigned>(BF16Bits(y1)) << 16);
+                // two outputs rounded to BF16 by one conversion; a BF16 with all exponent bits set is not finite
+                const __nv_bfloat162 pair = __floats2bfloat162_rn(__fmul_rn(__fmul_rn(v[q][j], kHadamardScale), scale[32 * q + c0 + j]),
+                                                                  __fmul_rn(__fmul_rn(v[q][j + 1], kHadamardScale), scale[32 * q + c0 + j + 1]));
+                packed[j >> 1] = *reinterpret_cast<const unsigned *>(&pair);
+                exponents |= ((packed[j >> 1] & 0x7f80u) == 0x7f80u) | ((packed[j >> 1] & 0x7f800000u) == 0x7f800000u);
               }
+              if (exponents)
+                Raise(a.bad);
               *reinterpret_cast<uint4 *>(out + 32 * q + c0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
           }

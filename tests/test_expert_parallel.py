@@ -168,7 +168,9 @@ def test_ranks_on_one_gpu_equal_the_single_gpu_prefill(oracle, gpu, world, chunk
     table = ExpertTable(1, hidden, inter, rate, gpu).fill_from_host(host)
     hub = EP.LoopbackHub(world)
     popularity = np.arange(1, 65, dtype=np.float64) ** -1.1
-    owner = EP.balanced_placement(popularity, world, replicas=1 if world > 2 else 0)  # a second copy of expert 0 on 4 and 8 ranks
+    owner = EP.balanced_placement(popularity, world)
+    if world > 2:  # a second copy of expert 0 on another rank
+        owner[0] |= ((int(owner[0]) + 1) % world + 1) << 8
     kernels = [ExpertKernels(table) for _ in range(world)]
     tokens *= chunks
     inputs = [_inputs(oracle, r, tokens, hidden) for r in range(world)]
@@ -226,7 +228,9 @@ def test_peer_memory_exchange_on_one_gpu_equals_the_single_gpu_prefill(oracle, g
     total = EP.PeerExchangePrefill.exchange_bytes(lib, world, cap, hidden)
     blocks = [torch.zeros(total, dtype=torch.uint8, device=gpu) for _ in range(world)]
     popularity = np.arange(1, 65, dtype=np.float64) ** -1.1
-    owner = EP.balanced_placement(popularity, world, replicas=1 if split_return else 0)  # with and without a second copy
+    owner = EP.balanced_placement(popularity, world)
+    if split_return:  # expert 0 (in every token's top-8 here more often than any other) held by two ranks
+        owner[0] |= ((int(owner[0]) + 1) % world + 1) << 8
     kernels = [ExpertKernels(table) for _ in range(world)]
     inputs = [_inputs(oracle, r, tokens, hidden) for r in range(world)]
     barrier = threading.Barrier(world)
