@@ -420,7 +420,7 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
         # popularity as a server would have measured it over earlier traffic: a long sample of the layer's routing
         sample, _ = zipf_routing(16384, seed=layer, device="cpu", popularity_seed=layer)
         popularity = np.bincount(sample.reshape(-1).numpy(), minlength=EXPERTS)
-        owners.append(EP.balanced_placement(popularity, world, replicas=replicas))
+        owners.append(EP.balanced_placement(popularity, world, replicas=min(replicas, 1), force=replicas == 2))
         loads.append((EP.placement_load(popularity, EP.balanced_placement(popularity, world), world),
                       EP.placement_load(popularity, owners[-1], world)))
         for c, n in chunks:
@@ -742,8 +742,9 @@ def main():
     ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
                     help="expert-parallel exchange: kernels over NVLink peer memory (default) or NCCL all-to-all")
     ap.add_argument("--ep-passes", type=int, default=5, help="timed passes of the expert-parallel batch (median reported)")
-    ap.add_argument("--ep-replicas", type=int, default=1, choices=[0, 1],
-                    help="1: the most popular expert of a layer is held by two ranks where that lowers the busiest rank's load")
+    ap.add_argument("--ep-replicas", type=int, default=1, choices=[0, 1, 2],
+                    help="1: the most popular expert of a layer is held by two ranks where that lowers the busiest rank's load; "
+                         "2: held by two ranks in any case (exercises the path on two or four GPUs)")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers of distinct weights to rotate over (profiling: fewer)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

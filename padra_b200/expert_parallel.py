@@ -27,7 +27,7 @@ EXPERTS, TOPK = 64, 8
 MAX_ROWS = 4096 * TOPK  # rows one grouped-projection call takes (a rank may receive more rows than it sends)
 
 
-def balanced_placement(popularity, world: int, replicas: int = 0) -> np.ndarray:
+def balanced_placement(popularity, world: int, replicas: int = 0, force: bool = False) -> np.ndarray:
     """owner[expert] for `world` ranks holding 64/world experts each: experts in order of falling popularity go to the
     rank with the least expected load that still has room (longest-processing-time-first).  Ties break towards the
     lower rank, so every rank computes the same table from the same popularity.
@@ -65,7 +65,8 @@ def balanced_placement(popularity, world: int, replicas: int = 0) -> np.ndarray:
     if not replicas or world < 2:
         return exact
     doubled = place(int(np.argmax(popularity)))
-    return doubled if placement_load(popularity, doubled, world) < placement_load(popularity, exact, world) else exact
+    # force: keep the copy even where it does not help (to exercise the path on few ranks)
+    return doubled if force or placement_load(popularity, doubled, world) < placement_load(popularity, exact, world) else exact
 
 
 def owner_ranks(owner: np.ndarray):
