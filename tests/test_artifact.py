@@ -143,9 +143,9 @@ def test_sha256_of_the_cpp_reader_matches_hashlib(tmp_path, host_tool):
 
 def test_forwarders_header_compiles(tmp_path):
     """padra_b200/host/bind.hpp against the reference's own DeviceMatrix and Tile declarations when the reference checkout
-    is present (PADRA_REFERENCE, default /root/reference), else against the layout-identical stand-ins; every forwarder
+    is present (PADRA_REFERENCE, else a directory `reference` beside the repository), else against the layout-identical stand-ins; every forwarder
     is instantiated."""
-    reference = Path(os.environ.get("PADRA_REFERENCE", "/root/reference"))
+    reference = Path(os.environ.get("PADRA_REFERENCE", str(Path(__file__).resolve().parents[2] / "reference")))
     tile_header = reference / "src" / "runtime" / "exl3_masked_schedule.h"
     source = tmp_path / "forwarders.cpp"
     if tile_header.exists():
