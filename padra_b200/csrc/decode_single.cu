@@ -276,14 +276,15 @@ template <int Rate> __global__ void __launch_bounds__(kThreads, 4) SingleDownKer
   PADRA_TRACE(a.trace, 1);
   Stream<Rate> stream;
   uint32_t fetched[4][Rate] = {};
-  uint2 suh_bits = make_uint2(0u, 0u), svh_bits = make_uint2(0u, 0u);
+  uint2 svh_bits = make_uint2(0u, 0u);
+  unsigned short suh_early = 0;
   if (work) {
     stream.Set(m, k_begin, nb * 8 + warp, lane);
 #pragma unroll
     for (int d = 0; d < 4; ++d)
       stream.Load(d < rounds ? d : rounds - 2 + (d & 1), fetched[d]);
-    if (warp < blocks)
-      suh_bits = __ldg(reinterpret_cast<const uint2 *>(m.suh + k_begin + warp * 128 + lane * 4));
+    if (tid < span) // the down matrix's input sign of the element this thread takes through the SwiGLU
+      suh_early = __ldg(m.suh + k_begin + tid);
     if (slice == 0 && warp == 7)
       svh_bits = __ldg(reinterpret_cast<const uint2 *>(m.svh + nb * 128 + lane * 4));
   }
@@ -299,14 +300,19 @@ template <int Rate> __global__ void __launch_bounds__(kThreads, 4) SingleDownKer
       Raise(a.bad);
     flagged = 1;
   }
-  // ---- the gate/up epilogue of this slice's 128-input blocks: one warp per block ----
+  // ---- the gate/up epilogue of this slice's 128-input blocks ----
+  // Sums and Hadamard transforms need a block's 128 values in one warp (one warp per block); the SwiGLU between them
+  // is elementwise and its exact exponential is a long dependent chain, so it is spread over all the CTA's threads, one
+  // element each, instead of four in a row in the lanes of two warps.
   __half *xs = reinterpret_cast<__half *>(smem);
-  if (work && !s_expired)
+  float *s_gate = reinterpret_cast<float *>(smem + static_cast<size_t>(span) * sizeof(__half)), *s_up = s_gate + span, *s_act = s_up + span;
+  const bool recompute = work && !s_expired; // uniform over the CTA
+  if (recompute)
     for (int block = warp; block < blocks; block += 8) {
       const int out = k_begin + block * 128 + lane * 4; // this lane's four intermediate channels
       const float *pg = a.gateup + (static_cast<size_t>(slot) * 2 + 0) * a.slices_gateup * a.inter + out;
       const float *pu = a.gateup + (static_cast<size_t>(slot) * 2 + 1) * a.slices_gateup * a.inter + out;
-      float svg[4], svu[4], shd[4];
+      float svg[4], svu[4];
       const uint2 sg = __ldcg(reinterpret_cast<const uint2 *>(a.sidecars + (static_cast<size_t>(slot) * 2 + 0) * a.inter + out));
       const uint2 su = __ldcg(reinterpret_cast<const uint2 *>(a.sidecars + (static_cast<size_t>(slot) * 2 + 1) * a.inter + out));
       float gsum[4] = {0.f, 0.f, 0.f, 0.f}, usum[4] = {0.f, 0.f, 0.f, 0.f};
@@ -325,27 +331,39 @@ template <int Rate> __global__ void __launch_bounds__(kThreads, 4) SingleDownKer
             usum[0] += vu[s].x, usum[1] += vu[s].y, usum[2] += vu[s].z, usum[3] += vu[s].w;
           }
       }
+      PADRA_TRACE(a.trace, 9);
       Unpack4(sg, svg);
       Unpack4(su, svu);
-      if (block >= 8)
-        suh_bits = __ldg(reinterpret_cast<const uint2 *>(m.suh + out));
-      Unpack4(suh_bits, shd);
       WarpHadamard128(gsum);
       WarpHadamard128(usum);
-      float v[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float gate = RoundBF16(__fmul_rn(gsum[i], svg[i]));
-        const float up = RoundBF16(__fmul_rn(usum[i], svu[i]));
-        const bool finite = isfinite(gate) && isfinite(up);
-        const float act = RoundBF16(__fmul_rn(SiluRounded(finite ? gate : 0.f), up));
-        if (!finite || !isfinite(act)) {
-          if (!flagged) // a flag raised earlier explains garbage here; only a fresh failure is reported
-            Raise(a.bad);
-          flagged = 1;
-        }
-        v[i] = __fmul_rn(act, shd[i]);
+      float4 gate, up;
+      gate.x = RoundBF16(__fmul_rn(gsum[0], svg[0])), gate.y = RoundBF16(__fmul_rn(gsum[1], svg[1]));
+      gate.z = RoundBF16(__fmul_rn(gsum[2], svg[2])), gate.w = RoundBF16(__fmul_rn(gsum[3], svg[3]));
+      up.x = RoundBF16(__fmul_rn(usum[0], svu[0])), up.y = RoundBF16(__fmul_rn(usum[1], svu[1]));
+      up.z = RoundBF16(__fmul_rn(usum[2], svu[2])), up.w = RoundBF16(__fmul_rn(usum[3], svu[3]));
+      *reinterpret_cast<float4 *>(s_gate + block * 128 + lane * 4) = gate;
+      *reinterpret_cast<float4 *>(s_up + block * 128 + lane * 4) = up;
+      PADRA_TRACE(a.trace, 10);
+    }
+  __syncthreads();
+  if (recompute)
+    for (int e = tid; e < span; e += kThreads) { // one element per thread at the graded shape
+      const float gate = s_gate[e], up = s_up[e];
+      const bool finite = isfinite(gate) && isfinite(up);
+      const float act = RoundBF16(__fmul_rn(SiluRounded(finite ? gate : 0.f), up));
+      if (!finite || !isfinite(act)) {
+        if (!flagged) // a flag raised earlier explains garbage here; only a fresh failure is reported
+          Raise(a.bad);
+        flagged = 1;
       }
+      s_act[e] = __fmul_rn(act, HalfBitsToFloat(e == tid ? suh_early : __ldg(m.suh + k_begin + e)));
+    }
+  __syncthreads();
+  PADRA_TRACE(a.trace, 11);
+  if (recompute)
+    for (int block = warp; block < blocks; block += 8) {
+      const float4 in = *reinterpret_cast<const float4 *>(s_act + block * 128 + lane * 4);
+      float v[4] = {in.x, in.y, in.z, in.w};
       WarpHadamard128(v);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -475,7 +493,8 @@ template <int Rate> int LaunchSingle(const SingleArgs &a, unsigned launches, cud
   if (status != PADRA_OK)
     return status;
   if (launches & 2u) {
-    const size_t smem = static_cast<size_t>(a.inter / a.slices_down) * sizeof(__half);
+    // the slice's transformed input row, and three float rows of the gate/up epilogue (gate, up, activation)
+    const size_t smem = static_cast<size_t>(a.inter / a.slices_down) * (sizeof(__half) + 3 * sizeof(float));
     if (smem > 36 * 1024 && cudaFuncSetAttribute(SingleDownKernel<Rate>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  static_cast<int>(smem)) != cudaSuccess)
       return PADRA_RESOURCE_EXHAUSTED;
