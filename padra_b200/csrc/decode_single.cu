@@ -210,11 +210,12 @@ template <int Rate> __global__ void __launch_bounds__(kThreads, 4) SingleGateUpK
     if (slice == 0 && warp == 7)
       *reinterpret_cast<uint2 *>(a.sidecars + (static_cast<size_t>(slot) * 2 + part) * a.inter + nb * 128 + lane * 4) = svh_bits;
   }
-  // delivered (or given up): the down kernel's CTAs that need this block count the arrivals
-  __threadfence();
-  __syncthreads();
-  if (tid == 0 && a.ready)
-    atomicAdd(a.ready + slot * kMaxBlocks + nb, 1u);
+  // delivered (or given up): the down kernel's CTAs that need this block count the arrivals.  Every warp counts itself
+  // as soon as its own stores are out (a release at device scope behind the warp's barrier), without waiting for the
+  // CTA's other warps.
+  __syncwarp();
+  if (lane == 0 && a.ready)
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.ready + slot * kMaxBlocks + nb) : "memory");
   PADRA_TRACE(a.trace, 6);
 }
 
@@ -289,26 +290,31 @@ template <int Rate> __global__ void __launch_bounds__(kThreads, 4) SingleDownKer
       svh_bits = __ldg(reinterpret_cast<const uint2 *>(m.svh + nb * 128 + lane * 4));
   }
   PADRA_TRACE(a.trace, 2);
-  // ---- the gate+up sums of this slice's blocks: wait for their 2 x slices producers each ----
-  if (tid < blocks && !WaitForArrivals(a.ready + slot * kMaxBlocks + k_begin / 128 + tid, 2u * a.slices_gateup))
-    s_expired = 1;
-  __syncthreads();
-  PADRA_TRACE(a.trace, 3);
-  int flagged = LoadFlag(a.bad);
-  if (s_expired) {
-    if (!tid)
-      Raise(a.bad);
-    flagged = 1;
-  }
+  // ---- the gate+up sums of this slice's blocks: the warp that sums a block waits for the block's producers (every warp
+  // of 2 x slices CTAs counts itself), then reads the error flag, which a producer raises before it counts itself ----
+  const unsigned producers = 2u * a.slices_gateup * (kThreads / 32);
+  int flagged = 0;
   // ---- the gate/up epilogue of this slice's 128-input blocks ----
   // Sums and Hadamard transforms need a block's 128 values in one warp (one warp per block); the SwiGLU between them
   // is elementwise and its exact exponential is a long dependent chain, so it is spread over all the CTA's threads, one
   // element each, instead of four in a row in the lanes of two warps.
   __half *xs = reinterpret_cast<__half *>(smem);
   float *s_gate = reinterpret_cast<float *>(smem + static_cast<size_t>(span) * sizeof(__half)), *s_up = s_gate + span, *s_act = s_up + span;
-  const bool recompute = work && !s_expired; // uniform over the CTA
-  if (recompute)
+  if (work)
     for (int block = warp; block < blocks; block += 8) {
+      int arrived = 1;
+      if (lane == 0 && !WaitForArrivals(a.ready + slot * kMaxBlocks + k_begin / 128 + block, producers)) {
+        s_expired = 1;
+        Raise(a.bad);
+        arrived = 0;
+      }
+      if (!__shfl_sync(0xffffffffu, arrived, 0)) {
+        flagged = 1;
+        continue;
+      }
+      if (block == warp)
+        PADRA_TRACE(a.trace, 3);
+      flagged |= LoadFlag(a.bad);
       const int out = k_begin + block * 128 + lane * 4; // this lane's four intermediate channels
       const float *pg = a.gateup + (static_cast<size_t>(slot) * 2 + 0) * a.slices_gateup * a.inter + out;
       const float *pu = a.gateup + (static_cast<size_t>(slot) * 2 + 1) * a.slices_gateup * a.inter + out;
@@ -346,6 +352,7 @@ template <int Rate> __global__ void __launch_bounds__(kThreads, 4) SingleDownKer
       PADRA_TRACE(a.trace, 10);
     }
   __syncthreads();
+  const bool recompute = work && !s_expired; // uniform over the CTA
   if (recompute)
     for (int e = tid; e < span; e += kThreads) { // one element per thread at the graded shape
       const float gate = s_gate[e], up = s_up[e];
@@ -394,12 +401,15 @@ template <int Rate> __global__ void __launch_bounds__(kThreads, 4) SingleDownKer
       *reinterpret_cast<uint2 *>(a.svh_rows + static_cast<size_t>(slot) * a.hidden + nb * 128 + lane * 4) = svh_bits;
   }
   // ---- ticket: the CTA that delivers the last of the block's 8 x slices sums combines ----
-  __threadfence();
+  // One thread draws the ticket behind the CTA's barrier with release and acquire at device scope: the release covers the
+  // sums the CTA's threads stored before the barrier, the acquire (in the CTA that turns out to be last) the other CTAs'.
   __syncthreads();
   PADRA_TRACE(a.trace, 6);
   if (tid == 0) {
     unsigned *ticket = a.tickets + nb;
-    const bool last = atomicAdd(ticket, 1u) == static_cast<unsigned>(kTopK) * a.slices_down - 1u;
+    unsigned drawn;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(drawn) : "l"(ticket) : "memory");
+    const bool last = drawn == static_cast<unsigned>(kTopK) * a.slices_down - 1u;
     if (last)
       *ticket = 0; // nobody else touches it before the next call
     s_last = last;
@@ -408,7 +418,6 @@ template <int Rate> __global__ void __launch_bounds__(kThreads, 4) SingleDownKer
   PADRA_TRACE(a.trace, 7);
   if (!s_last)
     return;
-  __threadfence();
   // one round trip: flag, the eight slots' sums and sidecars, routing weights, the residual row
   const int out = nb * 128 + lane * 4; // warp = slot from here on
   flagged = LoadFlag(a.bad);
