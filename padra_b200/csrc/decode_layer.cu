@@ -422,20 +422,26 @@ __global__ void __launch_bounds__(kThreads, 4) LayerProjectionKernel(LayerArgs a
   }
 
   // ---- ticket: which CTA delivered the last slice? ----
+  // The tickets are drawn behind the CTA's barrier with release and acquire at device scope: the release covers the sums
+  // the CTA's threads stored before the barrier, the acquire (where the ticket turns out to be the last) the other CTAs'.
+  auto draw = [](unsigned *ticket) {
+    unsigned drawn;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(drawn) : "l"(ticket) : "memory");
+    return drawn;
+  };
   if (tid == 0)
     s_done = 0;
-  __threadfence();
   __syncthreads();
   PADRA_TRACE(a.trace, 9);
   if (Phase == 0) {
     unsigned *ticket = a.tickets + static_cast<size_t>(blockIdx.y) * kMaxBlocks + nb;
-    if (tid == 0 && atomicAdd(ticket, 1u) == 2u * a.slices - 1u) {
+    if (tid == 0 && draw(ticket) == 2u * a.slices - 1u) {
       *ticket = 0; // nobody else touches it before the next call
       s_done = 1;
     }
   } else if (tid < count) {
     unsigned *ticket = a.tickets + static_cast<size_t>(rows[tid] >> 3) * kMaxBlocks + nb;
-    if (atomicAdd(ticket, 1u) == static_cast<unsigned>(kTopK) * a.slices - 1u) {
+    if (draw(ticket) == static_cast<unsigned>(kTopK) * a.slices - 1u) {
       *ticket = 0;
       atomicOr(&s_done, 1u << tid);
     }
@@ -445,7 +451,6 @@ __global__ void __launch_bounds__(kThreads, 4) LayerProjectionKernel(LayerArgs a
   const unsigned done = s_done;
   if (!done)
     return;
-  __threadfence();
   if (__syncthreads_or(LoadFlag(a.bad)))
     return; // some slice was not computed: leave x and the down inputs alone
 
