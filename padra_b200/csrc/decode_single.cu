@@ -277,15 +277,29 @@ template <int Rate> __global__ void __launch_bounds__(kThreads, 4) SingleDownKer
   PADRA_TRACE(a.trace, 1);
   Stream<Rate> stream;
   uint32_t fetched[4][Rate] = {};
-  uint2 svh_bits = make_uint2(0u, 0u);
-  unsigned short suh_early = 0;
+  uint2 svh_bits = make_uint2(0u, 0u), suh_bits = make_uint2(0u, 0u);
+  // Where a slice has no more elements than the CTA has threads (two blocks at the graded shape) the SwiGLU of the
+  // gate/up epilogue is spread over all threads and needs three float rows and the signs in shared memory; longer slices
+  // keep everything in the registers of the block's warp and need the transformed row only.  (The dynamic shared memory
+  // is kept small on purpose: a down kernel that asks for much more shared memory per SM than the gate+up kernel makes the
+  // SM switch its shared-memory configuration between the two, and they then no longer run side by side.)
+  const bool spread = span <= kThreads;
+  __half *xs = reinterpret_cast<__half *>(smem);
+  float *s_gate = reinterpret_cast<float *>(smem + static_cast<size_t>(span) * sizeof(__half)), *s_up = s_gate + span, *s_act = s_up + span;
+  unsigned short *s_suh = reinterpret_cast<unsigned short *>(s_act + span);
   if (work) {
     stream.Set(m, k_begin, nb * 8 + warp, lane);
 #pragma unroll
     for (int d = 0; d < 4; ++d)
       stream.Load(d < rounds ? d : rounds - 2 + (d & 1), fetched[d]);
-    if (tid < span) // the down matrix's input sign of the element this thread takes through the SwiGLU
-      suh_early = __ldg(m.suh + k_begin + tid);
+    // the down matrix's input signs of the slice, which the SwiGLU below multiplies by: into shared memory where the
+    // SwiGLU is spread over the threads, else in the registers of the warp that owns the block
+    if (spread) {
+      for (int e = tid; e < span; e += kThreads)
+        s_suh[e] = __ldg(m.suh + k_begin + e);
+    } else if (warp < blocks) {
+      suh_bits = __ldg(reinterpret_cast<const uint2 *>(m.suh + k_begin + warp * 128 + lane * 4));
+    }
     if (slice == 0 && warp == 7)
       svh_bits = __ldg(reinterpret_cast<const uint2 *>(m.svh + nb * 128 + lane * 4));
   }
@@ -296,10 +310,9 @@ template <int Rate> __global__ void __launch_bounds__(kThreads, 4) SingleDownKer
   int flagged = 0;
   // ---- the gate/up epilogue of this slice's 128-input blocks ----
   // Sums and Hadamard transforms need a block's 128 values in one warp (one warp per block); the SwiGLU between them
-  // is elementwise and its exact exponential is a long dependent chain, so it is spread over all the CTA's threads, one
-  // element each, instead of four in a row in the lanes of two warps.
-  __half *xs = reinterpret_cast<__half *>(smem);
-  float *s_gate = reinterpret_cast<float *>(smem + static_cast<size_t>(span) * sizeof(__half)), *s_up = s_gate + span, *s_act = s_up + span;
+  // is elementwise and its exact exponential is a long dependent chain, so where a slice has no more elements than the CTA
+  // has threads (two blocks at the graded shape: six of the eight warps would idle) it is spread over all threads, one
+  // element each.  Longer slices keep every warp busy with a block of its own, and there the block's warp does it.
   if (work)
     for (int block = warp; block < blocks; block += 8) {
       int arrived = 1;
@@ -347,27 +360,73 @@ template <int Rate> __global__ void __launch_bounds__(kThreads, 4) SingleDownKer
       gate.z = RoundBF16(__fmul_rn(gsum[2], svg[2])), gate.w = RoundBF16(__fmul_rn(gsum[3], svg[3]));
       up.x = RoundBF16(__fmul_rn(usum[0], svu[0])), up.y = RoundBF16(__fmul_rn(usum[1], svu[1]));
       up.z = RoundBF16(__fmul_rn(usum[2], svu[2])), up.w = RoundBF16(__fmul_rn(usum[3], svu[3]));
-      *reinterpret_cast<float4 *>(s_gate + block * 128 + lane * 4) = gate;
-      *reinterpret_cast<float4 *>(s_up + block * 128 + lane * 4) = up;
+      if (spread) {
+        *reinterpret_cast<float4 *>(s_gate + block * 128 + lane * 4) = gate;
+        *reinterpret_cast<float4 *>(s_up + block * 128 + lane * 4) = up;
+      } else { // long slices: the block's warp applies the SwiGLU and the input transform itself
+        if (block >= 8)
+          suh_bits = __ldg(reinterpret_cast<const uint2 *>(m.suh + out));
+        float shd[4], v[4];
+        Unpack4(suh_bits, shd);
+        const float gv[4] = {gate.x, gate.y, gate.z, gate.w}, uv[4] = {up.x, up.y, up.z, up.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const bool finite = isfinite(gv[i]) && isfinite(uv[i]);
+          const float act = RoundBF16(__fmul_rn(SiluRounded(finite ? gv[i] : 0.f), uv[i]));
+          if (!finite || !isfinite(act)) {
+            if (!flagged)
+              Raise(a.bad);
+            flagged = 1;
+          }
+          v[i] = __fmul_rn(act, shd[i]);
+        }
+        WarpHadamard128(v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float r = RoundBF16(v[i]);
+          const __half h = __float2half_rn(r);
+          if (!isfinite(r) || (__half_as_ushort(h) & 0x7c00) == 0x7c00) {
+            if (!flagged)
+              Raise(a.bad);
+            flagged = 1;
+          }
+          xs[PermutedPlace(block * 128 + lane * 4 + i)] = h;
+        }
+      }
       PADRA_TRACE(a.trace, 10);
     }
   __syncthreads();
   const bool recompute = work && !s_expired; // uniform over the CTA
-  if (recompute)
-    for (int e = tid; e < span; e += kThreads) { // one element per thread at the graded shape
-      const float gate = s_gate[e], up = s_up[e];
-      const bool finite = isfinite(gate) && isfinite(up);
-      const float act = RoundBF16(__fmul_rn(SiluRounded(finite ? gate : 0.f), up));
-      if (!finite || !isfinite(act)) {
-        if (!flagged) // a flag raised earlier explains garbage here; only a fresh failure is reported
-          Raise(a.bad);
-        flagged = 1;
+  if (recompute && spread)
+    for (int e0 = tid; e0 < span; e0 += 4 * kThreads) { // one element per thread at the graded shape
+      // up to four elements a thread at a time, so that their exponentials (long dependent chains) overlap
+      float gate[4], up[4], act[4];
+      bool finite[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = e0 + j * kThreads;
+        gate[j] = e < span ? s_gate[e] : 0.f, up[j] = e < span ? s_up[e] : 0.f;
+        finite[j] = isfinite(gate[j]) && isfinite(up[j]);
       }
-      s_act[e] = __fmul_rn(act, HalfBitsToFloat(e == tid ? suh_early : __ldg(m.suh + k_begin + e)));
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        act[j] = e0 + j * kThreads < span ? RoundBF16(__fmul_rn(SiluRounded(finite[j] ? gate[j] : 0.f), up[j])) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = e0 + j * kThreads;
+        if (e < span) {
+          if (!finite[j] || !isfinite(act[j])) {
+            if (!flagged) // a flag raised earlier explains garbage here; only a fresh failure is reported
+              Raise(a.bad);
+            flagged = 1;
+          }
+          s_act[e] = __fmul_rn(act[j], HalfBitsToFloat(s_suh[e]));
+        }
+      }
     }
   __syncthreads();
   PADRA_TRACE(a.trace, 11);
-  if (recompute)
+  if (recompute && spread)
     for (int block = warp; block < blocks; block += 8) {
       const float4 in = *reinterpret_cast<const float4 *>(s_act + block * 128 + lane * 4);
       float v[4] = {in.x, in.y, in.z, in.w};
@@ -492,6 +551,7 @@ template <int Rate> __global__ void __launch_bounds__(kThreads, 4) SingleDownKer
 
 template <int Rate> int LaunchSingle(const SingleArgs &a, unsigned launches, cudaStream_t stream) {
   int status = PADRA_OK;
+
   if (launches & 1u) {
     const size_t smem = static_cast<size_t>(a.hidden / a.slices_gateup) * sizeof(__half);
     if (smem > 40 * 1024 && cudaFuncSetAttribute(SingleGateUpKernel<Rate>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -502,8 +562,10 @@ template <int Rate> int LaunchSingle(const SingleArgs &a, unsigned launches, cud
   if (status != PADRA_OK)
     return status;
   if (launches & 2u) {
-    // the slice's transformed input row, and three float rows of the gate/up epilogue (gate, up, activation)
-    const size_t smem = static_cast<size_t>(a.inter / a.slices_down) * (sizeof(__half) + 3 * sizeof(float));
+    // the slice's transformed input row; for slices of at most one element per thread also three float rows of the gate/up
+    // epilogue (gate, up, activation) and the input signs
+    const size_t span = static_cast<size_t>(a.inter / a.slices_down);
+    const size_t smem = span * (span <= static_cast<size_t>(kThreads) ? 2 * sizeof(__half) + 3 * sizeof(float) : sizeof(__half));
     if (smem > 36 * 1024 && cudaFuncSetAttribute(SingleDownKernel<Rate>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  static_cast<int>(smem)) != cudaSuccess)
       return PADRA_RESOURCE_EXHAUSTED;
