@@ -71,6 +71,7 @@ extern int g_trace_launch;
 #endif
 
 // K-slices: enough CTAs to fill the machine several deep, slices of whole 128-input blocks.
+// PADRA_DECODE_SLICES (read once per process) overrides the default of four: a tuning aid, not part of the interface.
 inline int SliceOverride() {
   static const int value = [] {
     const char *text = std::getenv("PADRA_DECODE_SLICES");
@@ -112,6 +113,8 @@ struct LayerWorkspace {
 
 template <typename... KernelArgs, typename... Args>
 inline int LaunchProgrammatic(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  // PADRA_DECODE_NO_OVERLAP (read once per process) launches in plain stream order: a diagnostic that takes the
+  // overlap of consecutive launches out of a timing; results are the same either way
   static const int allowed = std::getenv("PADRA_DECODE_NO_OVERLAP") ? 0 : 1;
   cudaLaunchAttribute attribute{};
   attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
