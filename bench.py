@@ -522,7 +522,7 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
         times.append(a.elapsed_time(b) / 1e3)
         assert k.bad_flag() == 0 and bool(torch.isfinite(x).all()), "expert-parallel prefill raised the error flag"
     return {"times": times, "batch": batch, "layers": layers, "chunk": chunk, "exchange": exchange, "parity_rows": parity_rows,
-            "placement": {"second_copy_of_hottest_expert": bool(replicas and world > 1),
+            "placement": {"layers_with_a_second_copy_of_the_hottest_expert": int(sum(bool((np.asarray(o) >> 8).any()) for o in owners)),
                           "busiest_rank_over_mean_64_per_rank_exact": round(float(np.mean([a for a, _ in loads])), 4),
                           "busiest_rank_over_mean_as_run": round(float(np.mean([b for _, b in loads])), 4)}}
 
