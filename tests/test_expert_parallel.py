@@ -131,8 +131,9 @@ def _gloo_rank(rank, world, port, results):
         host = O.HostMatrices(1, hidden, inter, 4, seed=21)
         x, ids, w = _inputs(oracle, rank, tokens, hidden)
         popularity = np.arange(1, 65, dtype=np.float64) ** -1.1
-        ep = EP.ExpertParallelPrefill(HostBackend(oracle, host, hidden, inter, 4), EP.GroupExchange(),
-                                      EP.balanced_placement(popularity, world))
+        owner = EP.balanced_placement(popularity, world)
+        owner[0] |= ((int(owner[0]) + 1) % world + 1) << 8  # expert 0 held by both ranks: odd tokens' pairs go to the second
+        ep = EP.ExpertParallelPrefill(HostBackend(oracle, host, hidden, inter, 4), EP.GroupExchange(), owner)
         got = torch.from_numpy(x.copy())
         ep.layer(0, torch.from_numpy(ids.reshape(-1)), torch.from_numpy(w.reshape(-1)), torch.from_numpy(x), got)
         want, bad = oracle.moe_layer(host.table, 0, ids, w, x, hidden, inter)
