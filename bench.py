@@ -561,18 +561,21 @@ def run_ours(args):
         k.moe_decode_layer(s["layer"], s["ids"], s["w"], s["normalized"], s["x"], TOKENS, stream=stream)
 
     # The step as a serving loop replays it: CUDA graphs.  One graph holds `layers` consecutive layer steps (the expert
-    # layers of one token's pass through the model, each with routing and inputs of its own); single-step graphs cover
-    # what is left when the step count is not a multiple of the layer count.
+    # layers of one token's pass through the model, each with routing and inputs of its own); a graph of the first few
+    # layers covers what is left when the step count is not a multiple of the layer count.
     passes = [capture(stream, lambda v=v: [layer_call(s) for s in slots[v * layers:(v + 1) * layers]]) for v in range(2)]
-    singles = [capture(stream, lambda s=s: layer_call(s)) for s in slots[:layers]]
+    partial = {}
     kernels_per_step = 2  # split-K gate+up projection; split-K down projection with the gate/up epilogue in front and the combine behind
 
     def run_steps(count):
         full, rest = divmod(count, layers)
         for i in range(full):
             passes[i % 2].replay()
-        for i in range(rest):
-            singles[i].replay()
+        if rest:
+            partial[rest].replay()
+
+    for rest in {args.warmup % layers, args.steps % layers} - {0}:  # captured here, outside every timed region
+        partial[rest] = capture(stream, lambda rest=rest: [layer_call(s) for s in slots[:rest]])
 
     def barrier():
         if world > 1:
