@@ -657,15 +657,14 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) PrefillGemmKernel(PrefillA
 // x~ rows in expert-grouped order: row (offset of expert e) + i holds the transform of the i-th pair routed to e.
 // Parts 0/1: x~ = fp16(B(H128(x[token] * suh)))  (reference: src/cuda/expert_exl3_prefill_warp.cuh:14-57);
 // part 2: x = SwiGLU(gate[pair], up[pair]) first (expert_exl3_prefill_packed_activations.cuh:17-73).
-// A launch with gridDim.y == 2 transforms the rows for parts `first_part` and `first_part + 1` (gate and up: same input,
-// each part's own signs), the second part's rows `second_offset` halves behind the first's.
+// second_offset != 0: the launch transforms the rows for parts `first_part` and `first_part + 1` (gate and up: the same
+// input, read once, each part's own signs), the second part's rows `second_offset` halves behind the first's.
 __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices, int layer, int first_part, const int *groups,
                                                           const int *counts, const float *input, const unsigned short *gate,
                                                           const unsigned short *up, const unsigned short *pair_rows,
                                                           const unsigned short *table, __half *transformed, size_t second_offset,
                                                           int group_stride, int pairs, int hidden, int inter, int format, int *bad) {
-  const int part = first_part + static_cast<int>(blockIdx.y);
-  transformed += blockIdx.y * second_offset;
+  const int part = first_part, parts = second_offset ? 2 : 1;
   __shared__ int s_offset[kExperts + 1], s_half;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int cols = part == 2 ? inter : hidden, blocks = cols / 128;
@@ -705,9 +704,14 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
   }
   // the descriptor is checked before anything is read through it: a table of another rate or shape, or a missing
   // sidecar, raises the flag and the row is skipped
-  const Matrix &dm = matrices[(static_cast<size_t>(layer) * kExperts + expert) * 3 + part];
-  const uint16_t *suh = dm.suh;
-  if (dm.format != format || dm.cols != cols || dm.rows != (part == 2 ? hidden : inter) || !suh || !dm.data) {
+  const uint16_t *suh[2] = {nullptr, nullptr};
+  bool fits = true;
+  for (int p = 0; p < parts; ++p) {
+    const Matrix &dm = matrices[(static_cast<size_t>(layer) * kExperts + expert) * 3 + part + p];
+    suh[p] = dm.suh;
+    fits = fits && dm.format == format && dm.cols == cols && dm.rows == (part == 2 ? hidden : inter) && suh[p] && dm.data;
+  }
+  if (!fits) {
     if (!lane)
       Raise(bad);
     continue;
@@ -715,7 +719,6 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
 #pragma unroll 4
   for (int h = 0; h < blocks; ++h) {
   const int k = h * 128 + lane * 4;
-  const uint2 sign = __ldg(reinterpret_cast<const uint2 *>(suh + k));
   float src[4];
   if (part == 2) {
     const uint2 gb = *reinterpret_cast<const uint2 *>(gate + static_cast<size_t>(pair) * cols + k);
@@ -744,21 +747,24 @@ __global__ void __launch_bounds__(256) PrefillInputKernel(const Matrix *matrices
     const float4 x = *reinterpret_cast<const float4 *>(input + static_cast<size_t>(pair >> 3) * cols + k);
     src[0] = x.x, src[1] = x.y, src[2] = x.z, src[3] = x.w;
   }
-  float v[4] = {__fmul_rn(src[0], HalfBitsToFloat(sign.x & 0xffffu)), __fmul_rn(src[1], HalfBitsToFloat(sign.x >> 16)),
-                __fmul_rn(src[2], HalfBitsToFloat(sign.y & 0xffffu)), __fmul_rn(src[3], HalfBitsToFloat(sign.y >> 16))};
-  WarpHadamard128(v);
-  __half hv[4];
+  for (int p = 0; p < parts; ++p) {
+    const uint2 sign = __ldg(reinterpret_cast<const uint2 *>(suh[p] + k));
+    float v[4] = {__fmul_rn(src[0], HalfBitsToFloat(sign.x & 0xffffu)), __fmul_rn(src[1], HalfBitsToFloat(sign.x >> 16)),
+                  __fmul_rn(src[2], HalfBitsToFloat(sign.y & 0xffffu)), __fmul_rn(src[3], HalfBitsToFloat(sign.y >> 16))};
+    WarpHadamard128(v);
+    __half hv[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float r = RoundBF16(v[j]);
-    hv[j] = __float2half_rn(r);
-    if (!isfinite(r) || (__half_as_ushort(hv[j]) & 0x7c00) == 0x7c00)
-      Raise(bad);
+    for (int j = 0; j < 4; ++j) {
+      const float r = RoundBF16(v[j]);
+      hv[j] = __float2half_rn(r);
+      if (!isfinite(r) || (__half_as_ushort(hv[j]) & 0x7c00) == 0x7c00)
+        Raise(bad);
+    }
+    uint2 packed;
+    packed.x = static_cast<unsigned>(__half_as_ushort(hv[0])) | (static_cast<unsigned>(__half_as_ushort(hv[1])) << 16);
+    packed.y = static_cast<unsigned>(__half_as_ushort(hv[2])) | (static_cast<unsigned>(__half_as_ushort(hv[3])) << 16);
+    *reinterpret_cast<uint2 *>(transformed + p * second_offset + static_cast<size_t>(row) * cols + k) = packed;
   }
-  uint2 packed;
-  packed.x = static_cast<unsigned>(__half_as_ushort(hv[0])) | (static_cast<unsigned>(__half_as_ushort(hv[1])) << 16);
-  packed.y = static_cast<unsigned>(__half_as_ushort(hv[2])) | (static_cast<unsigned>(__half_as_ushort(hv[3])) << 16);
-  *reinterpret_cast<uint2 *>(transformed + static_cast<size_t>(row) * cols + k) = packed;
   }
   }
 }
@@ -824,9 +830,9 @@ static int LaunchPrefillGemm(const Matrix *matrices, int layer, int part, const 
   const int cols = part == 2 ? inter : hidden, map_rows = pairs < kMaxPairs ? pairs : kMaxPairs;
   __half *const transformed_second = static_cast<__half *>(transformed) + static_cast<size_t>(map_rows) * cols;
   if (block_begin == 0) {
-    PrefillInputKernel<<<dim3((map_rows + 7) / 8, output_second ? 2 : 1), 256, 0, stream>>>(
+    PrefillInputKernel<<<(map_rows + 7) / 8, 256, 0, stream>>>(
         matrices, layer, part, groups, counts, input, gate, up, pair_rows, table, static_cast<__half *>(transformed),
-        static_cast<size_t>(map_rows) * cols, group_stride, pairs, hidden, inter, FormatOfRate(rate), bad);
+        output_second ? static_cast<size_t>(map_rows) * cols : 0, group_stride, pairs, hidden, inter, FormatOfRate(rate), bad);
     if (cudaGetLastError() != cudaSuccess)
       return PADRA_INTERNAL;
   }
