@@ -394,7 +394,7 @@ def reference_kernels_leg(dev) -> dict | None:
 
 
 def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: str, passes: int, batch: int = 16384,
-                        chunk: int = 2048, replicas: int = 1) -> dict:
+                        chunk: int = 2048, replicas: int = 1, engine_count: int = 2) -> dict:
     """configs[4]: a batch of 16384 tokens through `layers` MoE layers, experts sharded 64/world per rank by measured
     popularity, tokens split evenly over the ranks (strong scaling), dispatch and combine per layer and chunk.  Between
     layers the next input is the RMS-normalised residual stream (this library's norm kernel), so layer l+1 depends on
@@ -408,8 +408,8 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
     from padra_b200.experts import bf16_values, zipf_routing
 
     local = batch // world
-    if world > 1 and local <= chunk:
-        chunk = local // 2  # at least two chunks per rank, so that one chunk's exchange overlaps the other's expert work
+    if world > 1:  # at least one chunk per engine, so that one chunk's exchange overlaps the others' expert work
+        chunk = min(chunk, max(256, local // engine_count))
     chunks = [(c, min(chunk, local - c)) for c in range(0, local, chunk)]
     g = torch.Generator(device=dev)
     g.manual_seed(500 + rank)
@@ -420,7 +420,7 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
         # popularity as a server would have measured it over earlier traffic: a long sample of the layer's routing
         sample, _ = zipf_routing(16384, seed=layer, device="cpu", popularity_seed=layer)
         popularity = np.bincount(sample.reshape(-1).numpy(), minlength=EXPERTS)
-        owners.append(EP.balanced_placement(popularity, world, replicas=min(replicas, 1), force=replicas == 2))
+        owners.append(EP.balanced_placement(popularity, world, replicas=abs(replicas), force=replicas < 0))
         loads.append((EP.placement_load(popularity, EP.balanced_placement(popularity, world), world),
                       EP.placement_load(popularity, owners[-1], world)))
         for c, n in chunks:
@@ -433,8 +433,8 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
     elif world > 1:
         # symmetric memory may be unavailable on a host (no peer access, no handle exchange): every rank then takes the
         # NCCL exchange, and the JSON line says which exchange ran
-        try:  # two engines with an exchange block each: the chunks of a layer alternate between them, on a stream each
-            peer = [EP.PeerExchangePrefill.over_group(k, owners[0], cap=chunk * TOPK) for _ in range(2)]
+        try:  # engines with an exchange block each: the chunks of a layer go to them in turn, on a stream each
+            peer = [EP.PeerExchangePrefill.over_group(k, owners[0], cap=chunk * TOPK) for _ in range(engine_count)]
             failed = 0
         except Exception as error:  # noqa: BLE001 - any failure of the rendezvous means "not available here"
             print(f"rank {rank}: peer exchange unavailable ({type(error).__name__}: {error}); using NCCL all-to-all", file=sys.stderr)
@@ -447,7 +447,7 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
             engines = [EP.ExpertParallelPrefill(backend, group_exchange, owners[layer]) for layer in range(layers)]
         else:
             device_owners = [torch.from_numpy(o.astype(np.int32)).to(dev) for o in owners]
-    lanes = 2 if peer is not None else 1
+    lanes = engine_count if peer is not None else 1
     normalized = [torch.empty((chunk, HIDDEN), dtype=torch.float32, device=dev) for _ in range(lanes)]
     streams = [torch.cuda.Stream(device=dev) for _ in range(lanes)] if peer is not None else None
 
@@ -522,6 +522,7 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
         times.append(a.elapsed_time(b) / 1e3)
         assert k.bad_flag() == 0 and bool(torch.isfinite(x).all()), "expert-parallel prefill raised the error flag"
     return {"times": times, "batch": batch, "layers": layers, "chunk": chunk, "exchange": exchange, "parity_rows": parity_rows,
+            "engines": lanes,
             "placement": {"layers_with_a_second_copy_of_the_hottest_expert": int(sum(bool((np.asarray(o) >> 8).any()) for o in owners)),
                           "busiest_rank_over_mean_64_per_rank_exact": round(float(np.mean([a for a, _ in loads])), 4),
                           "busiest_rank_over_mean_as_run": round(float(np.mean([b for _, b in loads])), 4)}}
@@ -648,7 +649,11 @@ def run_ours(args):
 
     ep = None
     if EXPERTS % world == 0 and not args.no_ep:
-        ep = expert_parallel_leg(k, dev, world, rank, layers, args.ep_exchange, passes=args.ep_passes, replicas=args.ep_replicas)
+        if world > 1 and args.ep_exchange == "peer":  # leave SMs to the other engine's exchange kernels beside the persistent GEMM
+            B.check(k.lib.padra_prefill_set_reserved_sms(args.ep_reserved_sms), "padra_prefill_set_reserved_sms")
+        ep = expert_parallel_leg(k, dev, world, rank, layers, args.ep_exchange, passes=args.ep_passes, replicas=args.ep_replicas,
+                                 engine_count=args.ep_engines)
+        B.check(k.lib.padra_prefill_set_reserved_sms(0), "padra_prefill_set_reserved_sms")
     if world > 1:
         t = torch.tensor([seconds, e2e_seconds] + (ep["times"] if ep else []), device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -677,7 +682,7 @@ def run_ours(args):
             "n_gpus": world, "scaling": "strong", "exchange": ep["exchange"] if world > 1 else "none", "ms_per_batch": best * 1e3,
             "ms_per_batch_min": min(ep["times"]) * 1e3, "passes": len(ep["times"]), "tokens_per_s": ep["batch"] / best,
             "tflops_all_gpus": flops / best / 1e12, "parity_checked": world > 1, "parity_rows": ep["parity_rows"],
-            "placement": ep["placement"],
+            "placement": ep["placement"], "chunk_tokens": ep["chunk"], "engines": ep["engines"],
             "timing": "CUDA events per rank, max over ranks, median of passes"}
     line.update({
         "config": dict(base_config(layers), weight_bytes_resident=table.total_bytes,
@@ -745,9 +750,11 @@ def main():
     ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
                     help="expert-parallel exchange: kernels over NVLink peer memory (default) or NCCL all-to-all")
     ap.add_argument("--ep-passes", type=int, default=5, help="timed passes of the expert-parallel batch (median reported)")
-    ap.add_argument("--ep-replicas", type=int, default=1, choices=[0, 1, 2],
-                    help="1: the most popular expert of a layer is held by two ranks where that lowers the busiest rank's load; "
-                         "2: held by two ranks in any case (exercises the path on two or four GPUs)")
+    ap.add_argument("--ep-replicas", type=int, default=2,
+                    help="k > 0: up to k of a layer's most popular experts are held by two ranks, as long as that lowers the "
+                         "busiest rank's load; -k: held by two ranks in any case (exercises the path on two or four GPUs)")
+    ap.add_argument("--ep-reserved-sms", type=int, default=0, help="SMs the grouped GEMM leaves free for the exchange kernels (several GPUs)")
+    ap.add_argument("--ep-engines", type=int, default=2, help="exchange engines (blocks and streams) per rank that take a layer's chunks in turn")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers of distinct weights to rotate over (profiling: fewer)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

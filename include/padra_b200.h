@@ -191,6 +191,11 @@ PADRA_API int padra_ep_wait(const void *block, int which, int world, int cap, in
 /* How long padra_ep_wait's kernel polls before it gives up, raises *bad and returns (1..60000 ms, default 2000; a
  * process-wide host setting read at launch).  A wait that expires leaves the stream and the context usable. */
 PADRA_API int padra_ep_set_wait_limit_ms(int milliseconds);
+/* SMs the tensor-memory grouped GEMM leaves free (0..64, default 0; a process-wide host setting read at launch).  The GEMM
+ * is persistent, one CTA per SM; with every SM taken, the kernels of another stream (the exchange of the next chunk:
+ * plan, dispatch, return, input transforms) cannot start until its CTAs retire.  A host that overlaps chunks leaves a few
+ * SMs to them. */
+PADRA_API int padra_prefill_set_reserved_sms(int sms);
 PADRA_API int padra_ep_group_received(const void *block, int world, int cap, int hidden, int *groups, int *counts,
                                       int group_stride, int *bad, padra_stream stream);
 PADRA_API int padra_ep_return(const unsigned short *down_rows, const unsigned long long *peer_blocks, int rank, int world,

@@ -40,6 +40,7 @@ SIGNATURES = {
     "padra_ep_dispatch": ([_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, C.c_uint, _p, _p], _i),
     "padra_ep_wait": ([_p, _i, _i, _i, _i, C.c_uint, _p, _p], _i),
     "padra_ep_set_wait_limit_ms": ([_i], _i),
+    "padra_prefill_set_reserved_sms": ([_i], _i),
     "padra_ep_group_received": ([_p, _i, _i, _i, _p, _p, _i, _p, _p], _i),
     "padra_ep_return": ([_p, _p, _i, _i, _i, _i, C.c_uint, _p, _p, _i, _i, _i], _i),
     "padra_ep_down_return": ([_p, _i, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, C.c_uint, _p, _p, _i, _i, _i], _i),

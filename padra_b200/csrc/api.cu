@@ -166,6 +166,10 @@ int padra_ep_set_wait_limit_ms(int milliseconds) {
   return SetExchangeWaitLimit(milliseconds);
 }
 
+int padra_prefill_set_reserved_sms(int sms) {
+  return SetPrefillReservedSms(sms);
+}
+
 int padra_ep_group_received(const void *block, int world, int cap, int hidden, int *groups, int *counts, int group_stride, int *bad,
                             padra_stream stream) {
   return LaunchGroupRegions(block, world, cap, hidden, groups, counts, group_stride, bad, S(stream));

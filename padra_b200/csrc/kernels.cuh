@@ -51,6 +51,7 @@ int LaunchDispatch(const float *activations, const int *order, const int *send_i
                    const unsigned long long *bases, int rank, int world, int cap, int pairs, int hidden, unsigned epoch, int *bad,
                    cudaStream_t stream);
 int SetExchangeWaitLimit(int milliseconds);
+int SetPrefillReservedSms(int sms);
 int LaunchWaitFlags(const void *block, int which, int world, int cap, int hidden, unsigned epoch, int *bad, cudaStream_t stream);
 int LaunchGroupRegions(const void *block, int world, int cap, int hidden, int *groups, int *counts, int group_stride, int *bad,
                        cudaStream_t stream);

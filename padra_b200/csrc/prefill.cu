@@ -29,6 +29,7 @@
 //     producers and the MMA thread already work on item i+1.
 // Every wait on an mbarrier is bounded in time: on expiry the CTA raises the sticky error flag, skips the rest of
 // its work, frees its tensor memory and leaves.
+#include <atomic>
 #include <cuda.h>
 
 #include "codec.cuh"
@@ -802,6 +803,14 @@ template <int Rate> int LaunchGemm(const PrefillArgs &a, const CUtensorMap &map,
 
 // `pair_rows` null: the reference's layout, pairs = tokens*8 and input row pair/8.  Otherwise one BF16 input row per
 // pair, any number of pairs per expert up to group_stride (rows that other ranks routed to this rank's experts).
+static std::atomic<int> g_reserved_sms{0};
+int SetPrefillReservedSms(int sms) {
+  if (sms < 0 || sms > 64)
+    return PADRA_INVALID_ARGUMENT;
+  g_reserved_sms.store(sms, std::memory_order_relaxed);
+  return PADRA_OK;
+}
+
 struct ReturnSpec {
   const unsigned long long *bases;
   int rank, world, cap;
@@ -857,7 +866,8 @@ static int LaunchPrefillGemm(const Matrix *matrices, int layer, int part, const 
   int device = 0, sms = 0;
   if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 1)
     return PADRA_INTERNAL;
-  const dim3 grid(sms); // persistent: one CTA per SM
+  const int reserved = g_reserved_sms.load(std::memory_order_relaxed);
+  const dim3 grid(sms - reserved > 0 ? sms - reserved : 1); // persistent: one CTA per SM, less the SMs left to other streams
   CUtensorMap map, map_second;
   if (const int status = MakeActivationMap(&map, transformed, map_rows, cols); status != PADRA_OK)
     return status;

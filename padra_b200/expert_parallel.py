@@ -32,41 +32,48 @@ def balanced_placement(popularity, world: int, replicas: int = 0, force: bool = 
     rank with the least expected load that still has room (longest-processing-time-first).  Ties break towards the
     lower rank, so every rank computes the same table from the same popularity.
 
-    replicas = 1: the most popular expert is held by a second rank as well (one extra expert's weights on that rank,
-    3 MB at K4 2048/1024) and its pairs are split between the two by token parity; its entry is
-    rank | (1 + second rank) << 8 (see owner_ranks).  With Zipf(1.1) routing on eight ranks the busiest rank's load
-    drops from 1.155 to about 1.03 times the mean."""
+    replicas = k > 0: up to k of the most popular experts are held by a second rank as well (at most one extra expert's
+    weights per rank: 3 MB at K4 2048/1024) and their pairs are split between the two ranks by token parity; such an
+    entry is rank | (1 + second rank) << 8 (see owner_ranks).  Copies are added, most popular expert first, only while
+    they lower the busiest rank's expected load.  With Zipf(1.1) routing on eight ranks the busiest rank's load drops
+    from 1.155 times the mean to 1.05 with one copy."""
     popularity = np.asarray(popularity, dtype=np.float64)
-    assert popularity.shape == (EXPERTS,) and EXPERTS % world == 0 and replicas in (0, 1)
+    assert popularity.shape == (EXPERTS,) and EXPERTS % world == 0 and 0 <= replicas <= world
 
-    def place(split: int) -> np.ndarray:
-        # items in order of falling share; the split expert is two items of half its popularity, the second of which
-        # takes its rank's extra slot (no room needed) and must not meet the first
-        items = [(popularity[e] / 2 if e == split else popularity[e], int(e), 0) for e in range(EXPERTS)]
-        if split >= 0:
-            items.append((popularity[split] / 2, split, 1))
+    def place(split) -> np.ndarray:
+        # items in order of falling share; a split expert is two items of half its popularity, the second of which takes
+        # a rank's extra slot (one per rank, no room needed) and must not meet the first
+        items = [(popularity[e] / 2 if e in split else popularity[e], int(e), 0) for e in range(EXPERTS)]
+        items += [(popularity[e] / 2, int(e), 1) for e in split]
         items.sort(key=lambda item: (-item[0], item[1], item[2]))
-        room, load = np.full(world, EXPERTS // world), np.zeros(world)
+        room, load, extra = np.full(world, EXPERTS // world), np.zeros(world), np.ones(world, dtype=bool)
         owner = np.empty(EXPERTS, dtype=np.int32)
         for share, e, second in items:
             if second:
-                candidates = np.array([r for r in range(world) if r != (owner[e] & 0xff)])
+                candidates = np.array([r for r in range(world) if r != (owner[e] & 0xff) and extra[r]])
             else:
                 candidates = np.where(room > 0)[0]
             r = int(candidates[np.argmin(load[candidates])])
             load[r] += share
             if second:
                 owner[e] |= (r + 1) << 8
+                extra[r] = False
             else:
                 owner[e], room[r] = r, room[r] - 1
         return owner
 
-    exact = place(-1)
-    if not replicas or world < 2:
-        return exact
-    doubled = place(int(np.argmax(popularity)))
-    # force: keep the copy even where it does not help (to exercise the path on few ranks)
-    return doubled if force or placement_load(popularity, doubled, world) < placement_load(popularity, exact, world) else exact
+    best = place(())
+    if world < 2:
+        return best
+    hottest = [int(e) for e in np.argsort(-popularity, kind="stable")]
+    for k in range(1, replicas + 1):
+        candidate = place(tuple(hottest[:k]))
+        # force: keep the copies even where they do not help (to exercise the path on few ranks)
+        if force or placement_load(popularity, candidate, world) < placement_load(popularity, best, world):
+            best = candidate
+        else:
+            break
+    return best
 
 
 def owner_ranks(owner: np.ndarray):
@@ -303,6 +310,9 @@ class PeerExchangePrefill:
         self.down = None if fused_return else torch.empty((rows, self.hidden), dtype=torch.uint16, device=dev)
         self.transformed = torch.empty((self.MAX_GROUPED, max(self.hidden, self.inter)), dtype=torch.float16, device=dev)
         self.transformed_up = torch.empty((self.MAX_GROUPED, self.hidden), dtype=torch.float16, device=dev)
+        # gate and up as one launch: both parts' transformed rows, the second part's behind the first's
+        self.merged_gate_up = True
+        self.transformed_both = torch.empty((2 * min(rows, self.MAX_GROUPED), self.hidden), dtype=torch.float16, device=dev)
         self.backend = KernelBackend(kernels)
         self.epoch = 0
         self._side = None  # this engine's second stream (two engines may run side by side, each on its own pair of streams)
@@ -362,15 +372,20 @@ class PeerExchangePrefill:
                 base + self.offsets[0], B.ptr(target), B.ptr(self.gate), B.ptr(self.up), B.ptr(k.table), B.ptr(transformed), bad,
                 on, k.t.rate, self.hidden, self.inter, *blocks), "padra_exl3_prefill_rows_launch")
 
-        # the up projection runs on a second stream beside the gate projection; both join before the down projection
         main, side = torch.cuda.current_stream(), self.side_stream()
-        fork, join = torch.cuda.Event(), torch.cuda.Event()
-        fork.record(main)
-        side.wait_event(fork)
-        project(1, self.up, self.transformed_up, side.cuda_stream)
-        join.record(side)
-        project(0, self.gate, self.transformed, stream)
-        main.wait_event(join)
+        if self.merged_gate_up:  # gate and up as one launch: one list of work items, one input transform
+            B.check(lib.padra_exl3_prefill_rows_gate_up_launch(
+                k.t.descriptors.data_ptr(), layer, B.ptr(self.groups), B.ptr(self.counts), self.MAX_GROUPED, self.world * self.cap,
+                base + self.offsets[0], B.ptr(self.gate), B.ptr(self.up), B.ptr(self.transformed_both), bad, stream, k.t.rate,
+                self.hidden, self.inter), "padra_exl3_prefill_rows_gate_up_launch")
+        else:  # the up projection runs on a second stream beside the gate projection; both join before the down projection
+            fork, join = torch.cuda.Event(), torch.cuda.Event()
+            fork.record(main)
+            side.wait_event(fork)
+            project(1, self.up, self.transformed_up, side.cuda_stream)
+            join.record(side)
+            project(0, self.gate, self.transformed, stream)
+            main.wait_event(join)
         if self.fused_return:  # the down projection's epilogue stores the rows into their sources' blocks itself
             B.check(lib.padra_ep_down_return(k.t.descriptors.data_ptr(), layer, B.ptr(self.groups), B.ptr(self.counts), self.MAX_GROUPED,
                                              B.ptr(self.gate), B.ptr(self.up), B.ptr(k.table), B.ptr(self.transformed), self.bases,
