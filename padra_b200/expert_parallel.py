@@ -38,7 +38,8 @@ def balanced_placement(popularity, world: int, replicas: int = 0, force: bool = 
     they lower the busiest rank's expected load.  With Zipf(1.1) routing on eight ranks the busiest rank's load drops
     from 1.155 times the mean to 1.05 with one copy."""
     popularity = np.asarray(popularity, dtype=np.float64)
-    assert popularity.shape == (EXPERTS,) and EXPERTS % world == 0 and 0 <= replicas <= world
+    assert popularity.shape == (EXPERTS,) and EXPERTS % world == 0 and replicas >= 0
+    replicas = min(replicas, world) if world > 1 else 0  # one extra expert per rank at most; nothing to copy to on one rank
 
     def place(split) -> np.ndarray:
         # items in order of falling share; a split expert is two items of half its popularity, the second of which takes

@@ -43,6 +43,10 @@ def test_a_second_copy_of_the_hottest_expert_lowers_the_busiest_rank():
         assert EP.placement_load(popularity, doubled, world) <= EP.placement_load(popularity, exact, world) + 1e-12
         if world == 8:  # the copy is only made where it helps
             assert (second >= 0).sum() == 1 and second[hottest] >= 0 and second[hottest] != first[hottest]
+    assert (EP.balanced_placement(popularity, 1, replicas=2) == 0).all()  # one rank: nothing to copy to
+    two = EP.balanced_placement(popularity, 8, replicas=2)
+    assert ((two >> 8) > 0).sum() == 2 and len(set(((two >> 8) & 0xff)[(two >> 8) > 0])) == 2  # two copies on two different ranks
+    assert EP.placement_load(popularity, two, 8) < EP.placement_load(popularity, EP.balanced_placement(popularity, 8, replicas=1), 8)
     assert EP.placement_load(popularity, EP.balanced_placement(popularity, 8), 8) > 1.12
     assert EP.placement_load(popularity, EP.balanced_placement(popularity, 8, replicas=1), 8) < 1.06
     # the plan sends the even tokens' pairs of that expert to the first rank and the odd tokens' to the second
