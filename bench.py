@@ -394,7 +394,7 @@ def reference_kernels_leg(dev) -> dict | None:
 
 
 def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: str, passes: int, batch: int = 16384,
-                        chunk: int = 2048, replicas: int = 1, engine_count: int = 2) -> dict:
+                        chunk: int = 2048, replicas: int = 1, engine_count: int = 2, returns: str = "auto") -> dict:
     """configs[4]: a batch of 16384 tokens through `layers` MoE layers, experts sharded 64/world per rank by measured
     popularity, tokens split evenly over the ranks (strong scaling), dispatch and combine per layer and chunk.  Between
     layers the next input is the RMS-normalised residual stream (this library's norm kernel), so layer l+1 depends on
@@ -411,6 +411,8 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
     if world > 1:  # at least one chunk per engine, so that one chunk's exchange overlaps the others' expert work
         chunk = min(chunk, max(256, local // engine_count))
     chunks = [(c, min(chunk, local - c)) for c in range(0, local, chunk)]
+    if returns == "auto":  # two halves pay for their extra launches on 2048-token chunks (40.1 against 40.5 ms on four GPUs), not on
+        returns = "split" if chunk >= 2048 else "plain"  # 1024-token chunks (22.3 against 22.0 ms on eight)
     g = torch.Generator(device=dev)
     g.manual_seed(500 + rank)
     x0 = bf16_values(torch.randn((local, HIDDEN), device=dev, generator=g))
@@ -434,7 +436,8 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
         # symmetric memory may be unavailable on a host (no peer access, no handle exchange): every rank then takes the
         # NCCL exchange, and the JSON line says which exchange ran
         try:  # engines with an exchange block each: the chunks of a layer go to them in turn, on a stream each
-            peer = [EP.PeerExchangePrefill.over_group(k, owners[0], cap=chunk * TOPK) for _ in range(engine_count)]
+            peer = [EP.PeerExchangePrefill.over_group(k, owners[0], cap=chunk * TOPK, fused_return=returns == "fused",
+                                                      split_return=returns == "split") for _ in range(engine_count)]
             failed = 0
         except Exception as error:  # noqa: BLE001 - any failure of the rendezvous means "not available here"
             print(f"rank {rank}: peer exchange unavailable ({type(error).__name__}: {error}); using NCCL all-to-all", file=sys.stderr)
@@ -522,7 +525,7 @@ def expert_parallel_leg(k, dev, world: int, rank: int, layers: int, exchange: st
         times.append(a.elapsed_time(b) / 1e3)
         assert k.bad_flag() == 0 and bool(torch.isfinite(x).all()), "expert-parallel prefill raised the error flag"
     return {"times": times, "batch": batch, "layers": layers, "chunk": chunk, "exchange": exchange, "parity_rows": parity_rows,
-            "engines": lanes,
+            "engines": lanes, "returns": returns,
             "placement": {"layers_with_a_second_copy_of_the_hottest_expert": int(sum(bool((np.asarray(o) >> 8).any()) for o in owners)),
                           "busiest_rank_over_mean_64_per_rank_exact": round(float(np.mean([a for a, _ in loads])), 4),
                           "busiest_rank_over_mean_as_run": round(float(np.mean([b for _, b in loads])), 4)}}
@@ -652,7 +655,7 @@ def run_ours(args):
         if world > 1 and args.ep_exchange == "peer":  # leave SMs to the other engine's exchange kernels beside the persistent GEMM
             B.check(k.lib.padra_prefill_set_reserved_sms(args.ep_reserved_sms), "padra_prefill_set_reserved_sms")
         ep = expert_parallel_leg(k, dev, world, rank, layers, args.ep_exchange, passes=args.ep_passes, replicas=args.ep_replicas,
-                                 engine_count=args.ep_engines)
+                                 engine_count=args.ep_engines, returns=args.ep_return)
         B.check(k.lib.padra_prefill_set_reserved_sms(0), "padra_prefill_set_reserved_sms")
     if world > 1:
         t = torch.tensor([seconds, e2e_seconds] + (ep["times"] if ep else []), device=dev, dtype=torch.float64)
@@ -682,7 +685,7 @@ def run_ours(args):
             "n_gpus": world, "scaling": "strong", "exchange": ep["exchange"] if world > 1 else "none", "ms_per_batch": best * 1e3,
             "ms_per_batch_min": min(ep["times"]) * 1e3, "passes": len(ep["times"]), "tokens_per_s": ep["batch"] / best,
             "tflops_all_gpus": flops / best / 1e12, "parity_checked": world > 1, "parity_rows": ep["parity_rows"],
-            "placement": ep["placement"], "chunk_tokens": ep["chunk"], "engines": ep["engines"],
+            "placement": ep["placement"], "chunk_tokens": ep["chunk"], "engines": ep["engines"], "return_mode": ep["returns"],
             "timing": "CUDA events per rank, max over ranks, median of passes"}
     line.update({
         "config": dict(base_config(layers), weight_bytes_resident=table.total_bytes,
@@ -754,6 +757,9 @@ def main():
                     help="k > 0: up to k of a layer's most popular experts are held by two ranks, as long as that lowers the "
                          "busiest rank's load; -k: held by two ranks in any case (exercises the path on two or four GPUs)")
     ap.add_argument("--ep-reserved-sms", type=int, default=0, help="SMs the grouped GEMM leaves free for the exchange kernels (several GPUs)")
+    ap.add_argument("--ep-return", default="auto", choices=["auto", "split", "fused", "plain"],
+                    help="how the down rows travel back: in two halves beside the second half's GEMM, from the GEMM's epilogue, "
+                         "or by one kernel after the GEMM")
     ap.add_argument("--ep-engines", type=int, default=2, help="exchange engines (blocks and streams) per rank that take a layer's chunks in turn")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers of distinct weights to rotate over (profiling: fewer)")
     args = ap.parse_args()

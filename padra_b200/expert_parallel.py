@@ -328,7 +328,7 @@ class PeerExchangePrefill:
         return lib.padra_ep_exchange_bytes(world, cap, hidden, None)
 
     @classmethod
-    def over_group(cls, kernels, owner, cap: int, group=None):
+    def over_group(cls, kernels, owner, cap: int, group=None, fused_return: bool = False, split_return: bool = True):
         """Exchange blocks in symmetric memory of a process group (one GPU per rank)."""
         import os
 
@@ -343,7 +343,8 @@ class PeerExchangePrefill:
         handle = symm_mem.rendezvous(block, group)
         torch.cuda.synchronize(kernels.t.device)
         dist.barrier(group)
-        engine = cls(kernels, owner, rank, world, cap, block, [int(p) for p in handle.buffer_ptrs])
+        engine = cls(kernels, owner, rank, world, cap, block, [int(p) for p in handle.buffer_ptrs], fused_return=fused_return,
+                     split_return=split_return)
         engine._handle = handle
         return engine
 
